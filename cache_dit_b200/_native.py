@@ -1,0 +1,205 @@
+"""ctypes binding of the C ABI declared in include/cache_dit_b200.h.
+
+The shared library is the product: there is no eager or CPU fallback.  `lib()` raises if the
+library is missing; every wrapper raises if it is handed a non-CUDA tensor.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import POINTER, c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_void_p
+
+import torch
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libcache_dit_b200.so")
+
+DTYPE_ID = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
+MAX_TAYLOR_TERMS = 5
+PRE_NONE, PRE_LAYERNORM_MOD, PRE_GELU_TANH = 0, 1, 2
+
+# name -> (restype, argtypes); mirrors include/cache_dit_b200.h one to one
+SIGNATURES = {
+  "cdb_abi_version": (c_int, []),
+  "cdb_status_string": (c_char_p, [c_int]),
+  "cdb_last_cuda_error": (c_char_p, []),
+  "cdb_rel_l1_scratch_bytes": (c_size_t, []),
+  "cdb_rel_l1": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p,
+                         c_size_t, c_void_p]),
+  "cdb_taylor_apply": (c_int, [c_void_p, POINTER(c_void_p), POINTER(c_float), POINTER(c_float), c_int,
+                               c_int, c_void_p, c_int64, c_int, c_void_p]),
+  "cdb_taylor_update": (c_int, [c_void_p, c_void_p, POINTER(c_void_p), POINTER(c_void_p), c_int, c_float,
+                                c_int64, c_int, c_void_p]),
+  "cdb_fp8_quant_rows": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
+  "cdb_fp8_quant_rows_fused": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p,
+                                       c_int64, c_int64, c_float, c_void_p, c_void_p, c_void_p]),
+  "cdb_fp8_gemm_rowscaled": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
+                                     c_int64, c_int64, c_int64, c_void_p, c_void_p]),
+}
+
+_lib = None
+
+
+class NativeLibraryError(RuntimeError):
+  pass
+
+
+def lib() -> ctypes.CDLL:
+  """Load libcache_dit_b200.so (once). Raises NativeLibraryError when it has not been built."""
+  global _lib
+  if _lib is None:
+    if not os.path.exists(LIB_PATH):
+      raise NativeLibraryError(
+        f"{LIB_PATH} is missing. Build it with `python -m cache_dit_b200.csrc.build` "
+        "(needs nvcc); cache_dit_b200 has no fallback path.")
+    handle = ctypes.CDLL(LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+      fn = getattr(handle, name)
+      fn.restype = res
+      fn.argtypes = args
+    _lib = handle
+  return _lib
+
+
+def check(status: int, what: str):
+  if status != 0:
+    L = lib()
+    msg = L.cdb_status_string(status).decode()
+    detail = L.cdb_last_cuda_error().decode() if status == 4 else ""
+    raise RuntimeError(f"{what} failed: {msg}" + (f" [{detail}]" if detail else ""))
+
+
+def _ptr(t):
+  return None if t is None else c_void_p(t.data_ptr())
+
+
+def _stream(t: torch.Tensor):
+  return c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _need_cuda(*tensors):
+  for t in tensors:
+    if t is not None and not t.is_cuda:
+      raise RuntimeError("cache_dit_b200 kernels take CUDA tensors only (no CPU fallback)")
+
+
+def _need_contig(*tensors):
+  for t in tensors:
+    if t is not None and not t.is_contiguous():
+      raise RuntimeError("cache_dit_b200 kernels need contiguous tensors")
+
+
+# scratch for the relative-L1 reduction: one zero-initialised buffer per (device, stream)
+_scratch = {}
+
+
+def rel_l1_scratch(device, stream_id: int) -> torch.Tensor:
+  key = (device.index if device.index is not None else torch.cuda.current_device(), stream_id)
+  buf = _scratch.get(key)
+  if buf is None:
+    buf = torch.zeros(lib().cdb_rel_l1_scratch_bytes(), dtype=torch.uint8, device=device)
+    _scratch[key] = buf
+  return buf
+
+
+def rel_l1(cur, base, prev, residual_out, means):
+  """See cdb_rel_l1. `means` is a float32[2] CUDA tensor that receives the two local means."""
+  _need_cuda(cur, base, prev, residual_out, means)
+  _need_contig(cur, base, prev, residual_out)
+  n = cur.numel()
+  for t in (base, prev, residual_out):
+    if t is not None and (t.numel() != n or t.dtype != cur.dtype):
+      raise RuntimeError("rel_l1: tensors must share shape and dtype")
+  scratch = None
+  if prev is not None:
+    scratch = rel_l1_scratch(cur.device, torch.cuda.current_stream(cur.device).cuda_stream)
+  st = lib().cdb_rel_l1(_ptr(cur), _ptr(base), _ptr(prev), _ptr(residual_out), n, DTYPE_ID[cur.dtype],
+                        _ptr(means), _ptr(scratch), 0 if scratch is None else scratch.numel(), _stream(cur))
+  check(st, "cdb_rel_l1")
+
+
+def taylor_apply(hidden, derivs, coef, power, add_hidden: bool, out):
+  _need_cuda(hidden, out, *derivs)
+  _need_contig(hidden, out, *derivs)
+  k = len(derivs)
+  n = out.numel()
+  for t in list(derivs) + ([hidden] if add_hidden else []):
+    if t.numel() != n or t.dtype != out.dtype:
+      raise RuntimeError("taylor_apply: tensors must share shape and dtype")
+  d = (c_void_p * k)(*[t.data_ptr() for t in derivs])
+  c = (c_float * k)(*coef)
+  p = (c_float * k)(*power)
+  st = lib().cdb_taylor_apply(_ptr(hidden) if add_hidden else None, d, c, p, k, int(add_hidden), _ptr(out),
+                              n, DTYPE_ID[out.dtype], _stream(out))
+  check(st, "cdb_taylor_apply")
+
+
+def taylor_update(after, before, prev, cur, n_new: int, window: float):
+  _need_cuda(after, before, *prev[:n_new], *cur[:n_new + 1])
+  _need_contig(after, before, *prev[:n_new], *cur[:n_new + 1])
+  n = after.numel()
+  for t in list(prev[:n_new]) + list(cur[:n_new + 1]) + ([before] if before is not None else []):
+    if t.numel() != n or t.dtype != after.dtype:
+      raise RuntimeError("taylor_update: tensors must share shape and dtype")
+  pp = (c_void_p * MAX_TAYLOR_TERMS)(*[t.data_ptr() for t in prev[:n_new]])
+  cc = (c_void_p * MAX_TAYLOR_TERMS)(*[t.data_ptr() for t in cur[:n_new + 1]])
+  st = lib().cdb_taylor_update(_ptr(after), _ptr(before), pp, cc, n_new, float(window), n,
+                               DTYPE_ID[after.dtype], _stream(after))
+  check(st, "cdb_taylor_update")
+
+
+def fp8_quant_rows(x2d, q, scale, preop=PRE_NONE, mod_shift=None, mod_scale=None, rows_per_batch=0,
+                   eps=0.0):
+  """x2d [rows, cols] bf16 (row stride may exceed cols); q [rows, cols] float8_e4m3fn; scale [rows] f32."""
+  _need_cuda(x2d, q, scale, mod_shift, mod_scale)
+  if x2d.dtype != torch.bfloat16 or x2d.dim() != 2 or x2d.stride(1) != 1:
+    raise RuntimeError("fp8_quant_rows: x must be a bf16 matrix with unit column stride")
+  rows, cols = x2d.shape
+  _need_contig(q, scale)
+  ld_mod = 0
+  if preop == PRE_LAYERNORM_MOD:
+    if mod_shift.dim() != 2 or mod_scale.dim() != 2 or mod_shift.stride(1) != 1 or mod_scale.stride(1) != 1 \
+        or mod_shift.stride(0) != mod_scale.stride(0) or mod_shift.dtype != torch.bfloat16 \
+        or mod_scale.dtype != torch.bfloat16:
+      raise RuntimeError("fp8_quant_rows: modulation must be two bf16 [batch, cols] matrices")
+    ld_mod = mod_shift.stride(0)
+  st = lib().cdb_fp8_quant_rows_fused(_ptr(x2d), rows, cols, x2d.stride(0) if rows > 1 else max(cols, x2d.stride(0)),
+                                      preop, _ptr(mod_shift), _ptr(mod_scale), rows_per_batch, ld_mod,
+                                      float(eps), _ptr(q), _ptr(scale), _stream(x2d))
+  check(st, "cdb_fp8_quant_rows")
+
+
+_status_words = {}
+
+
+def gemm_status_word(device) -> torch.Tensor:
+  idx = device.index if device.index is not None else torch.cuda.current_device()
+  w = _status_words.get(idx)
+  if w is None:
+    w = torch.zeros(1, dtype=torch.int32, device=device)
+    _status_words[idx] = w
+  return w
+
+
+def fp8_gemm_rowscaled(a_q, a_scale, w_q, w_scale, bias, out):
+  """out[M,N] bf16 = (a_q[M,K] @ w_q[N,K]^T) * a_scale[M] * w_scale[N] (+ bias[N])."""
+  _need_cuda(a_q, a_scale, w_q, w_scale, bias, out)
+  _need_contig(a_q, a_scale, w_q, w_scale, bias)
+  M, K = a_q.shape
+  N = w_q.shape[0]
+  if w_q.shape[1] != K or out.shape != (M, N) or out.stride(1) != 1 or out.dtype != torch.bfloat16:
+    raise RuntimeError("fp8_gemm_rowscaled: shape mismatch")
+  if a_scale.numel() != M or w_scale.numel() != N or a_scale.dtype != torch.float32 \
+      or w_scale.dtype != torch.float32:
+    raise RuntimeError("fp8_gemm_rowscaled: scales must be float32 [M] and [N]")
+  if bias is not None and (bias.dtype != torch.bfloat16 or bias.numel() != N):
+    raise RuntimeError("fp8_gemm_rowscaled: bias must be bf16 [N]")
+  st = lib().cdb_fp8_gemm_rowscaled(_ptr(a_q), _ptr(a_scale), _ptr(w_q), _ptr(w_scale), _ptr(bias), _ptr(out),
+                                    M, N, K, out.stride(0) if M > 1 else max(N, out.stride(0)),
+                                    _ptr(gemm_status_word(out.device)), _stream(out))
+  check(st, "cdb_fp8_gemm_rowscaled")
+
+
+def gemm_device_status(device) -> int:
+  """Non-zero if a bounded wait inside the GEMM kernel expired since the last reset (syncs)."""
+  return int(gemm_status_word(device).item())

@@ -1,0 +1,469 @@
+// Row-scaled FP8 (e4m3) GEMM for sm_100a: out[m,n] = (sum_k A[m,k] W[n,k]) * sa[m] * sw[n] (+ bias[n])
+//
+// Blackwell-native structure
+//   * operands: TMA (cp.async.bulk.tensor.2d, 128-byte swizzle) into a 4-stage shared-memory ring,
+//     one CTA per SM, every CTA loads its own tiles (no cluster-wide loads);
+//   * math: tcgen05.mma.cta_group::1.kind::f8f6f4, 128 x 256 x 32 per instruction, issued by one
+//     elected thread, fp32 accumulators in tensor memory (TMEM);
+//   * two 256-column TMEM accumulators so the epilogue of tile i overlaps the main loop of tile i+1;
+//   * epilogue: tcgen05.ld (32 lanes x 32 columns per warp), per-row x per-column scale, optional
+//     bias, bf16 pack, 16-byte stores;
+//   * persistent grid (one CTA per SM), static tile order with M fastest so the CTAs of a wave
+//     share weight tiles in L2.
+// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
+// warps 2..5 = epilogue (TMEM lane quarter = warp % 4).
+//
+// Every mbarrier wait is bounded: after ~2 s without progress the waiter raises a CTA-wide abort
+// flag, records a code in the caller's status word, all roles drain, TMEM is released and the
+// kernel returns, so a logic error cannot wedge the device.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+namespace cdb {
+
+constexpr int BM = 128;          // tile rows   (UMMA M)
+constexpr int BN = 256;          // tile cols   (UMMA N)
+constexpr int BK = 128;          // K bytes per stage = one 128-byte swizzle span of e4m3
+constexpr int UMMA_K = 32;       // K per tcgen05.mma for 8-bit inputs
+constexpr int STAGES = 4;
+constexpr int GEMM_THREADS = 192;
+constexpr int EPI_WARP0 = 2;
+constexpr int EPI_THREADS = 128;
+constexpr uint32_t TMEM_COLS = 512;  // 2 accumulators x 256 fp32 columns
+constexpr int A_STAGE_BYTES = BM * BK;
+constexpr int B_STAGE_BYTES = BN * BK;
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;
+
+struct __align__(8) GemmBarriers {
+  uint64_t full[STAGES];       // TMA bytes landed
+  uint64_t empty[STAGES];      // MMAs reading the stage retired
+  uint64_t acc_full[2];        // accumulator complete in TMEM
+  uint64_t acc_empty[2];       // epilogue drained the accumulator
+  uint32_t tmem_base;
+  volatile int abort_flag;
+};
+
+// dynamic shared memory: [<=1023 B alignment slack][STAGES x (A tile | B tile)][col scale][bias][barriers]
+constexpr int SMEM_TILE_BYTES = STAGES * STAGE_BYTES;
+constexpr int SMEM_EXTRA_BYTES = BN * 4 * 2 + (int)sizeof(GemmBarriers);
+constexpr int SMEM_TOTAL_BYTES = 1024 + SMEM_TILE_BYTES + SMEM_EXTRA_BYTES;
+
+// ---- PTX wrappers ------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait. Returns false if the CTA is aborting (or the wait itself ran out).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, GemmBarriers* gb,
+                                          int32_t* status_word, int code) {
+  uint64_t t0 = 0;
+  for (uint32_t it = 0;; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 255u) == 255u) {
+      if (gb->abort_flag) return false;
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > WAIT_LIMIT_NS) {
+        gb->abort_flag = 1;
+        if (status_word) atomicCAS(status_word, 0, code);
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(const CUtensorMap* map, uint64_t* bar, void* dst, int c0,
+                                            int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tcgen05_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                        uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+        "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),
+        "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),
+        "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor for a K-major tile stored as rows of 128 bytes with the
+// 128-byte swizzle (exactly what the TMA box writes): 8-row groups are 1024 bytes apart.
+//   bits [0,14)  start address >> 4        bits [16,30) leading byte offset >> 4 (unused: 1)
+//   bits [32,46) stride byte offset >> 4   bits [46,48) descriptor version = 1
+//   bits [61,64) layout type = 2 (128-byte swizzle)
+__device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+// Instruction descriptor, kind::f8f6f4: D = fp32, A = B = e4m3, both K-major, dense.
+//   bits [4,6) D format (1 = f32)   [7,10) A format (0 = e4m3)   [10,13) B format (0 = e4m3)
+//   bit 15 / 16 A / B major (0 = K) [17,23) N >> 3               [24,29) M >> 4
+constexpr uint32_t IDESC_E4M3_F32 = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
+// AND-reduction of a predicate over the 128 epilogue threads (named barrier 1).
+__device__ __forceinline__ bool epi_all(bool pred) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %1, 0;\n\t"
+      "bar.red.and.pred q, 1, %2, p;\n\t"
+      "selp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(r)
+      : "r"((uint32_t)pred), "n"(EPI_THREADS)
+      : "memory");
+  return r != 0;
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// ---- kernel --------------------------------------------------------------------------------
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+    fp8_gemm_rowscaled_kernel(const __grid_constant__ CUtensorMap map_a,
+                              const __grid_constant__ CUtensorMap map_w, const float* __restrict__ sa,
+                              const float* __restrict__ sw, const __nv_bfloat16* __restrict__ bias,
+                              __nv_bfloat16* __restrict__ out, int M, int N, int K, int64_t ld_out,
+                              int32_t* status_word) {
+  extern __shared__ uint8_t smem_raw[];
+  // 128-byte swizzle needs 1024-byte aligned tiles.
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  float* s_colscale = reinterpret_cast<float*>(smem + SMEM_TILE_BYTES);
+  float* s_bias = s_colscale + BN;
+  GemmBarriers* gb = reinterpret_cast<GemmBarriers*>(s_bias + BN);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int m_tiles = (M + BM - 1) / BM;
+  const int n_tiles = (N + BN - 1) / BN;
+  const int num_tiles = m_tiles * n_tiles;
+  const int k_blocks = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&gb->full[s], 1);
+      mbar_init(&gb->empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&gb->acc_full[b], 1);
+      mbar_init(&gb->acc_empty[b], EPI_THREADS / 32);
+    }
+    gb->abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(&gb->tmem_base)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = gb->tmem_base;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % m_tiles) * BM;
+        const int n0 = (tile / m_tiles) * BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1u;
+          ok = mbar_wait(&gb->empty[s], ph ^ 1u, gb, status_word, 1);
+          if (!ok) break;
+          uint8_t* a_dst = smem + s * STAGE_BYTES;
+          uint8_t* b_dst = a_dst + A_STAGE_BYTES;
+          mbar_expect_tx(&gb->full[s], STAGE_BYTES);
+          tma_load_2d(&map_a, &gb->full[s], a_dst, kb * BK, m0);
+          tma_load_2d(&map_w, &gb->full[s], b_dst, kb * BK, n0);
+        }
+      }
+      // Do not let the CTA retire while bulk copies into its shared memory are in flight:
+      // wait (bounded) until every armed stage has landed.
+      const uint32_t issued = it;
+      for (uint32_t j = (issued > STAGES ? issued - STAGES : 0); j < issued; ++j) {
+        const int s = j % STAGES;
+        const uint32_t ph = (j / STAGES) & 1u;
+        uint64_t t0 = global_timer_ns();
+        while (!mbar_try_wait(&gb->full[s], ph)) {
+          if (global_timer_ns() - t0 > WAIT_LIMIT_NS) break;
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      uint32_t it = 0, local_tile = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
+        const uint32_t buf = local_tile & 1u;
+        const uint32_t use = local_tile >> 1;  // how many times this buffer was used before
+        ok = mbar_wait(&gb->acc_empty[buf], (use & 1u) ^ 1u, gb, status_word, 2);
+        if (!ok) break;
+        tcgen05_fence_after();
+        const uint32_t tmem_d = tmem_base + buf * BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1u;
+          ok = mbar_wait(&gb->full[s], ph, gb, status_word, 3);
+          if (!ok) break;
+          tcgen05_fence_after();
+          const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
+          const uint32_t b_addr = a_addr + A_STAGE_BYTES;
+          const uint64_t adesc = make_kmajor_sw128_desc(a_addr);
+          const uint64_t bdesc = make_kmajor_sw128_desc(b_addr);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // advance 32 bytes along K inside the swizzle span: +2 in the (addr >> 4) field
+            umma_f8(tmem_d, adesc + (uint64_t)(k * (UMMA_K >> 4)), bdesc + (uint64_t)(k * (UMMA_K >> 4)),
+                    IDESC_E4M3_F32, (kb | k) != 0 ? 1u : 0u);
+          }
+          tcgen05_commit(&gb->empty[s]);  // frees the stage once these MMAs retire
+        }
+        if (ok) tcgen05_commit(&gb->acc_full[buf]);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------- epilogue (warps 2..5) ----------------
+    const int quarter = warp & 3;            // TMEM lanes [32*quarter, 32*quarter + 32)
+    const int et = threadIdx.x - EPI_WARP0 * 32;  // 0..127
+    uint32_t local_tile = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
+      const int m0 = (tile % m_tiles) * BM;
+      const int n0 = (tile / m_tiles) * BN;
+      const uint32_t buf = local_tile & 1u;
+      const uint32_t use = local_tile >> 1;
+      // (1) the previous tile's readers of the staged column scales are done
+      asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
+      for (int c = et; c < BN; c += EPI_THREADS) {
+        const int col = n0 + c;
+        s_colscale[c] = col < N ? __ldg(sw + col) : 0.f;
+        s_bias[c] = (bias != nullptr && col < N) ? __bfloat162float(bias[col]) : 0.f;
+      }
+      ok = mbar_wait(&gb->acc_full[buf], use & 1u, gb, status_word, 4);
+      // (2) one barrier publishes the staged scales AND makes the continue/abort decision uniform
+      // over the four epilogue warps, so no warp can be left alone at barrier (1).
+      ok = epi_all(ok);
+      if (!ok) break;
+      tcgen05_fence_after();
+
+      const int row = m0 + quarter * 32 + lane;
+      const float rs = row < M ? __ldg(sa + row) : 0.f;
+      __nv_bfloat16* orow = out + (int64_t)row * ld_out + n0;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t acc[32];
+        tmem_ld_32x32b_x32(taddr + c0, acc);
+        tmem_ld_wait();
+        if (row < M) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {  // 8 columns = one 16-byte store
+            const int cb = c0 + g * 8;
+            if (n0 + cb < N) {  // N % 8 == 0: a group is entirely inside or outside
+              uint32_t w[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const int c = cb + 2 * j;
+                float v0 = __uint_as_float(acc[g * 8 + 2 * j]) * rs * s_colscale[c] + s_bias[c];
+                float v1 = __uint_as_float(acc[g * 8 + 2 * j + 1]) * rs * s_colscale[c + 1] + s_bias[c + 1];
+                w[j] = pack_bf16x2(v0, v1);
+              }
+              *reinterpret_cast<uint4*>(orow + cb) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+          }
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&gb->acc_empty[buf]);
+    }
+  }
+
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS)
+                 : "memory");
+  }
+}
+
+// ---- host side -----------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// [rows, K] bytes, row-major; box = (128 bytes of K) x box_rows, 128-byte swizzle, zero fill.
+static bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t k, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {k, rows};
+  cuuint64_t strides[1] = {k};
+  cuuint32_t box[2] = {(cuuint32_t)BK, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+struct MapKey {
+  const void* p;
+  uint64_t rows, k;
+  uint32_t box_rows;
+  bool operator==(const MapKey& o) const {
+    return p == o.p && rows == o.rows && k == o.k && box_rows == o.box_rows;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    return std::hash<const void*>()(k.p) ^ (k.rows * 0x9E3779B97F4A7C15ull) ^ (k.k << 20) ^ k.box_rows;
+  }
+};
+
+// Encoding a tensor map costs a few microseconds of host time; weights keep their address for the
+// life of the model, activations come from a caching allocator, so a small cache hits almost always.
+static bool cached_map(CUtensorMap* out, const void* base, uint64_t rows, uint64_t k, uint32_t box_rows) {
+  static std::mutex mu;
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  MapKey key{base, rows, k, box_rows};
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) {
+    *out = it->second;
+    return true;
+  }
+  CUtensorMap m;
+  if (!make_map(&m, base, rows, k, box_rows)) return false;
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, m);
+  *out = m;
+  return true;
+}
+
+}  // namespace cdb
+
+using namespace cdb;
+
+extern "C" int cdb_fp8_gemm_rowscaled(const void* a_q, const float* a_scale, const void* w_q,
+                                      const float* w_scale, const void* bias, void* out, int64_t M,
+                                      int64_t N, int64_t K, int64_t ld_out, int32_t* status_word,
+                                      void* stream) {
+  if (!a_q || !a_scale || !w_q || !w_scale || !out || M < 0 || N <= 0 || K <= 0 || ld_out < N)
+    return CDB_ERR_BAD_ARGUMENT;
+  if (M == 0) return CDB_OK;
+  if (K % 16 != 0 || N % 8 != 0 || ld_out % 8 != 0 || !aligned16(a_q) || !aligned16(w_q) || !aligned16(out) ||
+      M > INT32_MAX || N > INT32_MAX || K > INT32_MAX)
+    return CDB_ERR_UNSUPPORTED;
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute(fp8_gemm_rowscaled_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    SMEM_TOTAL_BYTES);
+  });
+  CDB_CUDA_CHECK(attr_err);
+  CUtensorMap map_a, map_w;
+  if (!cached_map(&map_a, a_q, (uint64_t)M, (uint64_t)K, BM) ||
+      !cached_map(&map_w, w_q, (uint64_t)N, (uint64_t)K, BN)) {
+    set_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled");
+    return CDB_ERR_CUDA;
+  }
+  const int64_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int sms = sm_count();
+  const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
+  fp8_gemm_rowscaled_kernel<<<grid, GEMM_THREADS, SMEM_TOTAL_BYTES, static_cast<cudaStream_t>(stream)>>>(
+      map_a, map_w, a_scale, w_scale, static_cast<const __nv_bfloat16*>(bias),
+      static_cast<__nv_bfloat16*>(out), (int)M, (int)N, (int)K, ld_out, status_word);
+  CDB_CUDA_CHECK(cudaGetLastError());
+  return CDB_OK;
+}

@@ -1,0 +1,139 @@
+/*
+ * C ABI of the B200 (sm_100a) hot-path kernels behind cache-dit's public Python API.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream handle
+ * (a cudaStream_t passed as void*), enqueues work on that stream and returns a
+ * status code (0 = success).  Nothing here allocates device memory unless stated;
+ * the caller owns all buffers.  There is no CPU fallback: the functions need a
+ * CUDA device of compute capability 10.0.
+ *
+ * Each declaration names the part of the reference (vipshop/cache-dit, paths
+ * inside that project) whose eager PyTorch code it replaces.
+ */
+#ifndef CACHE_DIT_B200_H_
+#define CACHE_DIT_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define CDB_API __attribute__((visibility("default")))
+#else
+#define CDB_API
+#endif
+
+/* Storage dtype of activation tensors. */
+enum cdb_dtype { CDB_F32 = 0, CDB_BF16 = 1, CDB_F16 = 2 };
+
+/* Status codes. */
+enum cdb_status {
+  CDB_OK = 0,
+  CDB_ERR_BAD_ARGUMENT = 1,   /* null pointer, negative size, unknown dtype, ... */
+  CDB_ERR_UNSUPPORTED = 2,    /* shape or alignment the kernel does not cover */
+  CDB_ERR_SCRATCH_TOO_SMALL = 3,
+  CDB_ERR_CUDA = 4,           /* a CUDA runtime / driver call failed; see cdb_last_cuda_error */
+  CDB_ERR_NO_DEVICE = 5,      /* no sm_100 device is current */
+  CDB_ERR_DEVICE_TIMEOUT = 6  /* a bounded device-side wait ran out (read from a status word) */
+};
+
+#define CDB_MAX_TAYLOR_TERMS 5 /* Taylor order <= 4: terms dY[0..4] */
+
+CDB_API int cdb_abi_version(void);
+CDB_API const char* cdb_status_string(int status);
+/* Text of the last CUDA error seen by this library on the calling thread ("" if none). */
+CDB_API const char* cdb_last_cuda_error(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Relative-L1 check.  Replaces
+ *   Fn residual formation           src/cache_dit/caching/cache_blocks/pattern_base.py:195
+ *   (t1-t2).abs().mean(), t1.abs().mean()
+ *                                   src/cache_dit/caching/cache_contexts/cache_manager.py:609-610
+ * One pass over the tensors:
+ *   r      = base ? round_dtype(cur - base) : cur          (n elements of `dtype`)
+ *   if residual_out: residual_out = r
+ *   if prev:  means[0] = round_dtype( sum |round_dtype(prev - r)| / n )
+ *             means[1] = round_dtype( sum |prev| / n )
+ * `means` is two float32 on the device.  They are the two 0-dim tensors the reference
+ * all-reduces (cache_manager.py:612-614) and then divides (cache_manager.py:619).
+ * `scratch` is device memory of at least cdb_rel_l1_scratch_bytes() bytes that must be
+ * zero-filled once before its first use; the kernel leaves it zeroed for the next launch.
+ * Launches that share one scratch buffer must be ordered on one stream.
+ * ---------------------------------------------------------------------------------------- */
+CDB_API size_t cdb_rel_l1_scratch_bytes(void);
+CDB_API int cdb_rel_l1(const void* cur, const void* base, const void* prev, void* residual_out,
+               int64_t n, int dtype, float* means, void* scratch, size_t scratch_bytes,
+               void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Cached-residual apply.  Replaces
+ *   TaylorSeerState.approximate     src/cache_dit/caching/cache_contexts/calibrators/taylorseer.py:91-104
+ *   hidden_states_prev + hidden_states
+ *                                   src/cache_dit/caching/cache_contexts/cache_manager.py:830-834
+ *   approx = sum_i round(round(coef[i] * derivs[i]) * power[i])      (rounded after every op)
+ *   out    = add_hidden ? round(approx + hidden) : approx
+ * coef[i] = 1/i!, power[i] = elapsed^i are supplied by the host.  `out` may alias `hidden`.
+ * n_terms in [1, CDB_MAX_TAYLOR_TERMS]; a plain (non-Taylor) cached buffer is n_terms = 1.
+ * ---------------------------------------------------------------------------------------- */
+CDB_API int cdb_taylor_apply(const void* hidden, const void* const* derivs, const float* coef,
+                     const float* power, int n_terms, int add_hidden, void* out, int64_t n,
+                     int dtype, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * TaylorSeer derivative update.  Replaces
+ *   Mn residual formation           src/cache_dit/caching/cache_blocks/pattern_base.py:414,418
+ *   TaylorSeerState.derivative      src/cache_dit/caching/cache_contexts/calibrators/taylorseer.py:68-89
+ *   y       = before ? round(after - before) : after
+ *   cur[0]  = y                      (written unless cur[0] == after and before == NULL)
+ *   cur[i+1]= round(round(cur[i] - prev[i]) / window)   for i < n_new
+ * n_new in [0, CDB_MAX_TAYLOR_TERMS-1]: how many finite differences the host state allows.
+ * `cur[*]` must not alias `prev[*]`.
+ * ---------------------------------------------------------------------------------------- */
+CDB_API int cdb_taylor_update(const void* after, const void* before, const void* const* prev,
+                      void* const* cur, int n_new, float window, int64_t n, int dtype,
+                      void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Per-row dynamic FP8 (e4m3fn) quantization.  Replaces torchao's dynamic activation
+ * quantization selected by the reference at
+ *   src/cache_dit/quantization/torchao/quantize_ao.py:540-558  (PerRow, e4m3, zero scale -> 1 at :43-71)
+ *   scale[r] = amax_r / 448 (1 if the row is all zero); q = saturate_e4m3(x / scale[r])
+ * x is [rows, cols] bf16 row-major with row stride `ld_x` elements; q is [rows, cols] bytes,
+ * contiguous; scale is [rows] float32.  Also used once per weight at load time ([N, K] rows).
+ * ---------------------------------------------------------------------------------------- */
+CDB_API int cdb_fp8_quant_rows(const void* x, int64_t rows, int64_t cols, int64_t ld_x, void* q,
+                       float* scale, void* stream);
+
+/* Producer-fused variants: the bf16 tensor the reference would write and re-read is never
+ * materialised.  pre-op selects what is applied to each element before quantization.
+ *   CDB_PRE_LAYERNORM_MOD: y = layernorm(x_row, eps) * (1 + mod_scale[b]) + mod_shift[b]
+ *                          (adaLN-modulated LayerNorm without affine; b = row / rows_per_batch)
+ *   CDB_PRE_GELU_TANH:     y = gelu_tanh(x)
+ * Intermediate y is rounded to bf16 before quantization, as the unfused bf16 pipeline does. */
+enum cdb_preop { CDB_PRE_NONE = 0, CDB_PRE_LAYERNORM_MOD = 1, CDB_PRE_GELU_TANH = 2 };
+CDB_API int cdb_fp8_quant_rows_fused(const void* x, int64_t rows, int64_t cols, int64_t ld_x, int preop,
+                             const void* mod_shift, const void* mod_scale, int64_t rows_per_batch,
+                             int64_t ld_mod, float eps, void* q, float* scale, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Row-scaled FP8 GEMM.  Replaces the torch._scaled_mm call at
+ *   src/cache_dit/quantization/torchao/_scaled_mm.py:62-91
+ *   out[m, n] = (sum_k a_q[m, k] * w_q[n, k]) * a_scale[m] * w_scale[n] (+ bias[n])
+ * a_q [M, K] e4m3 row-major, w_q [N, K] e4m3 row-major (the linear layer's weight layout),
+ * scales float32, bias bf16 or NULL, out [M, N] bf16 row-major with row stride ld_out.
+ * Requirements: K % 16 == 0, N % 8 == 0, pointers 16-byte aligned.  Accumulation is fp32 in
+ * tensor memory (tcgen05).  `status_word` (device int32, may be NULL) receives a non-zero
+ * value if a bounded in-kernel wait expired.
+ * ---------------------------------------------------------------------------------------- */
+CDB_API int cdb_fp8_gemm_rowscaled(const void* a_q, const float* a_scale, const void* w_q,
+                           const float* w_scale, const void* bias, void* out, int64_t M,
+                           int64_t N, int64_t K, int64_t ld_out, int32_t* status_word,
+                           void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CACHE_DIT_B200_H_ */

@@ -1,0 +1,50 @@
+"""CPU checks of the FP8 restatement: the e4m3 grid against torch's own cast, quantizer properties."""
+import numpy as np
+import torch
+
+from oracle import fp8_oracle as F
+
+
+def test_e4m3_round_and_codes_match_torch_cast():
+  g = torch.Generator().manual_seed(0)
+  x = torch.randn(200000, generator=g) * torch.exp(3 * torch.randn(200000, generator=g))
+  x = torch.cat([x, torch.tensor([0.0, -0.0, 448.0, -448.0, 1e-9, 2.0**-9, 2.0**-10, 3 * 2.0**-10,
+                                  0.0155, 447.9, 464.0, 1e6, -1e6])])
+  clamped = x.clamp(-448, 448)
+  want = clamped.to(torch.float8_e4m3fn)
+  got_vals = F.e4m3_round(x.numpy())
+  np.testing.assert_array_equal(got_vals, want.float().numpy())
+  np.testing.assert_array_equal(F.e4m3_encode(got_vals), want.view(torch.uint8).numpy())
+  np.testing.assert_array_equal(F.e4m3_decode(want.view(torch.uint8).numpy()), want.float().numpy())
+
+
+def test_all_256_codes_round_trip():
+  codes = np.arange(256, dtype=np.uint8)
+  codes = codes[(codes & 0x7F) != 0x7F]  # 0x7F / 0xFF are NaN in e4m3fn
+  vals = F.e4m3_decode(codes)
+  keep = ~((vals == 0) & np.signbit(vals))
+  np.testing.assert_array_equal(F.e4m3_encode(vals)[keep], codes[keep])
+
+
+def test_quantize_rows_properties():
+  rng = np.random.RandomState(0)
+  x = rng.randn(64, 256).astype(np.float32)
+  x[3] = 0.0
+  x[5, 7] = 300.0
+  codes, scale = F.quantize_rows(x)
+  assert scale[3] == 1.0 and not codes[3].any()
+  deq = F.e4m3_decode(codes) * scale[:, None]
+  # the row maximum maps onto +-448 exactly and is recovered to float32 rounding
+  np.testing.assert_allclose(np.abs(deq).max(axis=1)[[0, 5]], np.abs(x).max(axis=1)[[0, 5]], rtol=1e-6)
+  rel = np.linalg.norm(deq - x) / np.linalg.norm(x)
+  assert rel < 0.04
+
+
+def test_fp8_linear_close_to_fp32_linear():
+  rng = np.random.RandomState(1)
+  x = F.round_bf16(rng.randn(96, 512).astype(np.float32))
+  w = F.round_bf16((0.02 * rng.randn(128, 512)).astype(np.float32))
+  b = F.round_bf16(rng.randn(128).astype(np.float32))
+  got = F.fp8_linear(x, w, b)
+  want = x @ w.T + b
+  assert np.linalg.norm(got - want) / np.linalg.norm(want) < 0.06

@@ -1,0 +1,262 @@
+"""Kernel-level parity on a B200: every C-ABI entry point against the numpy oracle."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import cache_oracle as O
+from oracle import fp8_oracle as F
+
+pytestmark = pytest.mark.gpu
+
+TD = {"fp32": torch.float32, "bf16": torch.bfloat16, "fp16": torch.float16}
+ULP = {"fp32": 1e-6, "bf16": 2.0**-8, "fp16": 2.0**-11}
+
+
+@pytest.fixture(scope="module")
+def nat():
+  from cache_dit_b200 import _native
+  _native.lib()
+  return _native
+
+
+def make(shape, dtype, seed, scale=1.0, device="cuda"):
+  g = torch.Generator().manual_seed(seed)
+  t = (torch.randn(shape, generator=g) * scale).to(TD[dtype])
+  return t.to(device), t.float().numpy()
+
+
+# ------------------------------------------------------------------------------ rel-L1
+@pytest.mark.parametrize("dtype", ["bf16", "fp32", "fp16"])
+@pytest.mark.parametrize("shape", [(1, 37, 72), (2, 19, 50), (1, 1, 5), (1, 512, 3072), (1, 4608, 3072)])
+@pytest.mark.parametrize("fused_residual", [False, True])
+def test_rel_l1_matches_oracle(nat, dtype, shape, fused_residual):
+  prev_d, prev = make(shape, dtype, 1)
+  means = torch.zeros(2, dtype=torch.float32, device="cuda")
+  if fused_residual:
+    h0_d, h0 = make(shape, dtype, 2)
+    noise_d, noise = make(shape, dtype, 3, 0.05)
+    h_d = (prev_d.float() + h0_d.float() + noise_d.float()).to(TD[dtype])
+    h = h_d.float().cpu().numpy()
+    res_d = torch.empty_like(h_d)
+    nat.rel_l1(h_d, h0_d, prev_d, res_d, means)
+    cur = O.residual(h, h0, dtype)
+    np.testing.assert_array_equal(res_d.float().cpu().numpy(), cur)
+  else:
+    noise_d, noise = make(shape, dtype, 3, 0.05)
+    cur_d = (prev_d.float() + noise_d.float()).to(TD[dtype])
+    cur = cur_d.float().cpu().numpy()
+    nat.rel_l1(cur_d, None, prev_d, None, means)
+  md, mp = O.local_means(prev, cur, dtype)
+  got = means.cpu().numpy()
+  # sums are accumulated in a different order than numpy's: allow one unit in the last place of
+  # the storage dtype on each mean (usually they are identical)
+  assert abs(got[0] - md) <= ULP[dtype] * abs(md), (got, md, mp)
+  assert abs(got[1] - mp) <= ULP[dtype] * abs(mp), (got, md, mp)
+  diff = float(O.rnd(np.float32(got[0]) / np.float32(got[1]), dtype))
+  assert abs(diff - O.rel_l1(prev, cur, dtype)) <= 1e-3 * diff + 2 * ULP[dtype] * diff
+
+
+def test_rel_l1_unaligned_views_and_repeat_launches(nat):
+  base_d, _ = make((4099, ), "bf16", 5)
+  other_d, _ = make((4099, ), "bf16", 6)
+  prev_d, cur_d = base_d[1:], other_d[1:]  # 4098 elements each, 2 bytes past a 16-byte boundary
+  means = torch.zeros(2, dtype=torch.float32, device="cuda")
+  want = O.local_means(prev_d.float().cpu().numpy(), cur_d.float().cpu().numpy(), "bf16")
+  for _ in range(3):  # the scratch ticket resets itself between launches
+    means.zero_()
+    nat.rel_l1(cur_d, None, prev_d, None, means)
+    got = means.cpu().numpy()
+    assert abs(got[0] - want[0]) <= 2.0**-8 * want[0]
+    assert abs(got[1] - want[1]) <= 2.0**-8 * want[1]
+
+
+def test_rel_l1_residual_only_and_run_to_run_determinism(nat):
+  h_d, h = make((1, 333, 129), "bf16", 7)
+  h0_d, h0 = make((1, 333, 129), "bf16", 8)
+  res_d = torch.empty_like(h_d)
+  nat.rel_l1(h_d, h0_d, None, res_d, None)
+  np.testing.assert_array_equal(res_d.float().cpu().numpy(), O.residual(h, h0, "bf16"))
+  prev_d, _ = make((1, 4608, 3072), "fp32", 9)
+  cur_d, _ = make((1, 4608, 3072), "fp32", 10)
+  m1 = torch.zeros(2, dtype=torch.float32, device="cuda")
+  m2 = torch.zeros(2, dtype=torch.float32, device="cuda")
+  nat.rel_l1(cur_d, None, prev_d, None, m1)
+  nat.rel_l1(cur_d, None, prev_d, None, m2)
+  assert torch.equal(m1, m2)
+
+
+# ------------------------------------------------------------------------------ Taylor
+@pytest.mark.parametrize("dtype", ["bf16", "fp32", "fp16"])
+@pytest.mark.parametrize("terms", [1, 2, 3, 5])
+@pytest.mark.parametrize("shape,add", [((1, 37, 72), True), ((1, 7, 13), True), ((1, 512, 3072), True),
+                                       ((1, 37, 72), False)])
+def test_taylor_apply_matches_oracle(nat, dtype, terms, shape, add):
+  import math
+  hid_d, hid = make(shape, dtype, 20)
+  ds = [make(shape, dtype, 21 + i, 0.3**i) for i in range(terms)]
+  elapsed = 3
+  out_d = torch.empty_like(hid_d)
+  nat.taylor_apply(hid_d, [d[0] for d in ds], [1.0 / math.factorial(i) for i in range(terms)],
+                   [float(elapsed**i) for i in range(terms)], add, out_d)
+  approx = O.taylor_series([d[1] for d in ds], elapsed, dtype)
+  want = O.apply_add(approx, hid, dtype) if add else approx
+  np.testing.assert_array_equal(out_d.float().cpu().numpy(), want)
+
+
+def test_taylor_apply_in_place(nat):
+  hid_d, hid = make((1, 100, 64), "bf16", 30)
+  d0, d0n = make((1, 100, 64), "bf16", 31)
+  d1, d1n = make((1, 100, 64), "bf16", 32, 0.1)
+  nat.taylor_apply(hid_d, [d0, d1], [1.0, 1.0], [1.0, 2.0], True, hid_d)
+  want = O.apply_add(O.taylor_series([d0n, d1n], 2, "bf16"), hid, "bf16")
+  np.testing.assert_array_equal(hid_d.float().cpu().numpy(), want)
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "fp32", "fp16"])
+@pytest.mark.parametrize("n_new", [0, 1, 2, 4])
+@pytest.mark.parametrize("shape", [(1, 37, 72), (1, 7, 13), (1, 512, 3072)])
+@pytest.mark.parametrize("fused_residual", [False, True])
+def test_taylor_update_matches_oracle(nat, dtype, n_new, shape, fused_residual):
+  after_d, after = make(shape, dtype, 40)
+  before_d, before = make(shape, dtype, 41) if fused_residual else (None, None)
+  prev = [make(shape, dtype, 42 + i, 0.5) for i in range(n_new)]
+  cur_d = [torch.empty_like(after_d) for _ in range(n_new + 1)]
+  window = 3
+  nat.taylor_update(after_d, before_d, [p[0] for p in prev], cur_d, n_new, float(window))
+  y = O.residual(after, before, dtype) if fused_residual else after
+  ladder = O.taylor_derivatives(y, [p[1] for p in prev] + [None], window, True, dtype)
+  for i in range(n_new + 1):
+    np.testing.assert_array_equal(cur_d[i].float().cpu().numpy(), ladder[i], err_msg=f"order {i}")
+
+
+# ------------------------------------------------------------------------------ FP8 quantization
+def activations(rows, cols, seed):
+  """N(0,1) with 0.1 % of the elements scaled by 20 (outliers), as bf16."""
+  g = torch.Generator().manual_seed(seed)
+  x = torch.randn(rows, cols, generator=g)
+  mask = torch.rand(rows, cols, generator=g) < 1e-3
+  x = torch.where(mask, x * 20.0, x).to(torch.bfloat16)
+  return x.cuda(), x.float().numpy()
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 8), (5, 72), (33, 3072), (257, 5120), (64, 12288), (16, 13824),
+                                       (8, 15360), (4, 16384), (4608, 3072)])
+def test_fp8_quant_rows_matches_oracle(nat, rows, cols):
+  x_d, x = activations(rows, cols, rows + cols)
+  if rows > 2:
+    x_d[2].zero_()
+    x[2] = 0.0
+  q = torch.empty(rows, cols, dtype=torch.float8_e4m3fn, device="cuda")
+  s = torch.empty(rows, dtype=torch.float32, device="cuda")
+  nat.fp8_quant_rows(x_d, q, s)
+  codes, scale = F.quantize_rows(x)
+  np.testing.assert_array_equal(s.cpu().numpy(), scale)
+  np.testing.assert_array_equal(q.view(torch.uint8).cpu().numpy(), codes)
+
+
+def test_fp8_quant_rows_strided_input(nat):
+  x_d, x = activations(40, 1024, 3)
+  view = x_d[:, 256:768]
+  q = torch.empty(40, 512, dtype=torch.float8_e4m3fn, device="cuda")
+  s = torch.empty(40, dtype=torch.float32, device="cuda")
+  nat.fp8_quant_rows(view, q, s)
+  codes, scale = F.quantize_rows(x[:, 256:768])
+  np.testing.assert_array_equal(s.cpu().numpy(), scale)
+  np.testing.assert_array_equal(q.view(torch.uint8).cpu().numpy(), codes)
+
+
+def _close_codes(q, s, want_vals, frac=2e-3, rel=2e-3):
+  """Fused pre-ops use device transcendental / fp32 statistics: a few elements may land on the
+  neighbouring bf16 value before quantization.  Compare dequantized values instead of codes."""
+  got = F.e4m3_decode(q.view(torch.uint8).cpu().numpy()) * s.cpu().numpy()[:, None]
+  codes, scale = F.quantize_rows(want_vals)
+  want = F.e4m3_decode(codes) * scale[:, None]
+  mism = np.mean(got != want)
+  err = np.linalg.norm(got - want) / max(np.linalg.norm(want), 1e-30)
+  assert mism < frac and err < rel, (mism, err)
+
+
+@pytest.mark.parametrize("rows,cols,batch", [(6, 72, 2), (512, 3072, 1), (96, 5120, 3)])
+def test_fp8_quant_fused_layernorm_modulate(nat, rows, cols, batch):
+  x_d, x = activations(rows, cols, 11)
+  sh_d, sh = make((batch, cols), "bf16", 12, 0.2)
+  sc_d, sc = make((batch, cols), "bf16", 13, 0.2)
+  q = torch.empty(rows, cols, dtype=torch.float8_e4m3fn, device="cuda")
+  s = torch.empty(rows, dtype=torch.float32, device="cuda")
+  rpb = rows // batch
+  nat.fp8_quant_rows(x_d, q, s, nat.PRE_LAYERNORM_MOD, sh_d, sc_d, rpb, 1e-6)
+  want = np.concatenate([F.layernorm_modulate(x[b * rpb:(b + 1) * rpb], sh[b], sc[b], 1e-6)
+                         for b in range(batch)])
+  _close_codes(q, s, want)
+
+
+@pytest.mark.parametrize("rows,cols", [(6, 72), (256, 12288)])
+def test_fp8_quant_fused_gelu(nat, rows, cols):
+  x_d, x = activations(rows, cols, 14)
+  q = torch.empty(rows, cols, dtype=torch.float8_e4m3fn, device="cuda")
+  s = torch.empty(rows, dtype=torch.float32, device="cuda")
+  nat.fp8_quant_rows(x_d, q, s, nat.PRE_GELU_TANH)
+  _close_codes(q, s, F.gelu_tanh(x))
+
+
+# ------------------------------------------------------------------------------ FP8 GEMM
+def rel_fro(a, b):
+  return float(np.linalg.norm(a.astype(np.float64) - b.astype(np.float64)) /
+               max(np.linalg.norm(b.astype(np.float64)), 1e-30))
+
+
+@pytest.mark.parametrize("M,N,K,bias", [
+  (128, 256, 128, False), (128, 256, 512, True), (1, 8, 16, False), (200, 264, 144, True),
+  (130, 520, 3072, False), (512, 3072, 3072, True), (4608, 3072, 3072, False),
+  (1024, 12288, 3072, True), (1024, 3072, 12288, False), (640, 13824, 5120, False),
+])
+def test_fp8_gemm_matches_oracle(nat, M, N, K, bias):
+  x_d, x = activations(M, K, M + N + K)
+  g = torch.Generator().manual_seed(99)
+  w = (0.02 * torch.randn(N, K, generator=g)).to(torch.bfloat16)
+  b = torch.randn(N, generator=g).to(torch.bfloat16) if bias else None
+  w_d = w.cuda()
+  aq = torch.empty(M, K, dtype=torch.float8_e4m3fn, device="cuda")
+  sa = torch.empty(M, dtype=torch.float32, device="cuda")
+  wq = torch.empty(N, K, dtype=torch.float8_e4m3fn, device="cuda")
+  sw = torch.empty(N, dtype=torch.float32, device="cuda")
+  nat.fp8_quant_rows(x_d, aq, sa)
+  nat.fp8_quant_rows(w_d, wq, sw)
+  out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+  nat.gemm_status_word(out.device).zero_()
+  nat.fp8_gemm_rowscaled(aq, sa, wq, sw, None if b is None else b.cuda(), out)
+  torch.cuda.synchronize()
+  assert nat.gemm_device_status(out.device) == 0
+  want = F.scaled_mm(aq.view(torch.uint8).cpu().numpy(), sa.cpu().numpy(),
+                     wq.view(torch.uint8).cpu().numpy(), sw.cpu().numpy(),
+                     None if b is None else b.float().numpy())
+  got = out.float().cpu().numpy()
+  assert np.isfinite(got).all()
+  err = rel_fro(got, want)
+  # north-star tolerance is 2e-2 relative Frobenius; identical quantized operands and fp32
+  # accumulation leave only bf16 output rounding flips, so hold the kernel to a far tighter bar
+  assert err < 2e-3, err
+  # and against the un-quantized bf16 linear it must stay inside FP8's own error (~4 %)
+  ref = x @ w.float().numpy().T + (0 if b is None else b.float().numpy())
+  assert rel_fro(got, ref) < 8e-2
+
+
+def test_fp8_gemm_strided_output_and_back_to_back(nat):
+  M, N, K = 256, 512, 256
+  x_d, _ = activations(M, K, 1)
+  w_d, _ = activations(N, K, 2)
+  aq = torch.empty(M, K, dtype=torch.float8_e4m3fn, device="cuda")
+  sa = torch.empty(M, dtype=torch.float32, device="cuda")
+  wq = torch.empty(N, K, dtype=torch.float8_e4m3fn, device="cuda")
+  sw = torch.empty(N, dtype=torch.float32, device="cuda")
+  nat.fp8_quant_rows(x_d, aq, sa)
+  nat.fp8_quant_rows(w_d, wq, sw)
+  big = torch.zeros(M, 2 * N, dtype=torch.bfloat16, device="cuda")
+  dense = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+  for _ in range(3):
+    nat.fp8_gemm_rowscaled(aq, sa, wq, sw, None, big[:, N:])
+    nat.fp8_gemm_rowscaled(aq, sa, wq, sw, None, dense)
+  torch.cuda.synchronize()
+  assert torch.equal(big[:, N:], dense)
+  assert not big[:, :N].any()
+  assert nat.gemm_device_status(dense.device) == 0
