@@ -5,10 +5,12 @@
 //   taylor_update_kernel Mn-residual formation + finite-difference derivative ladder
 //
 // All three are HBM-bound (no reuse), so the design goals are: touch every byte once, keep
-// >= 4 independent 16-byte loads in flight per thread, size the grid to one resident wave.
+// >= 4 independent 16-byte loads in flight per thread, size the grid to one resident wave, and
+// keep the instruction count per element low enough that issue never limits the stream.
 // Arithmetic mirrors the reference's eager PyTorch op-by-op rounding (each elementwise op
 // materialises a tensor in the storage dtype), which is what keeps hit/miss decisions
-// bit-identical in bf16.
+// bit-identical in bf16; the arithmetic policies in common.cuh do that with packed 16-bit
+// hardware ops.
 #include <cooperative_groups.h>
 
 #include "common.cuh"
@@ -17,10 +19,20 @@ namespace cg = cooperative_groups;
 
 namespace cdb {
 
+// CTAs of `kernel` that are resident at once on the whole device (one wave), from the occupancy
+// calculator, so that a grid-stride launch never leaves a partial second wave behind.
+template <class K>
+static int64_t resident_ctas(K kernel, int threads) {
+  int per_sm = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, 0) != cudaSuccess || per_sm < 1)
+    per_sm = 1;
+  return (int64_t)per_sm * sm_count();
+}
+
 // ------------------------------------------------------------------------------------------
 // relative-L1 reduction
 // ------------------------------------------------------------------------------------------
-constexpr int RL_THREADS = 512;
+constexpr int RL_THREADS = 256;
 constexpr int RL_CLUSTER = 2;        // CTA pair: always fits (SMs come in TPC pairs)
 constexpr int RL_MAX_CLUSTERS = 1024;
 constexpr int RL_UNROLL = 2;
@@ -31,86 +43,57 @@ struct RelL1Scratch {
   double partial[RL_MAX_CLUSTERS][2];
 };
 
-template <typename T, int W>
-struct Chunk {  // W elements: W == VEC -> one 16-byte access, W == 1 -> scalar fallback
-  T v[W];
-};
-
-template <typename T, int W>
-__device__ __forceinline__ Chunk<T, W> load_chunk(const T* p) {
-  Chunk<T, W> c;
-  if constexpr (W == 1) {
-    c.v[0] = *p;
-  } else {
-    Pack<T> k = ld_stream(p);
-#pragma unroll
-    for (int i = 0; i < W; ++i) c.v[i] = k.v[i];
-  }
-  return c;
-}
-template <typename T, int W>
-__device__ __forceinline__ void store_chunk(T* p, const Chunk<T, W>& c) {
-  if constexpr (W == 1) {
-    *p = c.v[0];
-  } else {
-    Pack<T> k;
-#pragma unroll
-    for (int i = 0; i < W; ++i) k.v[i] = c.v[i];
-    st_stream(p, k);
-  }
-}
-
-template <typename T, int W, bool HAS_BASE, bool HAS_PREV, bool WRITE_RES>
-__device__ __forceinline__ void rel_l1_chunk(const T* cur, const T* base, const T* prev, T* res,
+template <class A, int U, bool HAS_BASE, bool HAS_PREV, bool WRITE_RES>
+__device__ __forceinline__ void rel_l1_chunk(const typename A::T* cur, const typename A::T* base,
+                                             const typename A::T* prev, typename A::T* res,
                                              int64_t off, float& sd, float& sp) {
-  Chunk<T, W> c = load_chunk<T, W>(cur + off);
-  Chunk<T, W> b, p, r;
-  if constexpr (HAS_BASE) b = load_chunk<T, W>(base + off);
-  if constexpr (HAS_PREV) p = load_chunk<T, W>(prev + off);
+  Chunk<A, U> r = load_chunk<A, U>(cur + off);
+  Chunk<A, U> b, p;
+  if constexpr (HAS_BASE) b = load_chunk<A, U>(base + off);
+  if constexpr (HAS_PREV) p = load_chunk<A, U>(prev + off);
 #pragma unroll
-  for (int i = 0; i < W; ++i) {
-    float rv = DT<T>::load(c.v[i]);
-    if constexpr (HAS_BASE) rv = DT<T>::round(__fsub_rn(rv, DT<T>::load(b.v[i])));
-    if constexpr (WRITE_RES) r.v[i] = DT<T>::store(rv);
+  for (int i = 0; i < U; ++i) {
+    if constexpr (HAS_BASE) r.u[i] = A::sub(r.u[i], b.u[i]);  // Fn residual, rounded
     if constexpr (HAS_PREV) {
-      float pv = DT<T>::load(p.v[i]);
-      sd += fabsf(DT<T>::round(__fsub_rn(pv, rv)));
-      sp += fabsf(pv);
+      A::accum(sd, A::abs(A::sub(p.u[i], r.u[i])));           // |round(prev - r)|
+      A::accum(sp, A::abs(p.u[i]));                           // |prev|
     }
   }
-  if constexpr (WRITE_RES) store_chunk<T, W>(res + off, r);
+  if constexpr (WRITE_RES) store_chunk<A, U>(res + off, r);
 }
 
-template <typename T, int W, bool HAS_BASE, bool HAS_PREV, bool WRITE_RES>
+// A = vector policy with U units per 16 bytes, A1 = its one-element twin for the ragged tail.
+template <class A, class A1, int U, bool HAS_BASE, bool HAS_PREV, bool WRITE_RES>
 __global__ void __cluster_dims__(RL_CLUSTER, 1, 1) __launch_bounds__(RL_THREADS)
-    rel_l1_kernel(const T* __restrict__ cur, const T* __restrict__ base,
-                  const T* __restrict__ prev, T* __restrict__ res, int64_t n,
+    rel_l1_kernel(const typename A::T* __restrict__ cur, const typename A::T* __restrict__ base,
+                  const typename A::T* __restrict__ prev, typename A::T* __restrict__ res, int64_t n,
                   float* __restrict__ means, RelL1Scratch* __restrict__ scratch) {
+  constexpr int W = U * A::N;  // elements per chunk
   const int64_t nchunk = n / W;
   const int64_t stride = (int64_t)gridDim.x * RL_THREADS;
-  // Four accumulators: two per unrolled lane, so the adds do not serialise behind the loads.
+  // Two accumulators per sum, one per unrolled lane, so the adds do not serialise.
   float sd[RL_UNROLL] = {0.f, 0.f}, sp[RL_UNROLL] = {0.f, 0.f};
   int64_t i = (int64_t)blockIdx.x * RL_THREADS + threadIdx.x;
   for (; i + stride < nchunk; i += RL_UNROLL * stride) {
 #pragma unroll
     for (int u = 0; u < RL_UNROLL; ++u)
-      rel_l1_chunk<T, W, HAS_BASE, HAS_PREV, WRITE_RES>(cur, base, prev, res, (i + u * stride) * W,
+      rel_l1_chunk<A, U, HAS_BASE, HAS_PREV, WRITE_RES>(cur, base, prev, res, (i + u * stride) * W,
                                                         sd[u], sp[u]);
   }
   if (i < nchunk)
-    rel_l1_chunk<T, W, HAS_BASE, HAS_PREV, WRITE_RES>(cur, base, prev, res, i * W, sd[0], sp[0]);
+    rel_l1_chunk<A, U, HAS_BASE, HAS_PREV, WRITE_RES>(cur, base, prev, res, i * W, sd[0], sp[0]);
   if constexpr (W > 1) {  // ragged tail (< W elements), one thread
     if (blockIdx.x == 0 && threadIdx.x == 0)
       for (int64_t t = nchunk * W; t < n; ++t)
-        rel_l1_chunk<T, 1, HAS_BASE, HAS_PREV, WRITE_RES>(cur, base, prev, res, t, sd[1], sp[1]);
+        rel_l1_chunk<A1, 1, HAS_BASE, HAS_PREV, WRITE_RES>(cur, base, prev, res, t, sd[1], sp[1]);
   }
   if constexpr (!HAS_PREV) return;
 
   // thread -> warp (shuffle) -> CTA (shared memory) -> cluster (distributed shared memory)
   float d = warp_sum(sd[0] + sd[1]);
   float p = warp_sum(sp[0] + sp[1]);
-  __shared__ float s_warp[RL_THREADS / 32][2];
-  __shared__ double s_cta[RL_CLUSTER][2];  // slot r is written by cluster rank r (only rank 0's is read)
+  __shared__ float s_warp[RL_THREADS / 32][2];  // RL_THREADS / 32 <= 32 warps
+  __shared__ double s_cta[RL_CLUSTER][2];  // only rank 0's copy is read; slot r is written by rank r
   __shared__ int s_last;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if (lane == 0) {
@@ -164,28 +147,38 @@ __global__ void __cluster_dims__(RL_CLUSTER, 1, 1) __launch_bounds__(RL_THREADS)
     tp += __shfl_xor_sync(0xffffffffu, tp, o);
   }
   if (lane == 0) {
-    means[0] = DT<T>::round((float)(td / (double)n));
-    means[1] = DT<T>::round((float)(tp / (double)n));
+    means[0] = A::round1((float)(td / (double)n));
+    means[1] = A::round1((float)(tp / (double)n));
     scratch->ticket = 0;  // ready for the next launch on this stream
   }
 }
 
-template <typename T, int W>
+template <class A, class A1, int U, bool HB, bool HP, bool WR>
+static int launch_rel_l1_variant(const typename A::T* c, const typename A::T* b, const typename A::T* p,
+                                 typename A::T* r, int64_t n, float* means, RelL1Scratch* scratch,
+                                 cudaStream_t st) {
+  auto kernel = rel_l1_kernel<A, A1, U, HB, HP, WR>;
+  static const int64_t wave = resident_ctas(kernel, RL_THREADS);
+  const int64_t nchunk = n / (U * A::N);
+  int64_t want = (nchunk + (int64_t)RL_THREADS * RL_UNROLL - 1) / ((int64_t)RL_THREADS * RL_UNROLL);
+  int64_t cap = wave < RL_MAX_CLUSTERS * RL_CLUSTER ? wave : RL_MAX_CLUSTERS * RL_CLUSTER;
+  int64_t grid = want < cap ? want : cap;
+  grid = grid / RL_CLUSTER * RL_CLUSTER;
+  if (grid < RL_CLUSTER) grid = RL_CLUSTER;
+  kernel<<<(unsigned)grid, RL_THREADS, 0, st>>>(c, b, p, r, n, means, scratch);
+  CDB_CUDA_CHECK(cudaGetLastError());
+  return CDB_OK;
+}
+
+template <class A, class A1, int U>
 static int launch_rel_l1(const void* cur, const void* base, const void* prev, void* res, int64_t n,
                          float* means, RelL1Scratch* scratch, cudaStream_t st) {
-  const int64_t nchunk = n / W;
-  int64_t want = (nchunk + (int64_t)RL_THREADS * RL_UNROLL - 1) / ((int64_t)RL_THREADS * RL_UNROLL);
-  int64_t cap = (int64_t)sm_count() * (2048 / RL_THREADS);  // one resident wave
-  if (cap > RL_MAX_CLUSTERS * RL_CLUSTER) cap = RL_MAX_CLUSTERS * RL_CLUSTER;
-  int64_t grid = want < cap ? want : cap;
-  grid = (grid + RL_CLUSTER - 1) / RL_CLUSTER * RL_CLUSTER;
-  if (grid < RL_CLUSTER) grid = RL_CLUSTER;
+  using T = typename A::T;
   const T* c = static_cast<const T*>(cur);
   const T* b = static_cast<const T*>(base);
   const T* p = static_cast<const T*>(prev);
   T* r = static_cast<T*>(res);
-#define CDB_RL(HB, HP, WR) \
-  rel_l1_kernel<T, W, HB, HP, WR><<<(unsigned)grid, RL_THREADS, 0, st>>>(c, b, p, r, n, means, scratch)
+#define CDB_RL(HB, HP, WR) return launch_rel_l1_variant<A, A1, U, HB, HP, WR>(c, b, p, r, n, means, scratch, st)
   const bool hb = base != nullptr, hp = prev != nullptr, wr = res != nullptr;
   if (hb && hp && wr) CDB_RL(true, true, true);
   else if (hb && hp && !wr) CDB_RL(true, true, false);
@@ -193,10 +186,8 @@ static int launch_rel_l1(const void* cur, const void* base, const void* prev, vo
   else if (!hb && hp && wr) CDB_RL(false, true, true);
   else if (!hb && hp && !wr) CDB_RL(false, true, false);
   else if (!hb && !hp && wr) CDB_RL(false, false, true);
-  else return CDB_ERR_BAD_ARGUMENT;  // nothing to compute
 #undef CDB_RL
-  CDB_CUDA_CHECK(cudaGetLastError());
-  return CDB_OK;
+  return CDB_ERR_BAD_ARGUMENT;  // nothing to compute
 }
 
 // ------------------------------------------------------------------------------------------
@@ -211,44 +202,47 @@ struct ApplyArgs {
   float power[CDB_MAX_TAYLOR_TERMS];
 };
 
-template <typename T, int W, int TERMS, bool ADD>
-__device__ __forceinline__ void apply_chunk(const T* hidden, const ApplyArgs& a, T* out, int64_t off) {
-  Chunk<T, W> h, o, d[TERMS];
-  if constexpr (ADD) h = load_chunk<T, W>(hidden + off);
+template <class A, int U, int TERMS, bool ADD, bool EXACT>
+__device__ __forceinline__ void apply_chunk(const typename A::T* hidden, const ApplyArgs& a,
+                                            typename A::T* out, int64_t off) {
+  using T = typename A::T;
+  Chunk<A, U> h, o, d[TERMS];
+  if constexpr (ADD) h = load_chunk<A, U>(hidden + off);
 #pragma unroll
-  for (int t = 0; t < TERMS; ++t) d[t] = load_chunk<T, W>(static_cast<const T*>(a.deriv[t]) + off);
+  for (int t = 0; t < TERMS; ++t) d[t] = load_chunk<A, U>(static_cast<const T*>(a.deriv[t]) + off);
 #pragma unroll
-  for (int i = 0; i < W; ++i) {
+  for (int i = 0; i < U; ++i) {
     // output = 0; output += (1/t!) * dY[t] * elapsed**t  -- three rounded ops per term
-    float acc = 0.f;
+    typename A::V acc = A::zero();
 #pragma unroll
     for (int t = 0; t < TERMS; ++t) {
-      float term = DT<T>::round(__fmul_rn(a.coef[t], DT<T>::load(d[t].v[i])));
-      term = DT<T>::round(__fmul_rn(term, a.power[t]));
-      acc = DT<T>::round(__fadd_rn(acc, term));
+      typename A::V term = A::template mulc<EXACT>(d[t].u[i], a.coef[t]);
+      term = A::template mulc<EXACT>(term, a.power[t]);
+      acc = A::add(acc, term);
     }
-    if constexpr (ADD) acc = DT<T>::round(__fadd_rn(acc, DT<T>::load(h.v[i])));
-    o.v[i] = DT<T>::store(acc);
+    if constexpr (ADD) acc = A::add(acc, h.u[i]);
+    o.u[i] = acc;
   }
-  store_chunk<T, W>(out + off, o);
+  store_chunk<A, U>(out + off, o);
 }
 
-template <typename T, int W, int TERMS, bool ADD>
+template <class A, class A1, int U, int TERMS, bool ADD, bool EXACT>
 __global__ void __launch_bounds__(EW_THREADS)
-    taylor_apply_kernel(const T* __restrict__ hidden, const __grid_constant__ ApplyArgs a,
-                        T* __restrict__ out, int64_t n) {
+    taylor_apply_kernel(const typename A::T* __restrict__ hidden, const __grid_constant__ ApplyArgs a,
+                        typename A::T* __restrict__ out, int64_t n) {
+  constexpr int W = U * A::N;
   const int64_t nchunk = n / W;
   const int64_t stride = (int64_t)gridDim.x * EW_THREADS;
   int64_t i = (int64_t)blockIdx.x * EW_THREADS + threadIdx.x;
   for (; i + stride < nchunk; i += EW_UNROLL * stride) {
 #pragma unroll
     for (int u = 0; u < EW_UNROLL; ++u)
-      apply_chunk<T, W, TERMS, ADD>(hidden, a, out, (i + u * stride) * W);
+      apply_chunk<A, U, TERMS, ADD, EXACT>(hidden, a, out, (i + u * stride) * W);
   }
-  if (i < nchunk) apply_chunk<T, W, TERMS, ADD>(hidden, a, out, i * W);
+  if (i < nchunk) apply_chunk<A, U, TERMS, ADD, EXACT>(hidden, a, out, i * W);
   if constexpr (W > 1) {
     if (blockIdx.x == 0 && threadIdx.x == 0)
-      for (int64_t t = nchunk * W; t < n; ++t) apply_chunk<T, 1, TERMS, ADD>(hidden, a, out, t);
+      for (int64_t t = nchunk * W; t < n; ++t) apply_chunk<A1, 1, TERMS, ADD, false>(hidden, a, out, t);
   }
 }
 
@@ -257,71 +251,78 @@ struct UpdateArgs {
   void* cur[CDB_MAX_TAYLOR_TERMS];
 };
 
-template <typename T, int W, int NEW, bool HAS_BEFORE, bool WRITE_Y>
-__device__ __forceinline__ void update_chunk(const T* after, const T* before, const UpdateArgs& a,
-                                             float window, int64_t off) {
-  Chunk<T, W> y = load_chunk<T, W>(after + off);
-  Chunk<T, W> b, p[NEW > 0 ? NEW : 1], o[NEW > 0 ? NEW : 1];
-  if constexpr (HAS_BEFORE) b = load_chunk<T, W>(before + off);
+template <class A, int U, int NEW, bool HAS_BEFORE, bool WRITE_Y, bool POW2>
+__device__ __forceinline__ void update_chunk(const typename A::T* after, const typename A::T* before,
+                                             const UpdateArgs& a, float window, float inv_window,
+                                             int64_t off) {
+  using T = typename A::T;
+  Chunk<A, U> y = load_chunk<A, U>(after + off);
+  Chunk<A, U> b, p[NEW > 0 ? NEW : 1], o[NEW > 0 ? NEW : 1];
+  if constexpr (HAS_BEFORE) b = load_chunk<A, U>(before + off);
 #pragma unroll
-  for (int k = 0; k < NEW; ++k) p[k] = load_chunk<T, W>(static_cast<const T*>(a.prev[k]) + off);
+  for (int k = 0; k < NEW; ++k) p[k] = load_chunk<A, U>(static_cast<const T*>(a.prev[k]) + off);
 #pragma unroll
-  for (int i = 0; i < W; ++i) {
-    float v = DT<T>::load(y.v[i]);
-    if constexpr (HAS_BEFORE) {
-      v = DT<T>::round(__fsub_rn(v, DT<T>::load(b.v[i])));
-      y.v[i] = DT<T>::store(v);
-    }
+  for (int i = 0; i < U; ++i) {
+    if constexpr (HAS_BEFORE) y.u[i] = A::sub(y.u[i], b.u[i]);  // Mn residual, rounded
+    typename A::V v = y.u[i];
 #pragma unroll
     for (int k = 0; k < NEW; ++k) {
       // dY[k+1] = (dY[k] - dY_prev[k]) / window : a rounded subtraction, then a rounded division
-      v = DT<T>::round(__fsub_rn(v, DT<T>::load(p[k].v[i])));
-      v = DT<T>::round(__fdiv_rn(v, window));
-      o[k].v[i] = DT<T>::store(v);
+      v = A::template divc<POW2>(A::sub(v, p[k].u[i]), window, inv_window);
+      o[k].u[i] = v;
     }
   }
-  if constexpr (WRITE_Y) store_chunk<T, W>(static_cast<T*>(a.cur[0]) + off, y);
+  if constexpr (WRITE_Y) store_chunk<A, U>(static_cast<T*>(a.cur[0]) + off, y);
 #pragma unroll
-  for (int k = 0; k < NEW; ++k) store_chunk<T, W>(static_cast<T*>(a.cur[k + 1]) + off, o[k]);
+  for (int k = 0; k < NEW; ++k) store_chunk<A, U>(static_cast<T*>(a.cur[k + 1]) + off, o[k]);
 }
 
-template <typename T, int W, int NEW, bool HAS_BEFORE, bool WRITE_Y>
+template <class A, class A1, int U, int NEW, bool HAS_BEFORE, bool WRITE_Y, bool POW2>
 __global__ void __launch_bounds__(EW_THREADS)
-    taylor_update_kernel(const T* __restrict__ after, const T* __restrict__ before,
-                         const __grid_constant__ UpdateArgs a, float window, int64_t n) {
+    taylor_update_kernel(const typename A::T* __restrict__ after, const typename A::T* __restrict__ before,
+                         const __grid_constant__ UpdateArgs a, float window, float inv_window, int64_t n) {
+  constexpr int W = U * A::N;
   const int64_t nchunk = n / W;
   const int64_t stride = (int64_t)gridDim.x * EW_THREADS;
   int64_t i = (int64_t)blockIdx.x * EW_THREADS + threadIdx.x;
   for (; i + stride < nchunk; i += EW_UNROLL * stride) {
 #pragma unroll
     for (int u = 0; u < EW_UNROLL; ++u)
-      update_chunk<T, W, NEW, HAS_BEFORE, WRITE_Y>(after, before, a, window, (i + u * stride) * W);
+      update_chunk<A, U, NEW, HAS_BEFORE, WRITE_Y, POW2>(after, before, a, window, inv_window,
+                                                         (i + u * stride) * W);
   }
-  if (i < nchunk) update_chunk<T, W, NEW, HAS_BEFORE, WRITE_Y>(after, before, a, window, i * W);
+  if (i < nchunk)
+    update_chunk<A, U, NEW, HAS_BEFORE, WRITE_Y, POW2>(after, before, a, window, inv_window, i * W);
   if constexpr (W > 1) {
     if (blockIdx.x == 0 && threadIdx.x == 0)
       for (int64_t t = nchunk * W; t < n; ++t)
-        update_chunk<T, 1, NEW, HAS_BEFORE, WRITE_Y>(after, before, a, window, t);
+        update_chunk<A1, 1, NEW, HAS_BEFORE, WRITE_Y, false>(after, before, a, window, inv_window, t);
   }
 }
 
-static unsigned ew_grid(int64_t nchunk) {
+template <class A, class A1, int U, int TERMS, bool ADD, bool EX>
+static void launch_apply_variant(const typename A::T* h, const ApplyArgs& a, typename A::T* o, int64_t n,
+                                 cudaStream_t st) {
+  auto kernel = taylor_apply_kernel<A, A1, U, TERMS, ADD, EX>;
+  static const int64_t wave = resident_ctas(kernel, EW_THREADS);
+  const int64_t nchunk = n / (U * A::N);
   int64_t want = (nchunk + (int64_t)EW_THREADS * EW_UNROLL - 1) / ((int64_t)EW_THREADS * EW_UNROLL);
-  int64_t cap = (int64_t)sm_count() * (2048 / EW_THREADS);
-  int64_t g = want < cap ? want : cap;
-  return (unsigned)(g < 1 ? 1 : g);
+  int64_t g = want < wave ? want : wave;
+  kernel<<<(unsigned)(g < 1 ? 1 : g), EW_THREADS, 0, st>>>(h, a, o, n);
 }
 
-template <typename T, int W>
-static int launch_apply(const void* hidden, const ApplyArgs& a, int n_terms, bool add, void* out,
-                        int64_t n, cudaStream_t st) {
-  const unsigned grid = ew_grid(n / W);
+template <class A, class A1, int U>
+static int launch_apply(const void* hidden, const ApplyArgs& a, int n_terms, bool add, bool exact,
+                        void* out, int64_t n, cudaStream_t st) {
+  using T = typename A::T;
   const T* h = static_cast<const T*>(hidden);
   T* o = static_cast<T*>(out);
-#define CDB_AP(TERMS)                                                                        \
-  case TERMS:                                                                                \
-    if (add) taylor_apply_kernel<T, W, TERMS, true><<<grid, EW_THREADS, 0, st>>>(h, a, o, n); \
-    else taylor_apply_kernel<T, W, TERMS, false><<<grid, EW_THREADS, 0, st>>>(h, a, o, n);    \
+#define CDB_AP(TERMS)                                                                   \
+  case TERMS:                                                                           \
+    if (add && exact) launch_apply_variant<A, A1, U, TERMS, true, true>(h, a, o, n, st);  \
+    else if (add) launch_apply_variant<A, A1, U, TERMS, true, false>(h, a, o, n, st);     \
+    else if (exact) launch_apply_variant<A, A1, U, TERMS, false, true>(h, a, o, n, st);   \
+    else launch_apply_variant<A, A1, U, TERMS, false, false>(h, a, o, n, st);             \
     break;
   switch (n_terms) {
     CDB_AP(1) CDB_AP(2) CDB_AP(3) CDB_AP(4) CDB_AP(5)
@@ -332,26 +333,54 @@ static int launch_apply(const void* hidden, const ApplyArgs& a, int n_terms, boo
   return CDB_OK;
 }
 
-template <typename T, int W>
+template <class A, class A1, int U, int NEW, bool HB, bool WY, bool P2>
+static void launch_update_variant(const typename A::T* af, const typename A::T* bf, const UpdateArgs& a,
+                                  float window, int64_t n, cudaStream_t st) {
+  auto kernel = taylor_update_kernel<A, A1, U, NEW, HB, WY, P2>;
+  static const int64_t wave = resident_ctas(kernel, EW_THREADS);
+  const int64_t nchunk = n / (U * A::N);
+  int64_t want = (nchunk + (int64_t)EW_THREADS * EW_UNROLL - 1) / ((int64_t)EW_THREADS * EW_UNROLL);
+  int64_t g = want < wave ? want : wave;
+  kernel<<<(unsigned)(g < 1 ? 1 : g), EW_THREADS, 0, st>>>(af, bf, a, window, 1.0f / window, n);
+}
+
+template <class A, class A1, int U>
 static int launch_update(const void* after, const void* before, const UpdateArgs& a, int n_new,
-                         bool write_y, float window, int64_t n, cudaStream_t st) {
-  const unsigned grid = ew_grid(n / W);
+                         bool write_y, float window, bool pow2, int64_t n, cudaStream_t st) {
+  using T = typename A::T;
   const T* af = static_cast<const T*>(after);
   const T* bf = static_cast<const T*>(before);
   const bool hb = before != nullptr;
-#define CDB_UP(NEW)                                                                                  \
-  case NEW:                                                                                          \
-    if (hb) taylor_update_kernel<T, W, NEW, true, true><<<grid, EW_THREADS, 0, st>>>(af, bf, a, window, n); \
-    else if (write_y) taylor_update_kernel<T, W, NEW, false, true><<<grid, EW_THREADS, 0, st>>>(af, bf, a, window, n); \
-    else taylor_update_kernel<T, W, NEW, false, false><<<grid, EW_THREADS, 0, st>>>(af, bf, a, window, n); \
+#define CDB_UP2(NEW, HB, WY, P2) launch_update_variant<A, A1, U, NEW, HB, WY, P2>(af, bf, a, window, n, st)
+#define CDB_UP(NEW)                                        \
+  case NEW:                                                \
+    if (hb && pow2) CDB_UP2(NEW, true, true, true);        \
+    else if (hb) CDB_UP2(NEW, true, true, false);          \
+    else if (write_y && pow2) CDB_UP2(NEW, false, true, true);   \
+    else if (write_y) CDB_UP2(NEW, false, true, false);    \
+    else if (pow2) CDB_UP2(NEW, false, false, true);       \
+    else CDB_UP2(NEW, false, false, false);                \
     break;
   switch (n_new) {
     CDB_UP(0) CDB_UP(1) CDB_UP(2) CDB_UP(3) CDB_UP(4)
     default: return CDB_ERR_BAD_ARGUMENT;
   }
 #undef CDB_UP
+#undef CDB_UP2
   CDB_CUDA_CHECK(cudaGetLastError());
   return CDB_OK;
+}
+
+// True when `c` survives a round trip through the storage type, i.e. the packed 16-bit multiply
+// by the constant performs exactly the one rounding the float path would.
+static bool representable(float c, int dtype) {
+  if (dtype == CDB_F32) return true;
+  if (dtype == CDB_BF16) return __bfloat162float(__float2bfloat16_rn(c)) == c;
+  return __half2float(__float2half_rn(c)) == c && fabsf(c) <= 2048.f;
+}
+static bool is_pow2(float w) {
+  int e = 0;
+  return w > 0.f && frexpf(w, &e) == 0.5f && e >= -20 && e <= 20;
 }
 
 }  // namespace cdb
@@ -360,6 +389,18 @@ static int launch_update(const void* after, const void* before, const UpdateArgs
 // C ABI
 // ------------------------------------------------------------------------------------------
 using namespace cdb;
+
+#define CDB_DISPATCH(FN, vec, ...)                                                                  \
+  switch (dtype) {                                                                                  \
+    case CDB_F32:                                                                                   \
+      return vec ? FN<F32x1, F32x1, 4>(__VA_ARGS__) : FN<F32x1, F32x1, 1>(__VA_ARGS__);              \
+    case CDB_BF16:                                                                                  \
+      return vec ? FN<BF16x2, BF16x1, 4>(__VA_ARGS__) : FN<BF16x1, BF16x1, 1>(__VA_ARGS__);          \
+    case CDB_F16:                                                                                   \
+      return vec ? FN<F16x2, F16x1, 4>(__VA_ARGS__) : FN<F16x1, F16x1, 1>(__VA_ARGS__);              \
+    default:                                                                                        \
+      return CDB_ERR_BAD_ARGUMENT;                                                                  \
+  }
 
 extern "C" size_t cdb_rel_l1_scratch_bytes(void) { return sizeof(RelL1Scratch); }
 
@@ -375,19 +416,7 @@ extern "C" int cdb_rel_l1(const void* cur, const void* base, const void* prev, v
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   RelL1Scratch* sc = static_cast<RelL1Scratch*>(scratch);
   const bool vec = aligned16(cur) && aligned16(base) && aligned16(prev) && aligned16(residual_out);
-  switch (dtype) {
-    case CDB_F32:
-      return vec ? launch_rel_l1<float, 4>(cur, base, prev, residual_out, n, means, sc, st)
-                 : launch_rel_l1<float, 1>(cur, base, prev, residual_out, n, means, sc, st);
-    case CDB_BF16:
-      return vec ? launch_rel_l1<__nv_bfloat16, 8>(cur, base, prev, residual_out, n, means, sc, st)
-                 : launch_rel_l1<__nv_bfloat16, 1>(cur, base, prev, residual_out, n, means, sc, st);
-    case CDB_F16:
-      return vec ? launch_rel_l1<__half, 8>(cur, base, prev, residual_out, n, means, sc, st)
-                 : launch_rel_l1<__half, 1>(cur, base, prev, residual_out, n, means, sc, st);
-    default:
-      return CDB_ERR_BAD_ARGUMENT;
-  }
+  CDB_DISPATCH(launch_rel_l1, vec, cur, base, prev, residual_out, n, means, sc, st)
 }
 
 extern "C" int cdb_taylor_apply(const void* hidden, const void* const* derivs, const float* coef,
@@ -398,28 +427,18 @@ extern "C" int cdb_taylor_apply(const void* hidden, const void* const* derivs, c
   if (add_hidden && !hidden) return CDB_ERR_BAD_ARGUMENT;
   ApplyArgs a{};
   bool vec = aligned16(out) && (!add_hidden || aligned16(hidden));
+  bool exact = true;
   for (int t = 0; t < n_terms; ++t) {
     if (!derivs[t]) return CDB_ERR_BAD_ARGUMENT;
     a.deriv[t] = derivs[t];
     a.coef[t] = coef[t];
     a.power[t] = power[t];
     vec = vec && aligned16(derivs[t]);
+    exact = exact && representable(coef[t], dtype) && representable(power[t], dtype);
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const bool add = add_hidden != 0;
-  switch (dtype) {
-    case CDB_F32:
-      return vec ? launch_apply<float, 4>(hidden, a, n_terms, add, out, n, st)
-                 : launch_apply<float, 1>(hidden, a, n_terms, add, out, n, st);
-    case CDB_BF16:
-      return vec ? launch_apply<__nv_bfloat16, 8>(hidden, a, n_terms, add, out, n, st)
-                 : launch_apply<__nv_bfloat16, 1>(hidden, a, n_terms, add, out, n, st);
-    case CDB_F16:
-      return vec ? launch_apply<__half, 8>(hidden, a, n_terms, add, out, n, st)
-                 : launch_apply<__half, 1>(hidden, a, n_terms, add, out, n, st);
-    default:
-      return CDB_ERR_BAD_ARGUMENT;
-  }
+  CDB_DISPATCH(launch_apply, vec, hidden, a, n_terms, add, exact, out, n, st)
 }
 
 extern "C" int cdb_taylor_update(const void* after, const void* before, const void* const* prev,
@@ -441,18 +460,8 @@ extern "C" int cdb_taylor_update(const void* after, const void* before, const vo
   }
   const bool write_y = before != nullptr || cur[0] != after;
   if (!write_y && n_new == 0) return CDB_OK;
+  if (n_new == 0) window = 1.f;
+  const bool pow2 = is_pow2(window);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  switch (dtype) {
-    case CDB_F32:
-      return vec ? launch_update<float, 4>(after, before, a, n_new, write_y, window, n, st)
-                 : launch_update<float, 1>(after, before, a, n_new, write_y, window, n, st);
-    case CDB_BF16:
-      return vec ? launch_update<__nv_bfloat16, 8>(after, before, a, n_new, write_y, window, n, st)
-                 : launch_update<__nv_bfloat16, 1>(after, before, a, n_new, write_y, window, n, st);
-    case CDB_F16:
-      return vec ? launch_update<__half, 8>(after, before, a, n_new, write_y, window, n, st)
-                 : launch_update<__half, 1>(after, before, a, n_new, write_y, window, n, st);
-    default:
-      return CDB_ERR_BAD_ARGUMENT;
-  }
+  CDB_DISPATCH(launch_update, vec, after, before, a, n_new, write_y, window, pow2, n, st)
 }

@@ -27,54 +27,181 @@ int sm_count();
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-// ---- storage-dtype traits -------------------------------------------------------------
-// `round` returns the float nearest-even-rounded to the storage type, as a float: every
-// elementwise torch op in the reference materialises its result in the tensor dtype.
-template <typename T>
-struct DT;
-
-template <>
-struct DT<float> {
-  static constexpr int VEC = 4;  // elements per 16 bytes
-  __device__ static __forceinline__ float load(float v) { return v; }
-  __device__ static __forceinline__ float store(float v) { return v; }
-  __device__ static __forceinline__ float round(float v) { return v; }
-};
-template <>
-struct DT<__nv_bfloat16> {
-  static constexpr int VEC = 8;
-  __device__ static __forceinline__ float load(__nv_bfloat16 v) { return __bfloat162float(v); }
-  __device__ static __forceinline__ __nv_bfloat16 store(float v) { return __float2bfloat16_rn(v); }
-  __device__ static __forceinline__ float round(float v) {
-    return __bfloat162float(__float2bfloat16_rn(v));
+// ---- storage-dtype arithmetic policies ------------------------------------------------------
+// Every elementwise torch op in the reference materialises its result in the tensor dtype, so
+// a chain  c = a - b; d = |c|  is "round after every op".  For 16-bit storage the hardware's
+// packed HSUB2/HADD2/HMUL2 (bf16x2 / f16x2) round exactly once to the storage type, which is that
+// very semantics (the *_rn forms also forbid contraction into a fused multiply-add) at two
+// elements per instruction and without float<->16-bit conversion
+// instructions (those issue at a fraction of the FP32 rate and were the limiter of a first
+// version that rounded through float).
+//
+// A policy describes one 32-bit-or-smaller "unit": V = storage of the unit, N = elements in it.
+//   sub/add/mul : one rounded op per element        abs      : exact
+//   accum       : add every |element| to an fp32 accumulator
+//   mulc        : round(c * v) for a float constant c (exact fast path when c is representable)
+//   divc        : round(v / w) for a float constant w
+struct F32x1 {
+  using T = float;
+  using V = float;
+  static constexpr int N = 1;
+  __device__ static __forceinline__ V sub(V a, V b) { return __fsub_rn(a, b); }
+  __device__ static __forceinline__ V add(V a, V b) { return __fadd_rn(a, b); }
+  __device__ static __forceinline__ V abs(V a) { return fabsf(a); }
+  __device__ static __forceinline__ void accum(float& acc, V a) { acc += a; }
+  template <bool EXACT>
+  __device__ static __forceinline__ V mulc(V a, float c) { return __fmul_rn(c, a); }
+  template <bool POW2>
+  __device__ static __forceinline__ V divc(V a, float w, float inv_w) {
+    return POW2 ? __fmul_rn(a, inv_w) : __fdiv_rn(a, w);
   }
-};
-template <>
-struct DT<__half> {
-  static constexpr int VEC = 8;
-  __device__ static __forceinline__ float load(__half v) { return __half2float(v); }
-  __device__ static __forceinline__ __half store(float v) { return __float2half_rn(v); }
-  __device__ static __forceinline__ float round(float v) { return __half2float(__float2half_rn(v)); }
+  __device__ static __forceinline__ V zero() { return 0.f; }
+  __device__ static __forceinline__ float round1(float v) { return v; }
 };
 
-// 16-byte packet of T.
+struct BF16x2 {
+  using T = __nv_bfloat16;
+  using V = __nv_bfloat162;
+  static constexpr int N = 2;
+  __device__ static __forceinline__ V sub(V a, V b) { return __hsub2_rn(a, b); }
+  __device__ static __forceinline__ V add(V a, V b) { return __hadd2_rn(a, b); }
+  __device__ static __forceinline__ V abs(V a) { return __habs2(a); }
+  __device__ static __forceinline__ void accum(float& acc, V a) {
+    const uint32_t u = *reinterpret_cast<uint32_t*>(&a);  // bf16 -> fp32 is a 16-bit shift
+    acc += __uint_as_float(u << 16);
+    acc += __uint_as_float(u & 0xffff0000u);
+  }
+  template <bool EXACT>
+  __device__ static __forceinline__ V mulc(V a, float c) {
+    if constexpr (EXACT) {
+      return __hmul2_rn(a, __float2bfloat162_rn(c));
+    } else {
+      float2 f = __bfloat1622float2(a);
+      return __floats2bfloat162_rn(__fmul_rn(c, f.x), __fmul_rn(c, f.y));
+    }
+  }
+  template <bool POW2>
+  __device__ static __forceinline__ V divc(V a, float w, float inv_w) {
+    if constexpr (POW2) {
+      return __hmul2_rn(a, __float2bfloat162_rn(inv_w));
+    } else {
+      float2 f = __bfloat1622float2(a);
+      return __floats2bfloat162_rn(__fdiv_rn(f.x, w), __fdiv_rn(f.y, w));
+    }
+  }
+  __device__ static __forceinline__ V zero() { return __float2bfloat162_rn(0.f); }
+  __device__ static __forceinline__ float round1(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+};
+
+struct BF16x1 {
+  using T = __nv_bfloat16;
+  using V = __nv_bfloat16;
+  static constexpr int N = 1;
+  __device__ static __forceinline__ V sub(V a, V b) { return __hsub_rn(a, b); }
+  __device__ static __forceinline__ V add(V a, V b) { return __hadd_rn(a, b); }
+  __device__ static __forceinline__ V abs(V a) { return __habs(a); }
+  __device__ static __forceinline__ void accum(float& acc, V a) { acc += __bfloat162float(a); }
+  template <bool EXACT>
+  __device__ static __forceinline__ V mulc(V a, float c) {
+    return __float2bfloat16_rn(__fmul_rn(c, __bfloat162float(a)));
+  }
+  template <bool POW2>
+  __device__ static __forceinline__ V divc(V a, float w, float) {
+    return __float2bfloat16_rn(__fdiv_rn(__bfloat162float(a), w));
+  }
+  __device__ static __forceinline__ V zero() { return __float2bfloat16_rn(0.f); }
+  __device__ static __forceinline__ float round1(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+};
+
+struct F16x2 {
+  using T = __half;
+  using V = __half2;
+  static constexpr int N = 2;
+  __device__ static __forceinline__ V sub(V a, V b) { return __hsub2_rn(a, b); }
+  __device__ static __forceinline__ V add(V a, V b) { return __hadd2_rn(a, b); }
+  __device__ static __forceinline__ V abs(V a) { return __habs2(a); }
+  __device__ static __forceinline__ void accum(float& acc, V a) {
+    float2 f = __half22float2(a);
+    acc += f.x;
+    acc += f.y;
+  }
+  template <bool EXACT>
+  __device__ static __forceinline__ V mulc(V a, float c) {
+    if constexpr (EXACT) {
+      return __hmul2_rn(a, __float2half2_rn(c));
+    } else {
+      float2 f = __half22float2(a);
+      return __floats2half2_rn(__fmul_rn(c, f.x), __fmul_rn(c, f.y));
+    }
+  }
+  template <bool POW2>
+  __device__ static __forceinline__ V divc(V a, float w, float inv_w) {
+    // fp16 has a narrow exponent range: a power-of-two scale can still round (subnormals), so
+    // always divide in float and round once
+    float2 f = __half22float2(a);
+    return __floats2half2_rn(__fdiv_rn(f.x, w), __fdiv_rn(f.y, w));
+  }
+  __device__ static __forceinline__ V zero() { return __float2half2_rn(0.f); }
+  __device__ static __forceinline__ float round1(float v) { return __half2float(__float2half_rn(v)); }
+};
+
+struct F16x1 {
+  using T = __half;
+  using V = __half;
+  static constexpr int N = 1;
+  __device__ static __forceinline__ V sub(V a, V b) { return __hsub_rn(a, b); }
+  __device__ static __forceinline__ V add(V a, V b) { return __hadd_rn(a, b); }
+  __device__ static __forceinline__ V abs(V a) { return __habs(a); }
+  __device__ static __forceinline__ void accum(float& acc, V a) { acc += __half2float(a); }
+  template <bool EXACT>
+  __device__ static __forceinline__ V mulc(V a, float c) {
+    return __float2half_rn(__fmul_rn(c, __half2float(a)));
+  }
+  template <bool POW2>
+  __device__ static __forceinline__ V divc(V a, float w, float) {
+    return __float2half_rn(__fdiv_rn(__half2float(a), w));
+  }
+  __device__ static __forceinline__ V zero() { return __float2half_rn(0.f); }
+  __device__ static __forceinline__ float round1(float v) { return __half2float(__float2half_rn(v)); }
+};
+
+// 16-byte packet of bf16 for the quantization kernels.
 template <typename T>
 struct alignas(16) Pack {
-  T v[DT<T>::VEC];
+  T v[16 / sizeof(T)];
 };
-
-// Streaming (read-once / write-once) 128-bit accesses: keep them out of L1 and mark them
-// evict-first so the step's tensors do not push the weights out of L2.
 template <typename T>
 __device__ __forceinline__ Pack<T> ld_stream(const T* p) {
   Pack<T> r;
-  uint4 u = __ldcs(reinterpret_cast<const uint4*>(p));
-  *reinterpret_cast<uint4*>(&r) = u;
+  *reinterpret_cast<uint4*>(&r) = __ldcs(reinterpret_cast<const uint4*>(p));
   return r;
 }
-template <typename T>
-__device__ __forceinline__ void st_stream(T* p, const Pack<T>& v) {
-  __stcs(reinterpret_cast<uint4*>(p), *reinterpret_cast<const uint4*>(&v));
+
+// A chunk is U units of policy A handled by one thread at once: U = 16 / sizeof(V) gives one
+// streaming 128-bit access (kept out of L1, evict-first in L2), U = 1 with a one-element policy
+// is the fallback for pointers that are not 16-byte aligned and for ragged tails.
+template <class A, int U>
+struct Chunk {
+  typename A::V u[U];
+};
+template <class A, int U>
+__device__ __forceinline__ Chunk<A, U> load_chunk(const typename A::T* p) {
+  Chunk<A, U> c;
+  if constexpr (U * sizeof(typename A::V) == 16) {
+    *reinterpret_cast<uint4*>(&c) = __ldcs(reinterpret_cast<const uint4*>(p));
+  } else {
+    static_assert(U == 1 && A::N == 1, "scalar fallback handles one element");
+    c.u[0] = *p;
+  }
+  return c;
+}
+template <class A, int U>
+__device__ __forceinline__ void store_chunk(typename A::T* p, const Chunk<A, U>& c) {
+  if constexpr (U * sizeof(typename A::V) == 16) {
+    __stcs(reinterpret_cast<uint4*>(p), *reinterpret_cast<const uint4*>(&c));
+  } else {
+    *p = c.u[0];
+  }
 }
 
 __device__ __forceinline__ float warp_sum(float v) {

@@ -121,6 +121,17 @@ __global__ void __launch_bounds__(Q_MAX_THREADS)
     if (sc == 0.f) sc = 1.f;  // all-zero row: keep zeros exact instead of 0/0
     if (threadIdx.x == 0) scale[row] = sc;
 
+    // x / sc with one reciprocal per row: t = x * (1/sc) followed by one Newton correction
+    // (r = x - t*sc exactly by FMA; t += r * (1/sc)) reproduces the correctly rounded quotient;
+    // rows whose scale is so small that 1/sc would overflow take the plain division.
+    const bool tiny = sc < 1e-30f;
+    const float inv = tiny ? 0.f : __frcp_rn(sc);
+    auto quot = [&](float x) -> float {
+      if (tiny) return __fdiv_rn(x, sc);
+      float t = x * inv;
+      float r = fmaf(-t, sc, x);
+      return fmaf(r, inv, t);
+    };
     uint8_t* qr = q + row * (int64_t)cols;
 #pragma unroll
     for (int k = 0; k < VPT; ++k) {
@@ -129,8 +140,8 @@ __global__ void __launch_bounds__(Q_MAX_THREADS)
       uint32_t w[2];
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
-        float2 lo = make_float2(__fdiv_rn(v[k][h * 4 + 0], sc), __fdiv_rn(v[k][h * 4 + 1], sc));
-        float2 hi = make_float2(__fdiv_rn(v[k][h * 4 + 2], sc), __fdiv_rn(v[k][h * 4 + 3], sc));
+        float2 lo = make_float2(quot(v[k][h * 4 + 0]), quot(v[k][h * 4 + 1]));
+        float2 hi = make_float2(quot(v[k][h * 4 + 2]), quot(v[k][h * 4 + 3]));
         uint32_t a = __nv_cvt_float2_to_fp8x2(lo, __NV_SATFINITE, __NV_E4M3);
         uint32_t b = __nv_cvt_float2_to_fp8x2(hi, __NV_SATFINITE, __NV_E4M3);
         w[h] = a | (b << 16);
