@@ -1,0 +1,23 @@
+"""B200-native (sm_100a) hot path behind cache-dit's public API.
+
+    import cache_dit_b200 as cache_dit
+    cache_dit.enable_cache(pipe_or_adapter_or_transformer,
+                           cache_config=cache_dit.DBCacheConfig(...),
+                           calibrator_config=cache_dit.TaylorSeerCalibratorConfig(...),
+                           parallelism_config=cache_dit.ParallelismConfig(ulysses_size=8),
+                           quantize_config=cache_dit.QuantizeConfig(quant_type="float8_per_row"))
+
+The names exported here are those of the reference package (src/cache_dit/__init__.py:19-82) that
+belong to the DBCache / TaylorSeer / FP8-linear / Ulysses path.
+"""
+from .caching import (BasicCacheConfig, BlockAdapter, BlockAdapterRegister, CachedAdapter, CachedBlocks,
+                      CachedContext, CachedContextManager, CacheType, Calibrator, CalibratorBase,
+                      CalibratorConfig, ContextNotExistError, DBCacheConfig, ExtraCacheConfig,
+                      FakeDiffusionPipeline, ForwardPattern, LazyResidual, ParamsModifier, TaylorSeerCalibrator,
+                      TaylorSeerCalibratorConfig, UnifiedBlocks, block_range, cache_type, disable_cache,
+                      enable_cache, get_adapter, refresh_context, steps_mask, supported_pipelines)
+from .distributed import ParallelismConfig, enable_parallelism
+from .quantization import Float8RowwiseLinear, QuantizeConfig, quantize
+from .summary import CacheStats, strify, summary
+
+__version__ = "0.1.0"

@@ -1,0 +1,4 @@
+from .config import QuantizeBackend, QuantizeConfig
+from .linear import Float8RowwiseLinear, quantize_rows_fused
+from .quantize import quantize, remove_quantization_stats
+from . import ops

@@ -1,0 +1,90 @@
+"""`Float8RowwiseLinear`: an nn.Linear replacement backed by the sm_100a FP8 kernels.
+
+Semantics follow the float8 per-row dynamic inference path the reference selects
+(src/cache_dit/quantization/torchao/quantize_ao.py:540-558, 43-71 and .../_scaled_mm.py:62-91):
+weights are quantized once to e4m3 with one scale per output row, activations are quantized per
+token at every call, the product is scaled by both and returned in bf16.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import _native
+
+
+class Float8RowwiseLinear(torch.nn.Module):
+  """y = fp8_gemm(quant_rows(x), W_q) * a_scale * w_scale (+ bias); bf16 in, bf16 out."""
+
+  def __init__(self, in_features: int, out_features: int, weight_q: torch.Tensor, weight_scale: torch.Tensor,
+               bias: Optional[torch.Tensor]):
+    super().__init__()
+    self.in_features = in_features
+    self.out_features = out_features
+    self.register_buffer("weight_q", weight_q)          # [N, K] float8_e4m3fn
+    self.register_buffer("weight_scale", weight_scale)  # [N] float32
+    self.register_buffer("bias", bias)                  # [N] bf16 or None
+
+  @classmethod
+  def from_linear(cls, linear: torch.nn.Linear) -> "Float8RowwiseLinear":
+    w = linear.weight.detach()
+    if not w.is_cuda:
+      raise RuntimeError("float8_per_row quantization runs on the GPU: move the module to CUDA first")
+    if w.dtype != torch.bfloat16:
+      raise RuntimeError(f"float8_per_row needs bf16 weights, got {w.dtype}")
+    n, k = w.shape
+    if k % 16 != 0 or n % 8 != 0:
+      raise RuntimeError(f"float8_per_row needs in_features % 16 == 0 and out_features % 8 == 0, got {k}, {n}")
+    w_q = torch.empty((n, k), dtype=torch.float8_e4m3fn, device=w.device)
+    w_scale = torch.empty(n, dtype=torch.float32, device=w.device)
+    _native.fp8_quant_rows(w.contiguous(), w_q, w_scale)
+    bias = None if linear.bias is None else linear.bias.detach().to(torch.bfloat16).contiguous()
+    return cls(k, n, w_q, w_scale, bias)
+
+  @staticmethod
+  def supports(linear: torch.nn.Linear) -> bool:
+    n, k = linear.weight.shape
+    return linear.weight.dtype == torch.bfloat16 and k % 16 == 0 and n % 8 == 0 and k <= 16384
+
+  def quantize_input(self, x: torch.Tensor):
+    x2 = x.reshape(-1, self.in_features)
+    if x2.stride(-1) != 1:
+      x2 = x2.contiguous()
+    a_q = torch.empty(x2.shape, dtype=torch.float8_e4m3fn, device=x.device)
+    a_scale = torch.empty(x2.shape[0], dtype=torch.float32, device=x.device)
+    _native.fp8_quant_rows(x2, a_q, a_scale)
+    return a_q, a_scale
+
+  def forward_quantized(self, a_q: torch.Tensor, a_scale: torch.Tensor, lead_shape) -> torch.Tensor:
+    """Product for activations that a fused producer kernel already quantized."""
+    out = torch.empty((a_q.shape[0], self.out_features), dtype=torch.bfloat16, device=a_q.device)
+    _native.fp8_gemm_rowscaled(a_q, a_scale, self.weight_q, self.weight_scale, self.bias, out)
+    return out.view(*lead_shape, self.out_features)
+
+  def forward(self, x: torch.Tensor) -> torch.Tensor:
+    if x.dtype != torch.bfloat16:
+      x = x.to(torch.bfloat16)
+    a_q, a_scale = self.quantize_input(x)
+    return self.forward_quantized(a_q, a_scale, x.shape[:-1])
+
+  def extra_repr(self) -> str:
+    return f"in_features={self.in_features}, out_features={self.out_features}, bias={self.bias is not None}, fp8=e4m3 per-row"
+
+
+def quantize_rows_fused(x: torch.Tensor, preop: int, mod_shift=None, mod_scale=None, eps: float = 1e-6):
+  """Quantize `op(x)` without materialising it: op = adaLN-modulated LayerNorm or tanh-GELU.
+
+  x [B, S, C] or [rows, C] bf16; for the LayerNorm variant mod_shift / mod_scale are [B, C]."""
+  lead = x.shape[:-1]
+  x2 = x.reshape(-1, x.shape[-1])
+  if x2.stride(-1) != 1:
+    x2 = x2.contiguous()
+  a_q = torch.empty(x2.shape, dtype=torch.float8_e4m3fn, device=x.device)
+  a_scale = torch.empty(x2.shape[0], dtype=torch.float32, device=x.device)
+  rows_per_batch = 0
+  if preop == _native.PRE_LAYERNORM_MOD:
+    batch = mod_shift.shape[0]
+    rows_per_batch = x2.shape[0] // batch
+  _native.fp8_quant_rows(x2, a_q, a_scale, preop, mod_shift, mod_scale, rows_per_batch, eps)
+  return a_q, a_scale, lead

@@ -73,3 +73,63 @@ class OracleBackend:
   @staticmethod
   def to_numpy(a):
     return np.asarray(a, dtype=np.float32)
+
+
+class ProductBackend:
+  """tests/scenarios.py backend over cache_dit_b200's own CachedContextManager (any device)."""
+
+  def __init__(self, sc: dict, device="cpu", parallelized: bool = False):
+    import cache_dit_b200 as cd
+    cc = dict(sc["cache_config"])
+    cc.setdefault("enable_separate_cfg", False)
+    cal = sc["calibrator_config"]
+    self.device = device
+    self.parallelized = parallelized
+    self.mgr = cd.CachedContextManager("scenario", persistent_context=True)
+    self.mgr.new_context(name="ctx", cache_config=cd.DBCacheConfig(**cc),
+                         calibrator_config=None if cal is None else cd.TaylorSeerCalibratorConfig(**cal))
+
+  def _p(self, encoder=False):
+    res = self.mgr.is_encoder_cache_residual() if encoder else self.mgr.is_cache_residual()
+    return f"{PREFIX}_Bn_{'residual' if res else 'hidden_states'}"
+
+  def begin_call(self):
+    self.mgr.set_context("ctx")
+
+  def mark_step_begin(self):
+    self.mgr.mark_step_begin()
+
+  def current_step(self):
+    return self.mgr.get_current_step()
+
+  def can_cache(self, r):
+    return self.mgr.can_cache(r, parallelized=self.parallelized, prefix=f"{PREFIX}_Fn_residual")
+
+  def add_cached_step(self):
+    self.mgr.add_cached_step()
+
+  def apply_cache(self, h, e):
+    return self.mgr.apply_cache(h, e, prefix=self._p(), encoder_prefix=self._p(True))
+
+  def set_Fn_buffer(self, r):
+    self.mgr.set_Fn_buffer(r, prefix=f"{PREFIX}_Fn_residual")
+
+  def set_Bn_buffer(self, R):
+    self.mgr.set_Bn_buffer(R, prefix=self._p())
+
+  def set_Bn_encoder_buffer(self, Re):
+    self.mgr.set_Bn_encoder_buffer(Re, prefix=self._p(True))
+
+  def stats(self):
+    m = self.mgr
+    return stats_dict(m.get_cached_steps(), m.get_residual_diffs(), m.get_cfg_cached_steps(),
+                      m.get_cfg_residual_diffs(), m.get_accumulated_cached_steps(),
+                      m.get_cfg_accumulated_cached_steps(), m.get_accumulated_executed_steps(),
+                      m.get_accumulated_transformer_executed_steps())
+
+  def from_torch(self, t):
+    return t.to(self.device)
+
+  @staticmethod
+  def to_numpy(t):
+    return t.detach().float().cpu().numpy()

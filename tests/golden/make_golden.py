@@ -160,6 +160,30 @@ def taylor_known_answer(cache_dit) -> dict:
   return dict(state_steps=state_steps, d1=d1, approx_at_7=float(approx.flatten()[0]))
 
 
+def steps_mask_table(cache_dit) -> dict:
+  """`steps_mask` for every predefined policy over a range of schedule lengths, plus explicit bins."""
+  table = {}
+  for total in [4, 6] + list(range(8, 61)) + [64, 75, 100, 128]:
+    for policy in ("slow", "medium", "fast", "ultra"):
+      table[f"{policy}/{total}"] = cache_dit.steps_mask(total_steps=total, mask_policy=policy)
+  table["bins/a"] = cache_dit.steps_mask(compute_bins=[4, 2, 1], cache_bins=[3, 5, 2])
+  table["bins/b"] = cache_dit.steps_mask(compute_bins=[6, 1, 1, 1], cache_bins=[1, 2, 5], total_steps=14)
+  return table
+
+
+def config_tags(cache_dit) -> dict:
+  c = cache_dit
+  return {
+    "default": c.DBCacheConfig().strify(),
+    "scm": c.DBCacheConfig(Fn_compute_blocks=1, max_warmup_steps=4, max_cached_steps=10,
+                           max_continuous_cached_steps=3, residual_diff_threshold=0.12,
+                           steps_computation_mask=[1, 0, 1, 0], steps_computation_policy="static",
+                           num_inference_steps=4, force_refresh_step_hint=2, enable_separate_cfg=True).strify(),
+    "taylor": c.TaylorSeerCalibratorConfig(taylorseer_order=2).strify(),
+    "taylor_details": c.TaylorSeerCalibratorConfig(taylorseer_order=2).strify(details=True),
+  }
+
+
 def main():
   ap = argparse.ArgumentParser()
   ap.add_argument("--reference", required=True)
@@ -188,6 +212,8 @@ def main():
   if not args.only:
     json.dump(taylor_known_answer(cache_dit), open(os.path.join(HERE, "taylor_kat.json"), "w"),
               indent=1)
+    json.dump(dict(steps_mask=steps_mask_table(cache_dit), tags=config_tags(cache_dit)),
+              open(os.path.join(HERE, "host_tables.json"), "w"), sort_keys=True)
     try:
       from tests import block_scenarios as B
     except ImportError:
