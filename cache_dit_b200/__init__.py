@@ -19,5 +19,6 @@ from .caching import (BasicCacheConfig, BlockAdapter, BlockAdapterRegister, Cach
 from .distributed import ParallelismConfig, enable_parallelism
 from .quantization import Float8RowwiseLinear, QuantizeConfig, quantize
 from .summary import CacheStats, strify, summary
+from . import synthetic  # registers the block adapters of the DiT stand-ins
 
 __version__ = "0.1.0"

@@ -39,6 +39,12 @@ SIGNATURES = {
 
 _lib = None
 
+# Kernel launches issued through this binding since import (read by the benchmark), and an
+# optional per-launch timing hook: when `gemm_timer` is a list, every GEMM launch appends
+# (start_event, end_event, flops) recorded on the launching stream.
+launch_count = 0
+gemm_timer = None
+
 
 class NativeLibraryError(RuntimeError):
   pass
@@ -62,6 +68,8 @@ def lib() -> ctypes.CDLL:
 
 
 def check(status: int, what: str):
+  global launch_count
+  launch_count += 1
   if status != 0:
     L = lib()
     msg = L.cdb_status_string(status).decode()
@@ -194,9 +202,17 @@ def fp8_gemm_rowscaled(a_q, a_scale, w_q, w_scale, bias, out):
     raise RuntimeError("fp8_gemm_rowscaled: scales must be float32 [M] and [N]")
   if bias is not None and (bias.dtype != torch.bfloat16 or bias.numel() != N):
     raise RuntimeError("fp8_gemm_rowscaled: bias must be bf16 [N]")
+  timer = gemm_timer
+  if timer is not None:
+    start = torch.cuda.Event(enable_timing=True)
+    end = torch.cuda.Event(enable_timing=True)
+    start.record()
   st = lib().cdb_fp8_gemm_rowscaled(_ptr(a_q), _ptr(a_scale), _ptr(w_q), _ptr(w_scale), _ptr(bias), _ptr(out),
                                     M, N, K, out.stride(0) if M > 1 else max(N, out.stride(0)),
                                     _ptr(gemm_status_word(out.device)), _stream(out))
+  if timer is not None:
+    end.record()
+    timer.append((start, end, 2.0 * M * N * K))
   check(st, "cdb_fp8_gemm_rowscaled")
 
 

@@ -1,0 +1,216 @@
+"""Random-init stand-in with the architecture of FLUX.1-dev's transformer.
+
+19 double-stream + 38 single-stream blocks, hidden 3072, 24 heads of dim 128, RoPE over
+(16, 56, 56) axes, adaLN-Zero modulation, QK RMSNorm, tanh-GELU MLP of ratio 4.  Layer names follow
+the public diffusers implementation so that the quantization name filter and the block adapter see
+what they would see on the real model.  Both block kinds take
+`(hidden_states, encoder_hidden_states, temb, image_rotary_emb)` and return
+`(encoder_hidden_states, hidden_states)` (ForwardPattern.Pattern_1), so the two lists can be cached
+as one 57-block list, the way the reference adapts FLUX
+(src/cache_dit/caching/block_adapters/adapters.py:40-103, patch_functors/functor_flux.py:23-211).
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+from torch import nn
+
+from ..caching.block_adapters import BlockAdapter, BlockAdapterRegister
+from ..caching.forward_pattern import ForwardPattern
+from .layers import (RMSNorm, TimestepMLP, UlyssesGroup, apply_rope, attention, gelu_linear, norm_modulate,
+                     norm_modulate_linears, rope_frequencies, timestep_embedding)
+
+
+class AdaLayerNormZero(nn.Module):
+  """SiLU -> Linear -> n chunks of modulation parameters."""
+
+  def __init__(self, dim: int, chunks: int):
+    super().__init__()
+    self.chunks = chunks
+    self.linear = nn.Linear(dim, chunks * dim)
+
+  def forward(self, temb):
+    return self.linear(F.silu(temb)).chunk(self.chunks, dim=-1)
+
+
+class FeedForward(nn.Module):
+
+  def __init__(self, dim: int, inner: int):
+    super().__init__()
+    self.proj_in = nn.Linear(dim, inner)
+    self.proj_out = nn.Linear(inner, dim)
+
+
+class FluxAttention(nn.Module):
+
+  def __init__(self, dim: int, heads: int, joint: bool):
+    super().__init__()
+    self.heads = heads
+    self.head_dim = dim // heads
+    self.to_q = nn.Linear(dim, dim)
+    self.to_k = nn.Linear(dim, dim)
+    self.to_v = nn.Linear(dim, dim)
+    self.norm_q = RMSNorm(self.head_dim)
+    self.norm_k = RMSNorm(self.head_dim)
+    if joint:
+      self.to_out = nn.Linear(dim, dim)
+      self.add_q_proj = nn.Linear(dim, dim)
+      self.add_k_proj = nn.Linear(dim, dim)
+      self.add_v_proj = nn.Linear(dim, dim)
+      self.norm_added_q = RMSNorm(self.head_dim)
+      self.norm_added_k = RMSNorm(self.head_dim)
+      self.to_add_out = nn.Linear(dim, dim)
+
+  def heads_view(self, t):
+    return t.unflatten(-1, (self.heads, self.head_dim))
+
+
+class FluxTransformerBlock(nn.Module):
+  """Double-stream block: image and text tokens have their own weights and attend jointly."""
+
+  def __init__(self, dim: int, heads: int, mlp_ratio: float = 4.0):
+    super().__init__()
+    self.norm1 = AdaLayerNormZero(dim, 6)
+    self.norm1_context = AdaLayerNormZero(dim, 6)
+    self.attn = FluxAttention(dim, heads, joint=True)
+    self.ff = FeedForward(dim, int(dim * mlp_ratio))
+    self.ff_context = FeedForward(dim, int(dim * mlp_ratio))
+    self.cp: Optional[UlyssesGroup] = None
+
+  def forward(self, hidden_states, encoder_hidden_states, temb, image_rotary_emb):
+    a = self.attn
+    shift, scale, gate, shift_mlp, scale_mlp, gate_mlp = self.norm1(temb)
+    c_shift, c_scale, c_gate, c_shift_mlp, c_scale_mlp, c_gate_mlp = self.norm1_context(temb)
+    q, k, v = norm_modulate_linears(hidden_states, shift, scale, (a.to_q, a.to_k, a.to_v))
+    cq, ck, cv = norm_modulate_linears(encoder_hidden_states, c_shift, c_scale,
+                                       (a.add_q_proj, a.add_k_proj, a.add_v_proj))
+    q, k, v = a.norm_q(a.heads_view(q)), a.norm_k(a.heads_view(k)), a.heads_view(v)
+    cq, ck, cv = a.norm_added_q(a.heads_view(cq)), a.norm_added_k(a.heads_view(ck)), a.heads_view(cv)
+    q, k, v = torch.cat([cq, q], dim=1), torch.cat([ck, k], dim=1), torch.cat([cv, v], dim=1)
+    q, k = apply_rope(q, image_rotary_emb), apply_rope(k, image_rotary_emb)
+    o = attention(q, k, v, self.cp)
+    n_txt = encoder_hidden_states.shape[1]
+    hidden_states = hidden_states + gate[:, None] * a.to_out(o[:, n_txt:])
+    encoder_hidden_states = encoder_hidden_states + c_gate[:, None] * a.to_add_out(o[:, :n_txt])
+    (h, ) = norm_modulate_linears(hidden_states, shift_mlp, scale_mlp, (self.ff.proj_in, ))
+    hidden_states = hidden_states + gate_mlp[:, None] * gelu_linear(h, self.ff.proj_out)
+    (c, ) = norm_modulate_linears(encoder_hidden_states, c_shift_mlp, c_scale_mlp, (self.ff_context.proj_in, ))
+    encoder_hidden_states = encoder_hidden_states + c_gate_mlp[:, None] * gelu_linear(c, self.ff_context.proj_out)
+    return encoder_hidden_states, hidden_states
+
+
+class FluxSingleTransformerBlock(nn.Module):
+  """Single-stream block: text and image tokens share weights; attention and MLP run in parallel."""
+
+  def __init__(self, dim: int, heads: int, mlp_ratio: float = 4.0):
+    super().__init__()
+    self.norm = AdaLayerNormZero(dim, 3)
+    self.proj_mlp = nn.Linear(dim, int(dim * mlp_ratio))
+    self.attn = FluxAttention(dim, heads, joint=False)
+    self.proj_out = nn.Linear(dim + int(dim * mlp_ratio), dim)
+    self.cp: Optional[UlyssesGroup] = None
+
+  def forward(self, hidden_states, encoder_hidden_states, temb, image_rotary_emb):
+    a = self.attn
+    n_txt = encoder_hidden_states.shape[1]
+    x = torch.cat([encoder_hidden_states, hidden_states], dim=1)
+    shift, scale, gate = self.norm(temb)
+    q, k, v, mlp = norm_modulate_linears(x, shift, scale, (a.to_q, a.to_k, a.to_v, self.proj_mlp))
+    q, k, v = a.norm_q(a.heads_view(q)), a.norm_k(a.heads_view(k)), a.heads_view(v)
+    q, k = apply_rope(q, image_rotary_emb), apply_rope(k, image_rotary_emb)
+    o = attention(q, k, v, self.cp)
+    y = self.proj_out(torch.cat([o, F.gelu(mlp, approximate="tanh")], dim=-1))
+    x = x + gate[:, None] * y
+    return x[:, :n_txt], x[:, n_txt:]
+
+
+class FluxTransformer2DModel(nn.Module):
+  _repeated_blocks = ["FluxTransformerBlock", "FluxSingleTransformerBlock"]
+
+  def __init__(self, num_layers: int = 19, num_single_layers: int = 38, dim: int = 3072, heads: int = 24,
+               in_channels: int = 64, joint_attention_dim: int = 4096, pooled_projection_dim: int = 768,
+               axes_dims_rope: Tuple[int, int, int] = (16, 56, 56), guidance_embeds: bool = True):
+    super().__init__()
+    self.dim = dim
+    self.axes_dims_rope = axes_dims_rope
+    self.x_embedder = nn.Linear(in_channels, dim)
+    self.context_embedder = nn.Linear(joint_attention_dim, dim)
+    self.time_embedder = TimestepMLP(256, dim)
+    self.guidance_embedder = TimestepMLP(256, dim) if guidance_embeds else None
+    self.text_embedder = TimestepMLP(pooled_projection_dim, dim)
+    self.transformer_blocks = nn.ModuleList([FluxTransformerBlock(dim, heads) for _ in range(num_layers)])
+    self.single_transformer_blocks = nn.ModuleList(
+      [FluxSingleTransformerBlock(dim, heads) for _ in range(num_single_layers)])
+    self.norm_out = AdaLayerNormZero(dim, 2)
+    self.proj_out = nn.Linear(dim, in_channels)
+    self._cp: Optional[UlyssesGroup] = None
+
+  # ---- context parallelism: split tokens and ids at the root, gather after proj_out
+  # (the reference's plan for FLUX: src/cache_dit/distributed/transformers/flux.py:49-61)
+  def enable_context_parallel(self, config):
+    self._cp = UlyssesGroup(getattr(config, "_group", None))
+    for block in list(self.transformer_blocks) + list(self.single_transformer_blocks):
+      block.cp = self._cp
+
+  def disable_context_parallel(self):
+    self._cp = None
+    for block in list(self.transformer_blocks) + list(self.single_transformer_blocks):
+      block.cp = None
+
+  def forward(self, hidden_states, encoder_hidden_states, pooled_projections, timestep, img_ids, txt_ids,
+              guidance=None):
+    cp = self._cp
+    if cp is not None and cp.world > 1:
+      hidden_states = hidden_states.chunk(cp.world, dim=1)[cp.rank]
+      encoder_hidden_states = encoder_hidden_states.chunk(cp.world, dim=1)[cp.rank]
+      img_ids = img_ids.chunk(cp.world, dim=0)[cp.rank]
+      txt_ids = txt_ids.chunk(cp.world, dim=0)[cp.rank]
+    dt = hidden_states.dtype
+    hidden_states = self.x_embedder(hidden_states)
+    temb = self.time_embedder(timestep_embedding(timestep * 1000.0, 256).to(dt))
+    if self.guidance_embedder is not None and guidance is not None:
+      temb = temb + self.guidance_embedder(timestep_embedding(guidance * 1000.0, 256).to(dt))
+    temb = temb + self.text_embedder(pooled_projections)
+    encoder_hidden_states = self.context_embedder(encoder_hidden_states)
+    rope = rope_frequencies(torch.cat([txt_ids, img_ids], dim=0), self.axes_dims_rope)
+    for block in self.transformer_blocks:
+      encoder_hidden_states, hidden_states = block(hidden_states, encoder_hidden_states, temb, rope)
+    for block in self.single_transformer_blocks:
+      encoder_hidden_states, hidden_states = block(hidden_states, encoder_hidden_states, temb, rope)
+    shift, scale = self.norm_out(temb)
+    out = self.proj_out(norm_modulate(hidden_states, shift, scale))
+    if cp is not None and cp.world > 1:
+      import torch.distributed as dist
+      parts = [torch.empty_like(out) for _ in range(cp.world)]
+      dist.all_gather(parts, out.contiguous(), group=cp.group)
+      out = torch.cat(parts, dim=1)
+    return out
+
+  # ---- synthetic inputs of the 1024 x 1024 configuration: 4096 image + 512 text tokens
+  @staticmethod
+  def example_inputs(batch: int = 1, height: int = 1024, width: int = 1024, text_tokens: int = 512,
+                     device="cuda", dtype=torch.bfloat16, seed: int = 0, in_channels: int = 64,
+                     joint_attention_dim: int = 4096, pooled_projection_dim: int = 768):
+    g = torch.Generator().manual_seed(seed)
+    gh, gw = height // 16, width // 16
+    img_ids = torch.zeros(gh, gw, 3)
+    img_ids[..., 1] = torch.arange(gh)[:, None]
+    img_ids[..., 2] = torch.arange(gw)[None, :]
+    return dict(
+      hidden_states=torch.randn(batch, gh * gw, in_channels, generator=g).to(device=device, dtype=dtype),
+      encoder_hidden_states=torch.randn(batch, text_tokens, joint_attention_dim, generator=g).to(device=device, dtype=dtype),
+      pooled_projections=torch.randn(batch, pooled_projection_dim, generator=g).to(device=device, dtype=dtype),
+      img_ids=img_ids.reshape(-1, 3).to(device), txt_ids=torch.zeros(text_tokens, 3, device=device),
+      guidance=torch.full((batch, ), 3.5, device=device))
+
+
+@BlockAdapterRegister.register("Flux")
+def flux_adapter(pipe_or_transformer, **kwargs) -> BlockAdapter:
+  transformer = pipe_or_transformer if isinstance(pipe_or_transformer, nn.Module) else pipe_or_transformer.transformer
+  pipe = None if isinstance(pipe_or_transformer, nn.Module) else pipe_or_transformer
+  return BlockAdapter(pipe=pipe, transformer=transformer,
+                      blocks=transformer.transformer_blocks + transformer.single_transformer_blocks,
+                      blocks_name="transformer_blocks", dummy_blocks_names=["single_transformer_blocks"],
+                      forward_pattern=ForwardPattern.Pattern_1, check_forward_pattern=False, **kwargs)

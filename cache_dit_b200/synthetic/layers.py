@@ -1,0 +1,127 @@
+"""Building blocks shared by the random-init DiT stand-ins (FLUX-, Qwen-Image-, Wan-shape).
+
+These modules exist so the hot path can be exercised and timed without model weights: same layer
+shapes, same data flow, random parameters.  Where a linear layer has been swapped for
+`Float8RowwiseLinear`, the producer (adaLN-modulated LayerNorm, tanh-GELU) is fused into the
+activation-quantization kernel and the quantized activations are shared by all linears that read
+them (q/k/v), so the bf16 intermediate is never written.
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+import torch.nn.functional as F
+from torch import nn
+
+from .. import _native
+from ..quantization.linear import Float8RowwiseLinear, quantize_rows_fused
+
+
+def _all_fp8(linears: Sequence[nn.Module]) -> bool:
+  return all(isinstance(l, Float8RowwiseLinear) for l in linears)
+
+
+def norm_modulate_linears(x: torch.Tensor, shift: torch.Tensor, scale: torch.Tensor,
+                          linears: Sequence[nn.Module], eps: float = 1e-6) -> List[torch.Tensor]:
+  """[lin(LayerNorm(x) * (1 + scale) + shift) for lin in linears]; shift / scale are [B, C]."""
+  if _all_fp8(linears) and x.is_cuda:
+    # shift / scale are column slices of one modulation matrix: passed as strided views
+    a_q, a_scale, lead = quantize_rows_fused(x, _native.PRE_LAYERNORM_MOD, shift, scale, eps)
+    return [l.forward_quantized(a_q, a_scale, lead) for l in linears]
+  y = F.layer_norm(x, (x.shape[-1], ), eps=eps) * (1 + scale[:, None]) + shift[:, None]
+  return [l(y) for l in linears]
+
+
+def norm_modulate(x: torch.Tensor, shift: torch.Tensor, scale: torch.Tensor, eps: float = 1e-6):
+  return F.layer_norm(x, (x.shape[-1], ), eps=eps) * (1 + scale[:, None]) + shift[:, None]
+
+
+def gelu_linear(x: torch.Tensor, linear: nn.Module) -> torch.Tensor:
+  """linear(gelu_tanh(x))."""
+  if isinstance(linear, Float8RowwiseLinear) and x.is_cuda:
+    a_q, a_scale, lead = quantize_rows_fused(x, _native.PRE_GELU_TANH)
+    return linear.forward_quantized(a_q, a_scale, lead)
+  return linear(F.gelu(x, approximate="tanh"))
+
+
+class RMSNorm(nn.Module):
+
+  def __init__(self, dim: int, eps: float = 1e-6):
+    super().__init__()
+    self.eps = eps
+    self.weight = nn.Parameter(torch.ones(dim))
+
+  def forward(self, x):
+    return F.rms_norm(x, (x.shape[-1], ), self.weight, self.eps)
+
+
+def timestep_embedding(t: torch.Tensor, dim: int, max_period: float = 10000.0) -> torch.Tensor:
+  half = dim // 2
+  freqs = torch.exp(-math.log(max_period) * torch.arange(half, device=t.device, dtype=torch.float32) / half)
+  args = t.float()[:, None] * freqs[None]
+  return torch.cat([torch.cos(args), torch.sin(args)], dim=-1)
+
+
+class TimestepMLP(nn.Module):
+
+  def __init__(self, in_dim: int, dim: int):
+    super().__init__()
+    self.linear_1 = nn.Linear(in_dim, dim)
+    self.linear_2 = nn.Linear(dim, dim)
+
+  def forward(self, x):
+    return self.linear_2(F.silu(self.linear_1(x)))
+
+
+def rope_frequencies(ids: torch.Tensor, axes_dim: Sequence[int], theta: float = 10000.0):
+  """ids [S, n_axes] -> (cos, sin) [S, sum(axes_dim)] with each frequency repeated for its pair."""
+  cos, sin = [], []
+  for i, d in enumerate(axes_dim):
+    freqs = 1.0 / (theta**(torch.arange(0, d, 2, device=ids.device, dtype=torch.float32) / d))
+    ang = ids[:, i].float()[:, None] * freqs[None]
+    cos.append(torch.cos(ang).repeat_interleave(2, dim=-1))
+    sin.append(torch.sin(ang).repeat_interleave(2, dim=-1))
+  return torch.cat(cos, dim=-1), torch.cat(sin, dim=-1)
+
+
+def apply_rope(x: torch.Tensor, rope: Tuple[torch.Tensor, torch.Tensor]) -> torch.Tensor:
+  """x [B, S, H, D]; rotate consecutive pairs."""
+  cos, sin = rope
+  cos, sin = cos[None, :, None, :].to(x.dtype), sin[None, :, None, :].to(x.dtype)
+  x1, x2 = x.unflatten(-1, (-1, 2)).unbind(-1)
+  rot = torch.stack([-x2, x1], dim=-1).flatten(-2)
+  return x * cos + rot * sin
+
+
+class UlyssesGroup:
+  """What attention needs to know about context parallelism: the group and its size."""
+
+  def __init__(self, group=None):
+    import torch.distributed as dist
+    self.group = group
+    self.world = dist.get_world_size(group)
+    self.rank = dist.get_rank(group)
+
+
+def _all_to_all(x: torch.Tensor, scatter_dim: int, gather_dim: int, cp: UlyssesGroup) -> torch.Tensor:
+  """Split `scatter_dim` over the ranks and concatenate what arrives along `gather_dim`."""
+  import torch.distributed as dist
+  w = cp.world
+  chunks = [c.contiguous() for c in x.chunk(w, dim=scatter_dim)]
+  recv = [torch.empty_like(chunks[0]) for _ in range(w)]
+  dist.all_to_all(recv, chunks, group=cp.group)
+  return torch.cat(recv, dim=gather_dim)
+
+
+def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cp: Optional[UlyssesGroup] = None) -> torch.Tensor:
+  """q, k, v [B, S_local, H, D] -> [B, S_local, H*D].  Under Ulysses the heads are exchanged for the
+  full sequence before the attention kernel and back after it (four all-to-alls)."""
+  if cp is not None and cp.world > 1:
+    q, k, v = (_all_to_all(t, 2, 1, cp) for t in (q, k, v))  # [B, S, H/W, D]
+  o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2))
+  o = o.transpose(1, 2)  # [B, S, H(/W), D]
+  if cp is not None and cp.world > 1:
+    o = _all_to_all(o.contiguous(), 1, 2, cp)  # [B, S/W, H, D]
+  return o.flatten(2)
