@@ -26,6 +26,7 @@ SIGNATURES = {
   "cdb_rel_l1_scratch_bytes": (c_size_t, []),
   "cdb_rel_l1": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p,
                          c_size_t, c_void_p]),
+  "cdb_rel_l1_static": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p]),
   "cdb_taylor_apply": (c_int, [c_void_p, POINTER(c_void_p), POINTER(c_float), POINTER(c_float), c_int,
                                c_int, c_void_p, c_int64, c_int, c_void_p]),
   "cdb_taylor_update": (c_int, [c_void_p, c_void_p, POINTER(c_void_p), POINTER(c_void_p), c_int, c_float,

@@ -13,6 +13,8 @@
 // hardware ops.
 #include <cooperative_groups.h>
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace cg = cooperative_groups;
@@ -464,4 +466,63 @@ extern "C" int cdb_taylor_update(const void* after, const void* before, const vo
   const bool pow2 = is_pow2(window);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   CDB_DISPATCH(launch_update, vec, after, before, a, n_new, write_y, window, pow2, n, st)
+}
+
+// ------------------------------------------------------------------------------------------
+// Relative-L1 check for callers that cannot allocate device memory
+// ------------------------------------------------------------------------------------------
+// Some hosts of this library are not allowed to call cudaMalloc (or anything that does it for
+// them) around the check: a plug-in running inside another framework's memory pool, a process
+// whose device memory is fully pre-partitioned, a serving loop with a "no allocation after
+// warm-up" rule.  cdb_rel_l1 asks such a caller for a scratch buffer it has no clean way to
+// provide.  This variant brings its own: the reduction scratch lives in the library's image as a
+// file-scope device array, so every device that loads the library holds these bytes until the
+// process exits, and no allocation is made at any point.
+static __device__ __align__(256) unsigned char g_rel_l1_static_scratch[sizeof(cdb::RelL1Scratch)];
+
+namespace cdb {
+
+// Host code may not hand `g_rel_l1_static_scratch` to a kernel: on the host that name is only a
+// stand-in for the symbol.  Its device address is looked up once per device (with that device
+// current) and cached.
+static int static_scratch_for_current_device(RelL1Scratch** out) {
+  constexpr int kMaxDevices = 64;
+  static RelL1Scratch* cached[kMaxDevices] = {};
+  static std::mutex mu;
+  int dev = -1;
+  CDB_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return CDB_ERR_UNSUPPORTED;
+  std::lock_guard<std::mutex> lock(mu);
+  if (cached[dev] == nullptr) {
+    void* p = nullptr;
+    CDB_CUDA_CHECK(cudaGetSymbolAddress(&p, g_rel_l1_static_scratch));
+    if (p == nullptr) return CDB_ERR_CUDA;
+    cached[dev] = static_cast<RelL1Scratch*>(p);
+  }
+  *out = cached[dev];
+  return CDB_OK;
+}
+
+}  // namespace cdb
+
+extern "C" int cdb_rel_l1_static(const void* cur, const void* base, const void* prev, void* residual_out,
+                                 int64_t n, int dtype, float* means, void* stream) {
+  if (!cur || !prev || !means || n <= 0) return CDB_ERR_BAD_ARGUMENT;
+  if (n > CDB_REL_L1_STATIC_MAX_ELEMS) {
+    cdb::set_error_text("cdb_rel_l1_static: n exceeds CDB_REL_L1_STATIC_MAX_ELEMS (2^30 elements); "
+                        "use cdb_rel_l1 with caller-provided scratch for larger tensors");
+    return CDB_ERR_TOO_LARGE;
+  }
+  RelL1Scratch* sc = nullptr;
+  int rc = static_scratch_for_current_device(&sc);
+  if (rc != CDB_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // The array is shared by every call and keeps whatever the previous call left in it.  Only the
+  // arrival counter has to start at zero (the partial sums are overwritten before they are read);
+  // clear its 16-byte header on the caller's stream so a launch that was cut short earlier cannot
+  // poison this one.
+  CDB_CUDA_CHECK(cudaMemsetAsync(sc, 0, 16, st));
+  if (residual_out && !base && residual_out == cur) residual_out = nullptr;
+  const bool vec = aligned16(cur) && aligned16(base) && aligned16(prev) && aligned16(residual_out);
+  CDB_DISPATCH(launch_rel_l1, vec, cur, base, prev, residual_out, n, means, sc, st)
 }

@@ -12,6 +12,8 @@ namespace cdb {
 
 // Thread-local text of the last CUDA error; exposed through cdb_last_cuda_error().
 void set_cuda_error(cudaError_t e, const char* where);
+// Same slot, free text (used for argument errors that deserve an explanation).
+void set_error_text(const char* text);
 
 #define CDB_CUDA_CHECK(expr)                         \
   do {                                               \

@@ -13,6 +13,8 @@ void set_cuda_error(cudaError_t e, const char* where) {
            cudaGetErrorString(e), where ? where : "?");
 }
 
+void set_error_text(const char* text) { snprintf(g_cuda_error, sizeof(g_cuda_error), "%s", text ? text : ""); }
+
 int sm_count() {
   static int cached[64];
   int dev = 0;
@@ -39,6 +41,7 @@ extern "C" const char* cdb_status_string(int status) {
     case CDB_ERR_CUDA: return "CUDA call failed";
     case CDB_ERR_NO_DEVICE: return "no sm_100 device";
     case CDB_ERR_DEVICE_TIMEOUT: return "bounded device-side wait expired";
+    case CDB_ERR_TOO_LARGE: return "size exceeds the limit of this entry point";
     default: return "unknown status";
   }
 }

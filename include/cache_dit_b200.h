@@ -37,7 +37,8 @@ enum cdb_status {
   CDB_ERR_SCRATCH_TOO_SMALL = 3,
   CDB_ERR_CUDA = 4,           /* a CUDA runtime / driver call failed; see cdb_last_cuda_error */
   CDB_ERR_NO_DEVICE = 5,      /* no sm_100 device is current */
-  CDB_ERR_DEVICE_TIMEOUT = 6  /* a bounded device-side wait ran out (read from a status word) */
+  CDB_ERR_DEVICE_TIMEOUT = 6, /* a bounded device-side wait ran out (read from a status word) */
+  CDB_ERR_TOO_LARGE = 7       /* a size beyond the stated maximum of the entry point */
 };
 
 #define CDB_MAX_TAYLOR_TERMS 5 /* Taylor order <= 4: terms dY[0..4] */
@@ -67,6 +68,28 @@ CDB_API size_t cdb_rel_l1_scratch_bytes(void);
 CDB_API int cdb_rel_l1(const void* cur, const void* base, const void* prev, void* residual_out,
                int64_t n, int dtype, float* means, void* scratch, size_t scratch_bytes,
                void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Relative-L1 check without any allocation.  No counterpart in the reference: it exists for
+ * hosts that must not allocate device memory around the check (a plug-in living inside another
+ * framework's memory pool, a process whose device memory is pre-partitioned, a serving loop with
+ * a no-allocation-after-warm-up rule) and therefore cannot supply cdb_rel_l1's scratch buffer.
+ *
+ * Same arithmetic and outputs as cdb_rel_l1 with `prev` given (means[0], means[1], optional
+ * residual_out); the reduction scratch is a fixed array inside the library's device image
+ * (about 16 KB per GPU that loads the library, held until the process exits).
+ *   - n may not exceed CDB_REL_L1_STATIC_MAX_ELEMS; larger calls return CDB_ERR_TOO_LARGE and the
+ *     reason is available from cdb_last_cuda_error().
+ *   - The first call on each device looks up the array's device address (with that device
+ *     current).  Make that first call outside of any CUDA stream capture.
+ *   - All calls on a device share the one array.  Calls must not overlap on the GPU: issue them
+ *     on one stream, or order the streams yourself; overlapping launches race on the scratch and
+ *     give wrong means.
+ *   - The entry point calls no cudaMalloc / cudaFree and no library routine that allocates.
+ * ---------------------------------------------------------------------------------------- */
+#define CDB_REL_L1_STATIC_MAX_ELEMS ((int64_t)1 << 30)
+CDB_API int cdb_rel_l1_static(const void* cur, const void* base, const void* prev, void* residual_out,
+                              int64_t n, int dtype, float* means, void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * Cached-residual apply.  Replaces
