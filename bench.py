@@ -282,7 +282,11 @@ def run_ours(args):
   if rank == 0:
     sampler.start()
   launches0 = nat.launch_count
+  if args.profile_timed_region:
+    torch.cuda.profiler.start()
   ms = timed(stepper.step, args.steps, barrier)
+  if args.profile_timed_region:
+    torch.cuda.profiler.stop()
   launches = nat.launch_count - launches0
   clocks = sampler.stop() if rank == 0 else {}
   masks = [list(m) for m in stepper.masks]
@@ -426,6 +430,8 @@ def main():
   ap.add_argument("--steps", type=int, default=2 * STEPS_PER_GENERATION)
   ap.add_argument("--warmup", type=int, default=STEPS_PER_GENERATION)
   ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+  ap.add_argument("--profile-timed-region", action="store_true",
+                  help="bracket the first timed region with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
   ap.add_argument("--skip-extras", action="store_true",
                   help="leave out the cache-kernel microbenchmarks, the FP8 library peak and the CPU sample")
   args = ap.parse_args()

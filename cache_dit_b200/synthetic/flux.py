@@ -131,10 +131,14 @@ class FluxTransformer2DModel(nn.Module):
 
   def __init__(self, num_layers: int = 19, num_single_layers: int = 38, dim: int = 3072, heads: int = 24,
                in_channels: int = 64, joint_attention_dim: int = 4096, pooled_projection_dim: int = 768,
-               axes_dims_rope: Tuple[int, int, int] = (16, 56, 56), guidance_embeds: bool = True):
+               axes_dims_rope: Tuple[int, int, int] = (16, 56, 56), guidance_embeds: bool = True,
+               time_scale: float = 1000.0):
     super().__init__()
     self.dim = dim
     self.axes_dims_rope = axes_dims_rope
+    # multiplier of the timestep before the sinusoidal embedding (1000 in FLUX); a random-init
+    # embedder is smoother in t for smaller values
+    self.time_scale = time_scale
     self.x_embedder = nn.Linear(in_channels, dim)
     self.context_embedder = nn.Linear(joint_attention_dim, dim)
     self.time_embedder = TimestepMLP(256, dim)
@@ -169,7 +173,7 @@ class FluxTransformer2DModel(nn.Module):
       txt_ids = txt_ids.chunk(cp.world, dim=0)[cp.rank]
     dt = hidden_states.dtype
     hidden_states = self.x_embedder(hidden_states)
-    temb = self.time_embedder(timestep_embedding(timestep * 1000.0, 256).to(dt))
+    temb = self.time_embedder(timestep_embedding(timestep * self.time_scale, 256).to(dt))
     if self.guidance_embedder is not None and guidance is not None:
       temb = temb + self.guidance_embedder(timestep_embedding(guidance * 1000.0, 256).to(dt))
     temb = temb + self.text_embedder(pooled_projections)

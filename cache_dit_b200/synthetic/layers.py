@@ -110,8 +110,14 @@ def _all_to_all(x: torch.Tensor, scatter_dim: int, gather_dim: int, cp: UlyssesG
   import torch.distributed as dist
   w = cp.world
   chunks = [c.contiguous() for c in x.chunk(w, dim=scatter_dim)]
-  recv = [torch.empty_like(chunks[0]) for _ in range(w)]
-  dist.all_to_all(recv, chunks, group=cp.group)
+  if dist.get_backend(cp.group) == "gloo":
+    # gloo has no all-to-all: gather everything and keep this rank's slices (CPU tests only)
+    everything = [torch.empty_like(x) for _ in range(w)]
+    dist.all_gather(everything, x.contiguous(), group=cp.group)
+    recv = [e.chunk(w, dim=scatter_dim)[cp.rank] for e in everything]
+  else:
+    recv = [torch.empty_like(chunks[0]) for _ in range(w)]
+    dist.all_to_all(recv, chunks, group=cp.group)
   return torch.cat(recv, dim=gather_dim)
 
 
