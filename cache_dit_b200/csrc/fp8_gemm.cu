@@ -18,6 +18,8 @@
 // kernel returns, so a logic error cannot wedge the device.
 #include <cuda.h>
 
+#include <cstdlib>
+#include <cstring>
 #include <mutex>
 #include <unordered_map>
 
@@ -38,6 +40,10 @@ constexpr int A_STAGE_BYTES = BM * BK;
 constexpr int B_STAGE_BYTES = BN * BK;
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;
+// Which kernel large-M problems use unless CDB_GEMM_KERNEL overrides it.
+#ifndef CDB_GEMM_DEFAULT_PAIR
+#define CDB_GEMM_DEFAULT_PAIR 0
+#endif
 
 struct __align__(8) GemmBarriers {
   uint64_t full[STAGES];       // TMA bytes landed
@@ -364,6 +370,279 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
   }
 }
 
+// ---- CTA-pair variant (tcgen05 cta_group::2) ---------------------------------------------------
+// Two CTAs on the two SMs of a TPC work on one 256 x 256 tile.  Each CTA loads its own 128 rows
+// of A and only HALF of the weight tile (128 of its 256 rows); one elected thread of the even CTA
+// issues a single 256 x 256 x 32 MMA per K step that reads both halves through the pair's shared
+// memory, and each CTA receives the accumulator rows of its own A half in its own TMEM.  Per flop
+// this moves 2/3 of the bytes from L2 into shared memory and half of the weight bytes per SM,
+// which is what limits the single-CTA kernel.  No multicast is used anywhere: every TMA copy is a
+// plain per-CTA load whose completion is counted on the even CTA's barrier, and the MMA's
+// completion is committed to each CTA's barrier with one (non-multicast) commit per CTA.
+constexpr int P_STAGES = 6;
+constexpr int P_A_BYTES = 128 * BK;  // 128 rows of A per CTA
+constexpr int P_B_BYTES = 128 * BK;  // 128 rows (half) of the weight tile per CTA
+constexpr int P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;
+constexpr int P_BM = 256;            // tile rows per CTA pair
+
+struct __align__(8) PairBarriers {
+  uint64_t full[P_STAGES];   // even CTA's copy is used: bytes of both CTAs land here
+  uint64_t empty[P_STAGES];  // per CTA: the MMAs that read this CTA's stage have retired
+  uint64_t acc_full[2];      // per CTA: accumulator complete
+  uint64_t acc_empty[2];     // even CTA's copy is used: both CTAs' epilogues drained the buffer
+  uint32_t tmem_base;
+  volatile int abort_flag;
+};
+constexpr int P_SMEM_TILE_BYTES = P_STAGES * P_STAGE_BYTES;
+constexpr int P_SMEM_TOTAL_BYTES = 1024 + P_SMEM_TILE_BYTES + BN * 4 * 2 + (int)sizeof(PairBarriers);
+constexpr uint32_t IDESC_E4M3_F32_M256 =
+    (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(P_BM >> 4) << 24);
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// Address of the same shared-memory location in the CTA with the given rank of this cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// Per-CTA TMA load of a CTA pair: data goes to this CTA's shared memory, the byte count is
+// reported to the barrier at `bar_cluster_addr` (the even CTA's).
+__device__ __forceinline__ void tma_load_2d_pair(const CUtensorMap* map, uint32_t bar_cluster_addr, void* dst,
+                                                 int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void umma_f8_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrive on a barrier (given by its cluster address, in either CTA) when all MMAs issued so far retire.
+__device__ __forceinline__ void tcgen05_commit_pair(uint32_t bar_cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   bar_cluster_addr)
+               : "memory");
+}
+__device__ __forceinline__ bool pair_wait(uint64_t* bar, uint32_t parity, PairBarriers* gb, int32_t* status_word,
+                                          int code) {
+  uint64_t t0 = 0;
+  for (uint32_t it = 0;; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 255u) == 255u) {
+      if (gb->abort_flag) return false;
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > WAIT_LIMIT_NS) {
+        gb->abort_flag = 1;
+        if (status_word) atomicCAS(status_word, 0, code);
+        return false;
+      }
+    }
+  }
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+    fp8_gemm_rowscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
+                                   const __grid_constant__ CUtensorMap map_w, const float* __restrict__ sa,
+                                   const float* __restrict__ sw, const __nv_bfloat16* __restrict__ bias,
+                                   __nv_bfloat16* __restrict__ out, int M, int N, int K, int64_t ld_out,
+                                   int32_t* status_word) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  float* s_colscale = reinterpret_cast<float*>(smem + P_SMEM_TILE_BYTES);
+  float* s_bias = s_colscale + BN;
+  PairBarriers* gb = reinterpret_cast<PairBarriers*>(s_bias + BN);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0 = even CTA: owns the shared barriers, issues the MMAs
+  const int m_tiles = (M + P_BM - 1) / P_BM;
+  const int n_tiles = (N + BN - 1) / BN;
+  const int num_tiles = m_tiles * n_tiles;
+  const int k_blocks = (K + BK - 1) / BK;
+  const int pair_id = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < P_STAGES; ++s) {
+      mbar_init(&gb->full[s], 1);
+      mbar_init(&gb->empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&gb->acc_full[b], 1);
+      mbar_init(&gb->acc_empty[b], 2 * (EPI_THREADS / 32));
+    }
+    gb->abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {  // the same warp of both CTAs allocates the pair's tensor memory
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(&gb->tmem_base)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers exist before anything is signalled across the pair
+  tcgen05_fence_after();
+  const uint32_t tmem_base = gb->tmem_base;
+
+  if (warp == 0) {
+    // ---------------- TMA producer (both CTAs) ----------------
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
+        const int m0 = (tile % m_tiles) * P_BM + (int)rank * 128;
+        const int n0 = (tile / m_tiles) * BN + (int)rank * 128;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % P_STAGES;
+          const uint32_t ph = (it / P_STAGES) & 1u;
+          ok = pair_wait(&gb->empty[s], ph ^ 1u, gb, status_word, 11);
+          if (!ok) break;
+          uint8_t* a_dst = smem + s * P_STAGE_BYTES;
+          uint8_t* b_dst = a_dst + P_A_BYTES;
+          if (rank == 0) mbar_expect_tx(&gb->full[s], 2 * P_STAGE_BYTES);  // both CTAs' bytes
+          const uint32_t full_addr = map_to_cta(smem_u32(&gb->full[s]), 0);
+          tma_load_2d_pair(&map_a, full_addr, a_dst, kb * BK, m0);
+          tma_load_2d_pair(&map_w, full_addr, b_dst, kb * BK, n0);
+        }
+      }
+      // A CTA may not retire while copies into its shared memory are in flight or while the peer's
+      // MMAs still read its tiles: wait (bounded) until the consumer has released every stage used.
+      const uint32_t issued = it;
+      for (uint32_t j = (issued > P_STAGES ? issued - P_STAGES : 0); j < issued; ++j) {
+        const int s = j % P_STAGES;
+        const uint32_t ph = (j / P_STAGES) & 1u;
+        uint64_t t0 = global_timer_ns();
+        while (!mbar_try_wait(&gb->empty[s], ph)) {
+          if (gb->abort_flag || global_timer_ns() - t0 > WAIT_LIMIT_NS) break;
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (even CTA only) ----------------
+    if (lane == 0 && rank == 0) {
+      uint32_t it = 0, local_tile = 0;
+      bool ok = true;
+      for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs, ++local_tile) {
+        const uint32_t buf = local_tile & 1u;
+        const uint32_t use = local_tile >> 1;
+        ok = pair_wait(&gb->acc_empty[buf], (use & 1u) ^ 1u, gb, status_word, 12);
+        if (!ok) break;
+        tcgen05_fence_after();
+        const uint32_t tmem_d = tmem_base + buf * BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % P_STAGES;
+          const uint32_t ph = (it / P_STAGES) & 1u;
+          ok = pair_wait(&gb->full[s], ph, gb, status_word, 13);
+          if (!ok) break;
+          tcgen05_fence_after();
+          const uint32_t a_addr = smem_u32(smem + s * P_STAGE_BYTES);
+          const uint64_t adesc = make_kmajor_sw128_desc(a_addr);
+          const uint64_t bdesc = make_kmajor_sw128_desc(a_addr + P_A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            umma_f8_pair(tmem_d, adesc + (uint64_t)(k * (UMMA_K >> 4)), bdesc + (uint64_t)(k * (UMMA_K >> 4)),
+                         IDESC_E4M3_F32_M256, (kb | k) != 0 ? 1u : 0u);
+          }
+          const uint32_t e = smem_u32(&gb->empty[s]);
+          tcgen05_commit_pair(map_to_cta(e, 0));  // frees the stage in this CTA ...
+          tcgen05_commit_pair(map_to_cta(e, 1));  // ... and in the peer
+        }
+        if (ok) {
+          const uint32_t f = smem_u32(&gb->acc_full[buf]);
+          tcgen05_commit_pair(map_to_cta(f, 0));
+          tcgen05_commit_pair(map_to_cta(f, 1));
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------- epilogue (warps 2..5 of both CTAs): this CTA's 128 rows x 256 columns ----------------
+    const int quarter = warp & 3;
+    const int et = threadIdx.x - EPI_WARP0 * 32;
+    uint32_t local_tile = 0;
+    bool ok = true;
+    for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs, ++local_tile) {
+      const int m0 = (tile % m_tiles) * P_BM + (int)rank * 128;
+      const int n0 = (tile / m_tiles) * BN;
+      const uint32_t buf = local_tile & 1u;
+      const uint32_t use = local_tile >> 1;
+      asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
+      for (int c = et; c < BN; c += EPI_THREADS) {
+        const int col = n0 + c;
+        s_colscale[c] = col < N ? __ldg(sw + col) : 0.f;
+        s_bias[c] = (bias != nullptr && col < N) ? __bfloat162float(bias[col]) : 0.f;
+      }
+      ok = pair_wait(&gb->acc_full[buf], use & 1u, gb, status_word, 14);
+      ok = epi_all(ok);
+      if (!ok) break;
+      tcgen05_fence_after();
+
+      const int row = m0 + quarter * 32 + lane;
+      const float rs = row < M ? __ldg(sa + row) : 0.f;
+      __nv_bfloat16* orow = out + (int64_t)row * ld_out + n0;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t acc[32];
+        tmem_ld_32x32b_x32(taddr + c0, acc);
+        tmem_ld_wait();
+        if (row < M) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const int cb = c0 + g * 8;
+            if (n0 + cb < N) {
+              uint32_t w[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const int c = cb + 2 * j;
+                float v0 = __uint_as_float(acc[g * 8 + 2 * j]) * rs * s_colscale[c] + s_bias[c];
+                float v1 = __uint_as_float(acc[g * 8 + 2 * j + 1]) * rs * s_colscale[c + 1] + s_bias[c + 1];
+                w[j] = pack_bf16x2(v0, v1);
+              }
+              *reinterpret_cast<uint4*>(orow + cb) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+          }
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&gb->acc_empty[buf]), 0));
+    }
+  }
+
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // neither CTA leaves while the other may still touch its shared memory or TMEM
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS)
+                 : "memory");
+  }
+}
+
 // ---- host side -----------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
@@ -447,23 +726,45 @@ extern "C" int cdb_fp8_gemm_rowscaled(const void* a_q, const float* a_scale, con
     return CDB_ERR_UNSUPPORTED;
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
+  static int mode = 0;  // 0 = choose by shape, 1 = single-CTA kernel, 2 = CTA-pair kernel
   std::call_once(once, [] {
     attr_err = cudaFuncSetAttribute(fp8_gemm_rowscaled_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     SMEM_TOTAL_BYTES);
+    if (attr_err == cudaSuccess)
+      attr_err = cudaFuncSetAttribute(fp8_gemm_rowscaled_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      P_SMEM_TOTAL_BYTES);
+    const char* env = getenv("CDB_GEMM_KERNEL");  // tuning / testing knob: "1cta" | "2cta"
+    if (env && strcmp(env, "1cta") == 0) mode = 1;
+    if (env && strcmp(env, "2cta") == 0) mode = 2;
   });
   CDB_CUDA_CHECK(attr_err);
-  CUtensorMap map_a, map_w;
-  if (!cached_map(&map_a, a_q, (uint64_t)M, (uint64_t)K, BM) ||
-      !cached_map(&map_w, w_q, (uint64_t)N, (uint64_t)K, BN)) {
-    set_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled");
-    return CDB_ERR_CUDA;
-  }
-  const int64_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const int sms = sm_count();
-  const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
-  fp8_gemm_rowscaled_kernel<<<grid, GEMM_THREADS, SMEM_TOTAL_BYTES, static_cast<cudaStream_t>(stream)>>>(
-      map_a, map_w, a_scale, w_scale, static_cast<const __nv_bfloat16*>(bias),
-      static_cast<__nv_bfloat16*>(out), (int)M, (int)N, (int)K, ld_out, status_word);
+  const bool pair = mode == 2 || (mode == 0 && M > BM && CDB_GEMM_DEFAULT_PAIR);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  CUtensorMap map_a, map_w;
+  if (pair) {
+    if (!cached_map(&map_a, a_q, (uint64_t)M, (uint64_t)K, 128) ||
+        !cached_map(&map_w, w_q, (uint64_t)N, (uint64_t)K, 128)) {
+      set_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled");
+      return CDB_ERR_CUDA;
+    }
+    const int64_t tiles = ((M + P_BM - 1) / P_BM) * ((N + BN - 1) / BN);
+    const int64_t pairs = tiles < sms / 2 ? tiles : sms / 2;
+    fp8_gemm_rowscaled_pair_kernel<<<(unsigned)(2 * pairs), GEMM_THREADS, P_SMEM_TOTAL_BYTES, st>>>(
+        map_a, map_w, a_scale, w_scale, static_cast<const __nv_bfloat16*>(bias),
+        static_cast<__nv_bfloat16*>(out), (int)M, (int)N, (int)K, ld_out, status_word);
+  } else {
+    if (!cached_map(&map_a, a_q, (uint64_t)M, (uint64_t)K, BM) ||
+        !cached_map(&map_w, w_q, (uint64_t)N, (uint64_t)K, BN)) {
+      set_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled");
+      return CDB_ERR_CUDA;
+    }
+    const int64_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
+    fp8_gemm_rowscaled_kernel<<<grid, GEMM_THREADS, SMEM_TOTAL_BYTES, st>>>(
+        map_a, map_w, a_scale, w_scale, static_cast<const __nv_bfloat16*>(bias),
+        static_cast<__nv_bfloat16*>(out), (int)M, (int)N, (int)K, ld_out, status_word);
+  }
   CDB_CUDA_CHECK(cudaGetLastError());
   return CDB_OK;
 }

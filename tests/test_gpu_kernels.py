@@ -260,3 +260,56 @@ def test_fp8_gemm_strided_output_and_back_to_back(nat):
   assert torch.equal(big[:, N:], dense)
   assert not big[:, :N].any()
   assert nat.gemm_device_status(dense.device) == 0
+
+
+# ------------------------------------------------------------------------------ shapes of the sharded configs
+# Qwen-Image 1328^2: 6889 image tokens over 8 ranks -> shards of 862 / 861 tokens (uneven), hidden 3072;
+# Wan2.1-14B 81x720p: 75600 tokens over 8 ranks -> 9450 tokens, hidden 5120, FFN 13824.
+@pytest.mark.parametrize("shape", [(1, 862, 3072), (1, 861, 3072), (1, 256, 3072), (1, 9450, 5120)])
+def test_cache_kernels_on_context_parallel_shard_shapes(nat, shape):
+  prev_d, prev = make(shape, "bf16", 50)
+  h0_d, h0 = make(shape, "bf16", 51)
+  noise_d, _ = make(shape, "bf16", 52, 0.05)
+  h_d = (prev_d.float() + h0_d.float() + noise_d.float()).to(torch.bfloat16)
+  res_d = torch.empty_like(h_d)
+  means = torch.zeros(2, dtype=torch.float32, device="cuda")
+  nat.rel_l1(h_d, h0_d, prev_d, res_d, means)
+  cur = O.residual(h_d.float().cpu().numpy(), h0, "bf16")
+  np.testing.assert_array_equal(res_d.float().cpu().numpy(), cur)
+  md, mp = O.local_means(prev, cur, "bf16")
+  got = means.cpu().numpy()
+  assert abs(got[0] - md) <= 2.0**-8 * md and abs(got[1] - mp) <= 2.0**-8 * mp
+  d1_d, d1 = make(shape, "bf16", 53, 0.1)
+  out_d = torch.empty_like(h_d)
+  nat.taylor_apply(h_d, [prev_d, d1_d], [1.0, 1.0], [1.0, 2.0], True, out_d)
+  want = O.apply_add(O.taylor_series([prev, d1], 2, "bf16"), h_d.float().cpu().numpy(), "bf16")
+  np.testing.assert_array_equal(out_d.float().cpu().numpy(), want)
+
+
+@pytest.mark.parametrize("M,N,K", [(862, 3072, 3072), (9450, 13824, 5120), (9450, 5120, 13824), (512, 18432, 3072),
+                                   (1, 18432, 3072)])
+def test_fp8_gemm_on_model_shapes(nat, M, N, K):
+  x_d, x = activations(M, K, M + 1)
+  g = torch.Generator().manual_seed(98)
+  w_d = (0.02 * torch.randn(N, K, generator=g)).to(torch.bfloat16).cuda()
+  aq = torch.empty(M, K, dtype=torch.float8_e4m3fn, device="cuda")
+  sa = torch.empty(M, dtype=torch.float32, device="cuda")
+  wq = torch.empty(N, K, dtype=torch.float8_e4m3fn, device="cuda")
+  sw = torch.empty(N, dtype=torch.float32, device="cuda")
+  nat.fp8_quant_rows(x_d, aq, sa)
+  nat.fp8_quant_rows(w_d, wq, sw)
+  out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+  nat.fp8_gemm_rowscaled(aq, sa, wq, sw, None, out)
+  torch.cuda.synchronize()
+  assert nat.gemm_device_status(out.device) == 0
+  rows = slice(0, min(M, 1024))  # the CPU product of the largest shapes is checked on a row block
+  want = F.scaled_mm(aq[rows].view(torch.uint8).cpu().numpy(), sa[rows].cpu().numpy(),
+                     wq.view(torch.uint8).cpu().numpy(), sw.cpu().numpy())
+  got = out[rows].float().cpu().numpy()
+  assert np.isfinite(out.float()).all().item()
+  assert rel_fro(got, want) < 2e-3
+  if M > 1024:  # and the last row block (ragged M tile)
+    rows = slice(M - 300, M)
+    want = F.scaled_mm(aq[rows].view(torch.uint8).cpu().numpy(), sa[rows].cpu().numpy(),
+                       wq.view(torch.uint8).cpu().numpy(), sw.cpu().numpy())
+    assert rel_fro(out[rows].float().cpu().numpy(), want) < 2e-3
