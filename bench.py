@@ -347,14 +347,14 @@ def run_ours(args):
   if not args.skip_extras:
     line["roofline_cache_kernels"] = cache_kernel_rooflines(device, peaks["hbm_gbs"])
     line["roofline_cache_kernels"]["peak_source"] = f"{peak_kind} copy bandwidth"
-    line["cpu_baseline"] = cpu_baseline(sample_only=True)
+    line["cpu_baseline"] = cpu_baseline(sample_only=True, hits=len(masks[0]) if masks else None)
   if world > 1:
     dist.destroy_process_group()
   print(json.dumps(line), flush=True)
 
 
 # ------------------------------------------------------------------------------------ CPU arm
-def cpu_baseline(sample_only=False, repeats=1):
+def cpu_baseline(sample_only=False, hits=None):
   """The reference's path restated on the CPU (numpy oracle), timed on this host's cores.
 
   Sample: the cache ops of one step at full size (bf16 [1, 4608, 3072]: check, TaylorSeer update,
@@ -397,14 +397,15 @@ def cpu_baseline(sample_only=False, repeats=1):
   t_single = 3 * linear(4608, 3072, 3072) + linear(4608, 3072, 12288) + linear(4608, 15360, 3072)
   computed = 19 * t_double + 38 * t_single
   cached = 8 * t_double
-  hits = 14  # hit count of the reference schedule for this configuration
+  if hits is None:
+    hits = 14  # hit count of the reference's synthetic cache-step schedule (2 hits, 1 miss after warm-up)
   per_generation = (STEPS_PER_GENERATION - hits) * (computed + t_update) + hits * (cached + t_apply) \
       + (STEPS_PER_GENERATION - 8) * t_check
   return {"value": STEPS_PER_GENERATION / per_generation, "unit": "steps/s", "cores": os.cpu_count(),
           "kind": "port",
           "sample": ("numpy restatement: cache check/update/apply at [1,4608,3072] bf16 + FP8 linears of one "
-                     "double and one single block, extrapolated to 19+38 blocks and a 14-hit 28-step schedule; "
-                     "attention excluded"),
+                     "double and one single block, extrapolated to 19+38 blocks and a 28-step schedule with the "
+                     f"GPU run's hit count ({hits}); attention excluded"),
           "seconds": {"check": t_check, "update": t_update, "apply": t_apply, "double_block_linears": t_double,
                       "single_block_linears": t_single}}
 

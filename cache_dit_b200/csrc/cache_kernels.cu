@@ -41,8 +41,9 @@ constexpr int RL_UNROLL = 2;
 
 struct RelL1Scratch {
   unsigned int ticket;  // clusters finished in the current launch; self-resetting
-  unsigned int pad[3];
-  double partial[RL_MAX_CLUSTERS][2];
+  unsigned int pad;
+  double sum[2];        // fp64 accumulators of the two sums; self-resetting
+  double reserved;
 };
 
 template <class A, int U, bool HAS_BASE, bool HAS_PREV, bool WRITE_RES>
@@ -96,7 +97,6 @@ __global__ void __cluster_dims__(RL_CLUSTER, 1, 1) __launch_bounds__(RL_THREADS)
   float p = warp_sum(sp[0] + sp[1]);
   __shared__ float s_warp[RL_THREADS / 32][2];  // RL_THREADS / 32 <= 32 warps
   __shared__ double s_cta[RL_CLUSTER][2];  // only rank 0's copy is read; slot r is written by rank r
-  __shared__ int s_last;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if (lane == 0) {
     s_warp[warp][0] = d;
@@ -119,39 +119,33 @@ __global__ void __cluster_dims__(RL_CLUSTER, 1, 1) __launch_bounds__(RL_THREADS)
   cluster.sync();  // hardware cluster barrier: every CTA of the pair arrives exactly once
   if (rank != 0) return;
 
-  const unsigned nclusters = gridDim.x / RL_CLUSTER;
-  const unsigned cid = blockIdx.x / RL_CLUSTER;
+  // One thread per cluster adds the pair's sums to two fp64 accumulators (each addend is an fp32
+  // value, so the order of the additions changes the fp64 total by ~1e-16 relative at most, far
+  // below the final rounding to the storage dtype), then takes a ticket.  Whoever draws the last
+  // ticket publishes the means and leaves the scratch zeroed for the next launch.  The whole tail
+  // is two L2 round trips; nothing waits on anything.
   if (threadIdx.x == 0) {
+    const unsigned nclusters = gridDim.x / RL_CLUSTER;
     double td = 0.0, tp = 0.0;
 #pragma unroll
     for (int r = 0; r < RL_CLUSTER; ++r) {
       td += s_cta[r][0];
       tp += s_cta[r][1];
     }
-    scratch->partial[cid][0] = td;
-    scratch->partial[cid][1] = tp;
+    atomicAdd(&scratch->sum[0], td);
+    atomicAdd(&scratch->sum[1], tp);
     __threadfence();
-    unsigned t = atomicAdd(&scratch->ticket, 1u);
-    s_last = (t == nclusters - 1);
-  }
-  __syncthreads();
-  if (!s_last || warp != 0) return;
-  // Last cluster to finish folds the partials in a fixed order (run-to-run deterministic).
-  __threadfence();
-  double td = 0.0, tp = 0.0;
-  for (unsigned c = lane; c < nclusters; c += 32) {
-    td += __ldcg(&scratch->partial[c][0]);
-    tp += __ldcg(&scratch->partial[c][1]);
-  }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    td += __shfl_xor_sync(0xffffffffu, td, o);
-    tp += __shfl_xor_sync(0xffffffffu, tp, o);
-  }
-  if (lane == 0) {
-    means[0] = A::round1((float)(td / (double)n));
-    means[1] = A::round1((float)(tp / (double)n));
-    scratch->ticket = 0;  // ready for the next launch on this stream
+    const unsigned t = atomicAdd(&scratch->ticket, 1u);
+    if (t == nclusters - 1) {
+      __threadfence();
+      const double sd_all = __longlong_as_double(
+          (long long)atomicExch(reinterpret_cast<unsigned long long*>(&scratch->sum[0]), 0ull));
+      const double sp_all = __longlong_as_double(
+          (long long)atomicExch(reinterpret_cast<unsigned long long*>(&scratch->sum[1]), 0ull));
+      means[0] = A::round1((float)(sd_all / (double)n));
+      means[1] = A::round1((float)(sp_all / (double)n));
+      scratch->ticket = 0;
+    }
   }
 }
 
@@ -518,10 +512,9 @@ extern "C" int cdb_rel_l1_static(const void* cur, const void* base, const void* 
   if (rc != CDB_OK) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   // The array is shared by every call and keeps whatever the previous call left in it.  Only the
-  // arrival counter has to start at zero (the partial sums are overwritten before they are read);
-  // clear its 16-byte header on the caller's stream so a launch that was cut short earlier cannot
-  // poison this one.
-  CDB_CUDA_CHECK(cudaMemsetAsync(sc, 0, 16, st));
+  // arrival counter and the two accumulators have to start at zero; clear them on the caller's
+  // stream so a launch that was cut short earlier cannot poison this one.
+  CDB_CUDA_CHECK(cudaMemsetAsync(sc, 0, sizeof(RelL1Scratch), st));
   if (residual_out && !base && residual_out == cur) residual_out = nullptr;
   const bool vec = aligned16(cur) && aligned16(base) && aligned16(prev) && aligned16(residual_out);
   CDB_DISPATCH(launch_rel_l1, vec, cur, base, prev, residual_out, n, means, sc, st)

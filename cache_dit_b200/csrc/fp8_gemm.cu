@@ -42,7 +42,7 @@ constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;
 // Which kernel large-M problems use unless CDB_GEMM_KERNEL overrides it.
 #ifndef CDB_GEMM_DEFAULT_PAIR
-#define CDB_GEMM_DEFAULT_PAIR 0
+#define CDB_GEMM_DEFAULT_PAIR 1
 #endif
 
 struct __align__(8) GemmBarriers {
@@ -739,7 +739,7 @@ extern "C" int cdb_fp8_gemm_rowscaled(const void* a_q, const float* a_scale, con
   });
   CDB_CUDA_CHECK(attr_err);
   const int sms = sm_count();
-  const bool pair = mode == 2 || (mode == 0 && M > BM && CDB_GEMM_DEFAULT_PAIR);
+  const bool pair = mode == 2 || (mode == 0 && M > 512 && CDB_GEMM_DEFAULT_PAIR);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   CUtensorMap map_a, map_w;
   if (pair) {

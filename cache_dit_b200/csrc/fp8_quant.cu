@@ -1,18 +1,18 @@
 // Per-row dynamic FP8 (e4m3fn) quantization for sm_100a, optionally fused with the op that
 // produces the row (adaLN-modulated LayerNorm, tanh-GELU).
 //
-// One CTA owns one row at a time and keeps the whole row in registers between the amax pass
-// and the conversion pass, so every input byte is read from HBM exactly once and only the
-// 1-byte codes plus one float per row are written.  HBM-bound: 2 B read + 1 B written per
-// element.
+// A row is owned by 32, 64, 128 or 256 threads (one warp up to 3072 columns, so the common
+// case needs no block barrier) and stays in registers as packed bf16 between the amax pass and
+// the conversion pass: every input byte is read from HBM exactly once and only the 1-byte codes
+// plus one float per row are written.  HBM-bound: 2 B read + 1 B written per element.
 #include <cuda_fp8.h>
+
+#include <cstdlib>
 
 #include "common.cuh"
 
 namespace cdb {
 
-constexpr int Q_MAX_THREADS = 256;
-constexpr int Q_MAX_VPT = 8;            // 16-byte packets per thread -> cols <= 256*8*8 = 16384
 constexpr float E4M3_MAX = 448.0f;
 
 struct QuantFuse {
@@ -23,155 +23,223 @@ struct QuantFuse {
   float eps;
 };
 
-__device__ __forceinline__ float bf16r(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
-
-// Block-wide reductions over <= 8 warps; result broadcast to every thread.
-template <bool MAX>
-__device__ __forceinline__ float block_reduce(float v, float* smem /*[8]*/) {
-  v = MAX ? warp_max(v) : warp_sum(v);
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
-  __syncthreads();  // smem may still be read by the previous reduction
-  if (lane == 0) smem[warp] = v;
-  __syncthreads();
-  float r = lane < nwarp ? smem[lane] : (MAX ? 0.f : 0.f);
-  r = MAX ? warp_max(r) : warp_sum(r);
-  return r;
-}
-
+// tanh-GELU as x * sigmoid(2u), u = sqrt(2/pi) (x + 0.044715 x^3): one fast exponential and one
+// fast division instead of the ~25-instruction tanhf.  Their ~1e-6 relative error disappears in
+// the rounding of the result to bf16 except for a handful of values per million that sit on a
+// rounding boundary.
 __device__ __forceinline__ float gelu_tanh(float x) {
   const float k0 = 0.7978845608028654f, k1 = 0.044715f;
-  float inner = k0 * (x + k1 * x * x * x);
-  return 0.5f * x * (1.0f + tanhf(inner));
+  const float u = k0 * (x + k1 * x * x * x);
+  return __fdividef(x, 1.0f + __expf(-2.0f * u));
 }
 
-template <int VPT, int PREOP>
-__global__ void __launch_bounds__(Q_MAX_THREADS)
+// bf16x2 word <-> two floats (bf16 -> fp32 is a 16-bit shift: no conversion instruction)
+__device__ __forceinline__ float lo_f(uint32_t u) { return __uint_as_float(u << 16); }
+__device__ __forceinline__ float hi_f(uint32_t u) { return __uint_as_float(u & 0xffff0000u); }
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ __nv_bfloat162 as_bf2(uint32_t u) { return *reinterpret_cast<__nv_bfloat162*>(&u); }
+__device__ __forceinline__ uint32_t as_u32(__nv_bfloat162 v) { return *reinterpret_cast<uint32_t*>(&v); }
+
+constexpr int Q_CTA = 256;  // threads per CTA; a CTA works on Q_CTA / TPR rows at once
+
+// Reduction over the TPR threads that share a row: shuffles inside the warp, then (TPR > 32)
+// one shared-memory exchange between the row's warps.  `slot` alternates so that one
+// __syncthreads per reduction is enough.
+template <int TPR, bool MAX>
+__device__ __forceinline__ float row_reduce(float v, float (*s_red)[Q_CTA / 32], int& slot) {
+  v = MAX ? warp_max(v) : warp_sum(v);
+  if constexpr (TPR > 32) {
+    constexpr int WPR = TPR / 32;  // warps per row
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0) s_red[slot][warp] = v;
+    __syncthreads();
+    const int first = (warp / WPR) * WPR;
+    float r = s_red[slot][first];
+#pragma unroll
+    for (int w = 1; w < WPR; ++w) r = MAX ? fmaxf(r, s_red[slot][first + w]) : r + s_red[slot][first + w];
+    slot = (slot + 1) % 3;
+    return r;
+  } else {
+    return v;
+  }
+}
+
+// TPR threads per row (a warp for rows up to 3072 columns, so most rows need no barrier at all),
+// VPT 16-byte packets per thread kept as packed bf16 in registers between the amax pass and the
+// conversion pass.
+template <int TPR, int VPT, int PREOP>
+__global__ void __launch_bounds__(Q_CTA)
     fp8_quant_rows_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int cols, int64_t ld_x,
                           const QuantFuse f, uint8_t* __restrict__ q, float* __restrict__ scale) {
-  __shared__ float s_red[8];
+  constexpr int RPC = Q_CTA / TPR;  // rows per CTA and iteration
+  __shared__ float s_red[3][Q_CTA / 32];
+  int slot = 0;
   const int npack = cols >> 3;
-  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
-    const __nv_bfloat16* xr = x + row * ld_x;
-    float v[VPT][8];
-    bool live[VPT];
+  const int group = threadIdx.x / TPR, tig = threadIdx.x % TPR;
+  const int64_t iters = (rows + (int64_t)gridDim.x * RPC - 1) / ((int64_t)gridDim.x * RPC);
+  for (int64_t it = 0; it < iters; ++it) {  // same trip count for every thread: barriers stay aligned
+    const int64_t row = (it * gridDim.x + blockIdx.x) * RPC + group;
+    const bool valid = row < rows;
+    const __nv_bfloat16* xr = x + (valid ? row : 0) * ld_x;
+    uint4 pk[VPT];
 #pragma unroll
     for (int k = 0; k < VPT; ++k) {
-      const int p = threadIdx.x + k * blockDim.x;
-      live[k] = p < npack;
-      if (live[k]) {
-        Pack<__nv_bfloat16> pk = ld_stream(xr + (int64_t)p * 8);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v[k][i] = __bfloat162float(pk.v[i]);
-      } else {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v[k][i] = 0.f;
-      }
+      const int p = tig + k * TPR;
+      pk[k] = (valid && p < npack) ? __ldcs(reinterpret_cast<const uint4*>(xr) + p) : make_uint4(0, 0, 0, 0);
     }
 
     if constexpr (PREOP == CDB_PRE_LAYERNORM_MOD) {
-      // LayerNorm statistics in fp32 from registers (two-pass), result rounded to bf16, then
-      // y = round(round(norm * round(1 + scale)) + shift) like the eager bf16 modulation.
+      // LayerNorm statistics in fp32 from registers (two passes), the normalised value rounded to
+      // bf16, then y = round(round(norm * round(1 + scale)) + shift): the rounding points of the
+      // eager bf16 modulation, done with packed bf16 arithmetic.
       float s = 0.f;
 #pragma unroll
-      for (int k = 0; k < VPT; ++k)
+      for (int k = 0; k < VPT; ++k) {
+        const uint32_t w[4] = {pk[k].x, pk[k].y, pk[k].z, pk[k].w};
 #pragma unroll
-        for (int i = 0; i < 8; ++i) s += v[k][i];
-      const float mean = block_reduce<false>(s, s_red) / (float)cols;
+        for (int j = 0; j < 4; ++j) s += lo_f(w[j]) + hi_f(w[j]);
+      }
+      const float mean = row_reduce<TPR, false>(s, s_red, slot) / (float)cols;
       float ss = 0.f;
 #pragma unroll
-      for (int k = 0; k < VPT; ++k)
-        if (live[k])
+      for (int k = 0; k < VPT; ++k) {
+        if (tig + k * TPR < npack) {
+          const uint32_t w[4] = {pk[k].x, pk[k].y, pk[k].z, pk[k].w};
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            float d = v[k][i] - mean;
-            ss += d * d;
+          for (int j = 0; j < 4; ++j) {
+            const float a = lo_f(w[j]) - mean, b = hi_f(w[j]) - mean;
+            ss += a * a + b * b;
           }
-      const float var = block_reduce<false>(ss, s_red) / (float)cols;
+        }
+      }
+      const float var = row_reduce<TPR, false>(ss, s_red, slot) / (float)cols;
       const float rstd = rsqrtf(var + f.eps);
-      const int64_t b = row / f.rows_per_batch;
-      const __nv_bfloat16* sh = f.shift + b * f.ld_mod;
-      const __nv_bfloat16* sc = f.scale + b * f.ld_mod;
+      const int64_t bidx = (valid ? row : 0) / f.rows_per_batch;
+      const uint4* sh = reinterpret_cast<const uint4*>(f.shift + bidx * f.ld_mod);
+      const uint4* sc = reinterpret_cast<const uint4*>(f.scale + bidx * f.ld_mod);
+      const __nv_bfloat162 one = __float2bfloat162_rn(1.0f);
 #pragma unroll
       for (int k = 0; k < VPT; ++k) {
-        if (!live[k]) continue;
-        const int p = threadIdx.x + k * blockDim.x;
-        Pack<__nv_bfloat16> psh = *reinterpret_cast<const Pack<__nv_bfloat16>*>(sh + p * 8);
-        Pack<__nv_bfloat16> psc = *reinterpret_cast<const Pack<__nv_bfloat16>*>(sc + p * 8);
+        const int p = tig + k * TPR;
+        if (p < npack) {
+          const uint4 vsh = __ldg(sh + p), vsc = __ldg(sc + p);
+          uint32_t w[4] = {pk[k].x, pk[k].y, pk[k].z, pk[k].w};
+          const uint32_t wsh[4] = {vsh.x, vsh.y, vsh.z, vsh.w}, wsc[4] = {vsc.x, vsc.y, vsc.z, vsc.w};
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          float nrm = bf16r((v[k][i] - mean) * rstd);
-          float one_plus = bf16r(1.0f + __bfloat162float(psc.v[i]));
-          v[k][i] = bf16r(bf16r(nrm * one_plus) + __bfloat162float(psh.v[i]));
+          for (int j = 0; j < 4; ++j) {
+            const __nv_bfloat162 nrm = as_bf2(pack2((lo_f(w[j]) - mean) * rstd, (hi_f(w[j]) - mean) * rstd));
+            const __nv_bfloat162 one_plus = __hadd2_rn(one, as_bf2(wsc[j]));
+            w[j] = as_u32(__hadd2_rn(__hmul2_rn(nrm, one_plus), as_bf2(wsh[j])));
+          }
+          pk[k] = make_uint4(w[0], w[1], w[2], w[3]);
         }
       }
     } else if constexpr (PREOP == CDB_PRE_GELU_TANH) {
 #pragma unroll
-      for (int k = 0; k < VPT; ++k)
+      for (int k = 0; k < VPT; ++k) {
+        uint32_t w[4] = {pk[k].x, pk[k].y, pk[k].z, pk[k].w};
 #pragma unroll
-        for (int i = 0; i < 8; ++i) v[k][i] = bf16r(gelu_tanh(v[k][i]));
+        for (int j = 0; j < 4; ++j) w[j] = pack2(gelu_tanh(lo_f(w[j])), gelu_tanh(hi_f(w[j])));
+        pk[k] = make_uint4(w[0], w[1], w[2], w[3]);
+      }
     }
 
-    float amax = 0.f;
+    // row maximum of |y| with packed bf16 ops (exact: max and abs do not round)
+    __nv_bfloat162 m2 = __float2bfloat162_rn(0.f);
 #pragma unroll
-    for (int k = 0; k < VPT; ++k)
-#pragma unroll
-      for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[k][i]));
-    amax = block_reduce<true>(amax, s_red);
+    for (int k = 0; k < VPT; ++k) {
+      m2 = __hmax2(m2, __habs2(as_bf2(pk[k].x)));
+      m2 = __hmax2(m2, __habs2(as_bf2(pk[k].y)));
+      m2 = __hmax2(m2, __habs2(as_bf2(pk[k].z)));
+      m2 = __hmax2(m2, __habs2(as_bf2(pk[k].w)));
+    }
+    const uint32_t mu = as_u32(m2);
+    const float amax = row_reduce<TPR, true>(fmaxf(lo_f(mu), hi_f(mu)), s_red, slot);
     float sc = __fdiv_rn(amax, E4M3_MAX);
     if (sc == 0.f) sc = 1.f;  // all-zero row: keep zeros exact instead of 0/0
-    if (threadIdx.x == 0) scale[row] = sc;
+    if (valid && tig == 0) scale[row] = sc;
 
     // x / sc with one reciprocal per row: t = x * (1/sc) followed by one Newton correction
     // (r = x - t*sc exactly by FMA; t += r * (1/sc)) reproduces the correctly rounded quotient;
     // rows whose scale is so small that 1/sc would overflow take the plain division.
     const bool tiny = sc < 1e-30f;
     const float inv = tiny ? 0.f : __frcp_rn(sc);
-    auto quot = [&](float x) -> float {
-      if (tiny) return __fdiv_rn(x, sc);
-      float t = x * inv;
-      float r = fmaf(-t, sc, x);
+    auto quot = [&](float v) -> float {
+      if (tiny) return __fdiv_rn(v, sc);
+      float t = v * inv;
+      float r = fmaf(-t, sc, v);
       return fmaf(r, inv, t);
     };
-    uint8_t* qr = q + row * (int64_t)cols;
+    uint8_t* qr = q + (valid ? row : 0) * (int64_t)cols;
 #pragma unroll
     for (int k = 0; k < VPT; ++k) {
-      if (!live[k]) continue;
-      const int p = threadIdx.x + k * blockDim.x;
-      uint32_t w[2];
+      const int p = tig + k * TPR;
+      if (valid && p < npack) {
+        const uint32_t w[4] = {pk[k].x, pk[k].y, pk[k].z, pk[k].w};
+        uint32_t o[2];
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        float2 lo = make_float2(quot(v[k][h * 4 + 0]), quot(v[k][h * 4 + 1]));
-        float2 hi = make_float2(quot(v[k][h * 4 + 2]), quot(v[k][h * 4 + 3]));
-        uint32_t a = __nv_cvt_float2_to_fp8x2(lo, __NV_SATFINITE, __NV_E4M3);
-        uint32_t b = __nv_cvt_float2_to_fp8x2(hi, __NV_SATFINITE, __NV_E4M3);
-        w[h] = a | (b << 16);
+        for (int h = 0; h < 2; ++h) {
+          const uint32_t a = __nv_cvt_float2_to_fp8x2(make_float2(quot(lo_f(w[2 * h])), quot(hi_f(w[2 * h]))),
+                                                      __NV_SATFINITE, __NV_E4M3);
+          const uint32_t b = __nv_cvt_float2_to_fp8x2(
+              make_float2(quot(lo_f(w[2 * h + 1])), quot(hi_f(w[2 * h + 1]))), __NV_SATFINITE, __NV_E4M3);
+          o[h] = a | (b << 16);
+        }
+        __stcs(reinterpret_cast<uint2*>(qr + (int64_t)p * 8), make_uint2(o[0], o[1]));
       }
-      __stcs(reinterpret_cast<uint2*>(qr + (int64_t)p * 8), make_uint2(w[0], w[1]));
     }
   }
+}
+
+template <int TPR, int VPT, int PREOP>
+static void launch_quant_variant(const __nv_bfloat16* xp, int64_t rows, int cols, int64_t ld_x, const QuantFuse& f,
+                                 uint8_t* qp, float* scale, cudaStream_t st) {
+  auto kernel = fp8_quant_rows_kernel<TPR, VPT, PREOP>;
+  static int per_sm = 0;
+  if (per_sm == 0) {
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, Q_CTA, 0) != cudaSuccess || per_sm < 1)
+      per_sm = 1;
+  }
+  constexpr int RPC = Q_CTA / TPR;
+  const int64_t want = (rows + RPC - 1) / RPC;
+  const int64_t wave = (int64_t)per_sm * sm_count();
+  const unsigned grid = (unsigned)(want < wave ? want : wave);
+  kernel<<<grid, Q_CTA, 0, st>>>(xp, rows, cols, ld_x, f, qp, scale);
 }
 
 template <int PREOP>
 static int launch_quant(const void* x, int64_t rows, int64_t cols, int64_t ld_x, const QuantFuse& f,
                         void* q, float* scale, cudaStream_t st) {
   const int npack = (int)(cols / 8);
-  const int vpt = (npack + Q_MAX_THREADS - 1) / Q_MAX_THREADS;
-  if (vpt > Q_MAX_VPT) return CDB_ERR_UNSUPPORTED;
-  int threads = (npack + vpt - 1) / vpt;
-  threads = (threads + 31) / 32 * 32;
-  int64_t cap = (int64_t)sm_count() * (2048 / threads > 16 ? 16 : 2048 / threads);
-  const unsigned grid = (unsigned)(rows < cap ? rows : cap);
   const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
   uint8_t* qp = static_cast<uint8_t*>(q);
-#define CDB_Q(V)                                                                                   \
-  case V:                                                                                          \
-    fp8_quant_rows_kernel<V, PREOP><<<grid, threads, 0, st>>>(xp, rows, (int)cols, ld_x, f, qp, scale); \
-    break;
-  switch (vpt) {
-    CDB_Q(1) CDB_Q(2) CDB_Q(3) CDB_Q(4) CDB_Q(5) CDB_Q(6) CDB_Q(7) CDB_Q(8)
-    default: return CDB_ERR_UNSUPPORTED;
-  }
-#undef CDB_Q
+  const int c = (int)cols;
+  // Packets per thread: 6 for the plain and GELU variants (measured best on B200: 12 leaves too
+  // few rows in flight per SM, 1-4 add barriers without gaining bandwidth), 4 for the LayerNorm
+  // variant, which also holds the modulation vectors.  The smallest thread group that fits is
+  // used; CDB_QUANT_VMAX overrides the choice for tuning.
+  static const int vmax_env = [] { const char* e = getenv("CDB_QUANT_VMAX"); return e ? atoi(e) : 0; }();
+  const int vmax = vmax_env > 0 ? vmax_env : (PREOP == CDB_PRE_LAYERNORM_MOD ? 4 : 6);
+  int tpr = 32;
+  while (tpr < 256 && (npack + tpr - 1) / tpr > vmax) tpr *= 2;
+  const int v = (npack + tpr - 1) / tpr;
+  if (v > 12) return CDB_ERR_UNSUPPORTED;  // more than 24576 columns
+#define CDB_QV(TPR)                                                                              \
+  if (v <= 1) launch_quant_variant<TPR, 1, PREOP>(xp, rows, c, ld_x, f, qp, scale, st);         \
+  else if (v <= 2) launch_quant_variant<TPR, 2, PREOP>(xp, rows, c, ld_x, f, qp, scale, st);    \
+  else if (v <= 4) launch_quant_variant<TPR, 4, PREOP>(xp, rows, c, ld_x, f, qp, scale, st);    \
+  else if (v <= 6) launch_quant_variant<TPR, 6, PREOP>(xp, rows, c, ld_x, f, qp, scale, st);    \
+  else if (v <= 8) launch_quant_variant<TPR, 8, PREOP>(xp, rows, c, ld_x, f, qp, scale, st);    \
+  else if (v <= 10) launch_quant_variant<TPR, 10, PREOP>(xp, rows, c, ld_x, f, qp, scale, st);  \
+  else launch_quant_variant<TPR, 12, PREOP>(xp, rows, c, ld_x, f, qp, scale, st);
+  if (tpr == 32) { CDB_QV(32) }
+  else if (tpr == 64) { CDB_QV(64) }
+  else if (tpr == 128) { CDB_QV(128) }
+  else { CDB_QV(256) }
+#undef CDB_QV
   CDB_CUDA_CHECK(cudaGetLastError());
   return CDB_OK;
 }

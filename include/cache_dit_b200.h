@@ -77,7 +77,7 @@ CDB_API int cdb_rel_l1(const void* cur, const void* base, const void* prev, void
  *
  * Same arithmetic and outputs as cdb_rel_l1 with `prev` given (means[0], means[1], optional
  * residual_out); the reduction scratch is a fixed array inside the library's device image
- * (about 16 KB per GPU that loads the library, held until the process exits).
+ * (32 bytes per GPU that loads the library, held until the process exits).
  *   - n may not exceed CDB_REL_L1_STATIC_MAX_ELEMS; larger calls return CDB_ERR_TOO_LARGE and the
  *     reason is available from cdb_last_cuda_error().
  *   - The first call on each device looks up the array's device address (with that device
