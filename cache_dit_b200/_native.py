@@ -34,8 +34,14 @@ SIGNATURES = {
   "cdb_fp8_quant_rows": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
   "cdb_fp8_quant_rows_fused": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p,
                                        c_int64, c_int64, c_float, c_void_p, c_void_p, c_void_p]),
+  "cdb_fp8_quant_rows_concat_gelu": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64,
+                                             c_void_p, c_void_p, c_void_p]),
   "cdb_fp8_gemm_rowscaled": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                                      c_int64, c_int64, c_int64, c_void_p, c_void_p]),
+  "cdb_qk_norm_rope": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
+                               c_int64, c_int64, c_int, c_int, c_int, c_float, c_void_p]),
+  "cdb_gated_residual": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64,
+                                 c_int64, c_void_p]),
 }
 
 _lib = None
@@ -220,3 +226,55 @@ def fp8_gemm_rowscaled(a_q, a_scale, w_q, w_scale, bias, out):
 def gemm_device_status(device) -> int:
   """Non-zero if a bounded wait inside the GEMM kernel expired since the last reset (syncs)."""
   return int(gemm_status_word(device).item())
+
+
+def qk_norm_rope(x, norm_weight, cos, sin, out, pos_offset: int, heads: int, eps: float):
+  """Per-head RMSNorm + rotary embedding of x [batch, tokens, heads*head_dim] (rows may be a column
+  slice of a wider matrix), written into out[:, pos_offset:pos_offset+tokens] of the joint buffer
+  out [batch, total_tokens, heads, head_dim].  cos/sin are bf16 [total_tokens, head_dim]."""
+  _need_cuda(x, norm_weight, cos, sin, out)
+  _need_contig(norm_weight, cos, sin, out)
+  b, t, c = x.shape
+  d = c // heads
+  if x.dtype != torch.bfloat16 or x.stride(2) != 1 or (b > 1 and x.stride(0) != t * x.stride(1)):
+    raise RuntimeError("qk_norm_rope: x must be bf16 with unit column stride and uniformly strided rows")
+  if out.shape[0] != b or out.shape[2] != heads or out.shape[3] != d or cos.shape != (out.shape[1], d) \
+      or cos.dtype != torch.bfloat16 or sin.dtype != torch.bfloat16 or norm_weight.dtype != torch.bfloat16:
+    raise RuntimeError("qk_norm_rope: joint buffer / rotary table shapes do not match the projection")
+  st = lib().cdb_qk_norm_rope(_ptr(x), x.stride(1), _ptr(norm_weight), _ptr(cos), _ptr(sin), _ptr(out),
+                              heads * d, out.stride(0), b * t, t, int(pos_offset), heads, d, float(eps),
+                              _stream(x))
+  check(st, "cdb_qk_norm_rope")
+
+
+def gated_residual(x, gate, y):
+  """x + gate[:, None, :] * y for x [batch, tokens, cols] contiguous, gate [batch, cols] (rows may be a
+  column slice), y [batch, tokens, cols] (rows may be a column slice).  Returns a new tensor."""
+  _need_cuda(x, gate, y)
+  _need_contig(x)
+  b, t, c = x.shape
+  if x.dtype != torch.bfloat16 or y.dtype != x.dtype or gate.dtype != x.dtype or y.stride(2) != 1 \
+      or gate.stride(1) != 1 or (b > 1 and y.stride(0) != t * y.stride(1)) or y.shape != x.shape:
+    raise RuntimeError("gated_residual: bf16 operands with unit column stride and uniform row strides")
+  out = torch.empty_like(x)
+  st = lib().cdb_gated_residual(_ptr(x), _ptr(y), y.stride(1), _ptr(gate), gate.stride(0) if b > 1 else c,
+                                _ptr(out), b * t, t, c, _stream(x))
+  check(st, "cdb_gated_residual")
+  return out
+
+
+def fp8_quant_rows_concat_gelu(head2d, tail2d, q, scale):
+  """Quantize rows of [head | gelu_tanh(tail)] (bf16 matrices, rows may be strided) into q / scale."""
+  _need_cuda(head2d, tail2d, q, scale)
+  _need_contig(q, scale)
+  for t in (head2d, tail2d):
+    if t.dtype != torch.bfloat16 or t.dim() != 2 or t.stride(1) != 1:
+      raise RuntimeError("fp8_quant_rows_concat_gelu: bf16 matrices with unit column stride")
+  rows, c1 = head2d.shape
+  c2 = tail2d.shape[1]
+  if tail2d.shape[0] != rows or q.shape != (rows, c1 + c2):
+    raise RuntimeError("fp8_quant_rows_concat_gelu: row counts / output width do not match")
+  st = lib().cdb_fp8_quant_rows_concat_gelu(_ptr(head2d), c1, head2d.stride(0) if rows > 1 else max(c1, head2d.stride(0)),
+                                            _ptr(tail2d), c2, tail2d.stride(0) if rows > 1 else max(c2, tail2d.stride(0)),
+                                            rows, _ptr(q), _ptr(scale), _stream(head2d))
+  check(st, "cdb_fp8_quant_rows_concat_gelu")

@@ -21,6 +21,11 @@ struct QuantFuse {
   int64_t rows_per_batch;
   int64_t ld_mod;
   float eps;
+  // CDB_PRE_CONCAT_GELU: the row is [x row | gelu(tail row)]; the first `head_packs` 16-byte
+  // packets come from x, the rest from `tail` (row stride ld_tail)
+  const __nv_bfloat16* tail;
+  int64_t ld_tail;
+  int head_packs;
 };
 
 // tanh-GELU as x * sigmoid(2u), u = sqrt(2/pi) (x + 0.044715 x^3): one fast exponential and one
@@ -88,7 +93,14 @@ __global__ void __launch_bounds__(Q_CTA)
 #pragma unroll
     for (int k = 0; k < VPT; ++k) {
       const int p = tig + k * TPR;
-      pk[k] = (valid && p < npack) ? __ldcs(reinterpret_cast<const uint4*>(xr) + p) : make_uint4(0, 0, 0, 0);
+      if constexpr (PREOP == CDB_PRE_CONCAT_GELU) {
+        const uint4* src = p < f.head_packs
+                               ? reinterpret_cast<const uint4*>(xr) + p
+                               : reinterpret_cast<const uint4*>(f.tail + (valid ? row : 0) * f.ld_tail) + (p - f.head_packs);
+        pk[k] = (valid && p < npack) ? __ldcs(src) : make_uint4(0, 0, 0, 0);
+      } else {
+        pk[k] = (valid && p < npack) ? __ldcs(reinterpret_cast<const uint4*>(xr) + p) : make_uint4(0, 0, 0, 0);
+      }
     }
 
     if constexpr (PREOP == CDB_PRE_LAYERNORM_MOD) {
@@ -144,6 +156,16 @@ __global__ void __launch_bounds__(Q_CTA)
 #pragma unroll
         for (int j = 0; j < 4; ++j) w[j] = pack2(gelu_tanh(lo_f(w[j])), gelu_tanh(hi_f(w[j])));
         pk[k] = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    } else if constexpr (PREOP == CDB_PRE_CONCAT_GELU) {
+#pragma unroll
+      for (int k = 0; k < VPT; ++k) {
+        if (tig + k * TPR >= f.head_packs) {
+          uint32_t w[4] = {pk[k].x, pk[k].y, pk[k].z, pk[k].w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) w[j] = pack2(gelu_tanh(lo_f(w[j])), gelu_tanh(hi_f(w[j])));
+          pk[k] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
       }
     }
 
@@ -275,6 +297,24 @@ extern "C" int cdb_fp8_quant_rows_fused(const void* x, int64_t rows, int64_t col
     default:
       return CDB_ERR_BAD_ARGUMENT;
   }
+}
+
+extern "C" int cdb_fp8_quant_rows_concat_gelu(const void* head, int64_t head_cols, int64_t ld_head,
+                                              const void* tail, int64_t tail_cols, int64_t ld_tail, int64_t rows,
+                                              void* q, float* scale, void* stream) {
+  if (!head || !tail || !q || !scale || rows < 0 || head_cols <= 0 || tail_cols <= 0 || ld_head < head_cols ||
+      ld_tail < tail_cols)
+    return CDB_ERR_BAD_ARGUMENT;
+  if (rows == 0) return CDB_OK;
+  if (head_cols % 8 != 0 || tail_cols % 8 != 0 || ld_head % 8 != 0 || ld_tail % 8 != 0 || !aligned16(head) ||
+      !aligned16(tail) || (reinterpret_cast<uintptr_t>(q) & 7u))
+    return CDB_ERR_UNSUPPORTED;
+  QuantFuse f{};
+  f.tail = static_cast<const __nv_bfloat16*>(tail);
+  f.ld_tail = ld_tail;
+  f.head_packs = (int)(head_cols / 8);
+  return launch_quant<CDB_PRE_CONCAT_GELU>(head, rows, head_cols + tail_cols, ld_head, f, q, scale,
+                                           static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int cdb_fp8_quant_rows(const void* x, int64_t rows, int64_t cols, int64_t ld_x, void* q,

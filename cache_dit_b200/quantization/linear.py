@@ -88,3 +88,52 @@ def quantize_rows_fused(x: torch.Tensor, preop: int, mod_shift=None, mod_scale=N
     rows_per_batch = x2.shape[0] // batch
   _native.fp8_quant_rows(x2, a_q, a_scale, preop, mod_shift, mod_scale, rows_per_batch, eps)
   return a_q, a_scale, lead
+
+
+class FusedFloat8Linears(torch.nn.Module):
+  """Several FP8 linears that read the same activations, run as ONE GEMM over the concatenated
+  output rows (q/k/v, or q/k/v + MLP-in).  Per-row weight scales make this exactly the same
+  arithmetic as the separate products; the member layers keep working and share the storage
+  (their `weight_q` / `weight_scale` / `bias` become views into the fused tensors)."""
+
+  def __init__(self, linears):
+    super().__init__()
+    assert len({l.in_features for l in linears}) == 1
+    self.in_features = linears[0].in_features
+    self.splits = [l.out_features for l in linears]
+    self.out_features = sum(self.splits)
+    w = torch.cat([l.weight_q.view(torch.uint8) for l in linears], dim=0).view(torch.float8_e4m3fn)
+    s = torch.cat([l.weight_scale for l in linears], dim=0)
+    has_bias = [l.bias is not None for l in linears]
+    b = None
+    if any(has_bias):
+      b = torch.cat([l.bias if l.bias is not None else
+                     torch.zeros(l.out_features, dtype=torch.bfloat16, device=w.device) for l in linears])
+    self.register_buffer("weight_q", w)
+    self.register_buffer("weight_scale", s)
+    self.register_buffer("bias", b)
+    start = 0
+    for l, n, hb in zip(linears, self.splits, has_bias):
+      l.weight_q = w[start:start + n]
+      l.weight_scale = s[start:start + n]
+      if hb:
+        l.bias = b[start:start + n]
+      start += n
+
+  def forward_quantized(self, a_q: torch.Tensor, a_scale: torch.Tensor, lead_shape):
+    out = torch.empty((a_q.shape[0], self.out_features), dtype=torch.bfloat16, device=a_q.device)
+    _native.fp8_gemm_rowscaled(a_q, a_scale, self.weight_q, self.weight_scale, self.bias, out)
+    out = out.view(*lead_shape, self.out_features)
+    return out.split(self.splits, dim=-1)
+
+
+def fused_group(linears) -> FusedFloat8Linears:
+  """The fused module of a group of FP8 linears, built on first use and cached on the first member."""
+  head = linears[0]
+  key = tuple(id(l) for l in linears)
+  cache = head.__dict__.setdefault("_fused_groups", {})
+  fused = cache.get(key)
+  if fused is None:
+    fused = FusedFloat8Linears(list(linears))
+    cache[key] = fused
+  return fused

@@ -19,8 +19,9 @@ from torch import nn
 
 from ..caching.block_adapters import BlockAdapter, BlockAdapterRegister
 from ..caching.forward_pattern import ForwardPattern
-from .layers import (RMSNorm, TimestepMLP, UlyssesGroup, apply_rope, attention, gelu_linear, norm_modulate,
-                     norm_modulate_linears, rope_frequencies, timestep_embedding)
+from .layers import (RMSNorm, TimestepMLP, UlyssesGroup, attention, concat_gelu_linear, gated_add, gelu_linear,
+                     joint_qk_norm_rope, norm_modulate, norm_modulate_linears, rope_frequencies, rope_tables,
+                     timestep_embedding)
 
 
 class AdaLayerNormZero(nn.Module):
@@ -86,18 +87,17 @@ class FluxTransformerBlock(nn.Module):
     q, k, v = norm_modulate_linears(hidden_states, shift, scale, (a.to_q, a.to_k, a.to_v))
     cq, ck, cv = norm_modulate_linears(encoder_hidden_states, c_shift, c_scale,
                                        (a.add_q_proj, a.add_k_proj, a.add_v_proj))
-    q, k, v = a.norm_q(a.heads_view(q)), a.norm_k(a.heads_view(k)), a.heads_view(v)
-    cq, ck, cv = a.norm_added_q(a.heads_view(cq)), a.norm_added_k(a.heads_view(ck)), a.heads_view(cv)
-    q, k, v = torch.cat([cq, q], dim=1), torch.cat([ck, k], dim=1), torch.cat([cv, v], dim=1)
-    q, k = apply_rope(q, image_rotary_emb), apply_rope(k, image_rotary_emb)
+    q = joint_qk_norm_rope(((cq, a.norm_added_q), (q, a.norm_q)), image_rotary_emb, a.heads)
+    k = joint_qk_norm_rope(((ck, a.norm_added_k), (k, a.norm_k)), image_rotary_emb, a.heads)
+    v = torch.cat([a.heads_view(cv), a.heads_view(v)], dim=1)
     o = attention(q, k, v, self.cp)
     n_txt = encoder_hidden_states.shape[1]
-    hidden_states = hidden_states + gate[:, None] * a.to_out(o[:, n_txt:])
-    encoder_hidden_states = encoder_hidden_states + c_gate[:, None] * a.to_add_out(o[:, :n_txt])
+    hidden_states = gated_add(hidden_states, gate, a.to_out(o[:, n_txt:]))
+    encoder_hidden_states = gated_add(encoder_hidden_states, c_gate, a.to_add_out(o[:, :n_txt]))
     (h, ) = norm_modulate_linears(hidden_states, shift_mlp, scale_mlp, (self.ff.proj_in, ))
-    hidden_states = hidden_states + gate_mlp[:, None] * gelu_linear(h, self.ff.proj_out)
+    hidden_states = gated_add(hidden_states, gate_mlp, gelu_linear(h, self.ff.proj_out))
     (c, ) = norm_modulate_linears(encoder_hidden_states, c_shift_mlp, c_scale_mlp, (self.ff_context.proj_in, ))
-    encoder_hidden_states = encoder_hidden_states + c_gate_mlp[:, None] * gelu_linear(c, self.ff_context.proj_out)
+    encoder_hidden_states = gated_add(encoder_hidden_states, c_gate_mlp, gelu_linear(c, self.ff_context.proj_out))
     return encoder_hidden_states, hidden_states
 
 
@@ -118,11 +118,11 @@ class FluxSingleTransformerBlock(nn.Module):
     x = torch.cat([encoder_hidden_states, hidden_states], dim=1)
     shift, scale, gate = self.norm(temb)
     q, k, v, mlp = norm_modulate_linears(x, shift, scale, (a.to_q, a.to_k, a.to_v, self.proj_mlp))
-    q, k, v = a.norm_q(a.heads_view(q)), a.norm_k(a.heads_view(k)), a.heads_view(v)
-    q, k = apply_rope(q, image_rotary_emb), apply_rope(k, image_rotary_emb)
-    o = attention(q, k, v, self.cp)
-    y = self.proj_out(torch.cat([o, F.gelu(mlp, approximate="tanh")], dim=-1))
-    x = x + gate[:, None] * y
+    q = joint_qk_norm_rope(((q, a.norm_q), ), image_rotary_emb, a.heads)
+    k = joint_qk_norm_rope(((k, a.norm_k), ), image_rotary_emb, a.heads)
+    o = attention(q, k, a.heads_view(v), self.cp)
+    y = concat_gelu_linear(o, mlp, self.proj_out)
+    x = gated_add(x, gate, y)
     return x[:, :n_txt], x[:, n_txt:]
 
 
@@ -188,7 +188,7 @@ class FluxTransformer2DModel(nn.Module):
       temb = temb + self.guidance_embedder(timestep_embedding(guidance * 1000.0, 256).to(dt))
     temb = temb + self.text_embedder(pooled_projections)
     encoder_hidden_states = self.context_embedder(encoder_hidden_states)
-    rope = rope_frequencies(torch.cat([txt_ids, img_ids], dim=0), self.axes_dims_rope)
+    rope = rope_tables(rope_frequencies(torch.cat([txt_ids, img_ids], dim=0), self.axes_dims_rope), dt)
     for block in self.transformer_blocks:
       encoder_hidden_states, hidden_states = block(hidden_states, encoder_hidden_states, temb, rope)
     for block in self.single_transformer_blocks:

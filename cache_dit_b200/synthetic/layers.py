@@ -16,7 +16,7 @@ import torch.nn.functional as F
 from torch import nn
 
 from .. import _native
-from ..quantization.linear import Float8RowwiseLinear, quantize_rows_fused
+from ..quantization.linear import Float8RowwiseLinear, fused_group, quantize_rows_fused
 
 
 def _all_fp8(linears: Sequence[nn.Module]) -> bool:
@@ -29,7 +29,9 @@ def norm_modulate_linears(x: torch.Tensor, shift: torch.Tensor, scale: torch.Ten
   if _all_fp8(linears) and x.is_cuda:
     # shift / scale are column slices of one modulation matrix: passed as strided views
     a_q, a_scale, lead = quantize_rows_fused(x, _native.PRE_LAYERNORM_MOD, shift, scale, eps)
-    return [l.forward_quantized(a_q, a_scale, lead) for l in linears]
+    if len(linears) > 1:  # one GEMM over the concatenated output rows
+      return list(fused_group(linears).forward_quantized(a_q, a_scale, lead))
+    return [linears[0].forward_quantized(a_q, a_scale, lead)]
   y = F.layer_norm(x, (x.shape[-1], ), eps=eps) * (1 + scale[:, None]) + shift[:, None]
   return [l(y) for l in linears]
 
@@ -44,6 +46,18 @@ def gelu_linear(x: torch.Tensor, linear: nn.Module) -> torch.Tensor:
     a_q, a_scale, lead = quantize_rows_fused(x, _native.PRE_GELU_TANH)
     return linear.forward_quantized(a_q, a_scale, lead)
   return linear(F.gelu(x, approximate="tanh"))
+
+
+def concat_gelu_linear(head: torch.Tensor, tail: torch.Tensor, linear: nn.Module) -> torch.Tensor:
+  """linear(cat([head, gelu_tanh(tail)], dim=-1)): the output projection of a parallel attention + MLP
+  block.  With an FP8 linear neither the activated MLP branch nor the concatenation is written."""
+  if isinstance(linear, Float8RowwiseLinear) and head.is_cuda:
+    h2, t2 = head.reshape(-1, head.shape[-1]), tail.reshape(-1, tail.shape[-1])
+    a_q = torch.empty((h2.shape[0], h2.shape[1] + t2.shape[1]), dtype=torch.float8_e4m3fn, device=head.device)
+    a_scale = torch.empty(h2.shape[0], dtype=torch.float32, device=head.device)
+    _native.fp8_quant_rows_concat_gelu(h2, t2, a_q, a_scale)
+    return linear.forward_quantized(a_q, a_scale, head.shape[:-1])
+  return linear(torch.cat([head, F.gelu(tail, approximate="tanh")], dim=-1))
 
 
 class RMSNorm(nn.Module):
@@ -93,6 +107,42 @@ def apply_rope(x: torch.Tensor, rope: Tuple[torch.Tensor, torch.Tensor]) -> torc
   x1, x2 = x.unflatten(-1, (-1, 2)).unbind(-1)
   rot = torch.stack([-x2, x1], dim=-1).flatten(-2)
   return x * cos + rot * sin
+
+
+def rope_tables(rope: Tuple[torch.Tensor, torch.Tensor], dtype) -> Tuple[torch.Tensor, torch.Tensor]:
+  """The (cos, sin) tables in the activation dtype, contiguous: cast once per forward, not per block."""
+  return rope[0].to(dtype).contiguous(), rope[1].to(dtype).contiguous()
+
+
+def _glue_kernels_apply(x: torch.Tensor) -> bool:
+  return x.is_cuda and x.dtype == torch.bfloat16
+
+
+def joint_qk_norm_rope(parts: Sequence[Tuple[torch.Tensor, "RMSNorm"]], rope, heads: int) -> torch.Tensor:
+  """RoPE(concat over tokens of per-head RMSNorm(part)) -> [B, S_total, H, D].
+
+  `parts` are the projections [B, T_i, H*D] in sequence order (text first), each with its norm.  On
+  the GPU this is one kernel per part writing straight into the joint buffer; elsewhere the eager ops."""
+  x0 = parts[0][0]
+  d = x0.shape[-1] // heads
+  total = sum(p.shape[1] for p, _ in parts)
+  if _glue_kernels_apply(x0) and d in (64, 128, 256) and rope[0].dtype == x0.dtype and rope[0].is_contiguous():
+    out = torch.empty(x0.shape[0], total, heads, d, device=x0.device, dtype=x0.dtype)
+    off = 0
+    for x, norm in parts:
+      _native.qk_norm_rope(x, norm.weight, rope[0], rope[1], out, off, heads, norm.eps)
+      off += x.shape[1]
+    return out
+  normed = [norm(x.unflatten(-1, (heads, d))) for x, norm in parts]
+  return apply_rope(normed[0] if len(normed) == 1 else torch.cat(normed, dim=1), rope)
+
+
+def gated_add(x: torch.Tensor, gate: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
+  """x + gate[:, None] * y  (x, y [B, S, C]; gate [B, C])."""
+  if _glue_kernels_apply(x) and x.is_contiguous() and x.shape[-1] % 8 == 0 and y.stride(-1) == 1 \
+      and y.stride(1) % 8 == 0 and gate.stride(-1) == 1 and gate.stride(0) % 8 == 0:
+    return _native.gated_residual(x, gate, y)
+  return x + gate[:, None] * y
 
 
 class UlyssesGroup:

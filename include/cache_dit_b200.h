@@ -136,10 +136,24 @@ CDB_API int cdb_fp8_quant_rows(const void* x, int64_t rows, int64_t cols, int64_
  *                          (adaLN-modulated LayerNorm without affine; b = row / rows_per_batch)
  *   CDB_PRE_GELU_TANH:     y = gelu_tanh(x)
  * Intermediate y is rounded to bf16 before quantization, as the unfused bf16 pipeline does. */
-enum cdb_preop { CDB_PRE_NONE = 0, CDB_PRE_LAYERNORM_MOD = 1, CDB_PRE_GELU_TANH = 2 };
+enum cdb_preop {
+  CDB_PRE_NONE = 0,
+  CDB_PRE_LAYERNORM_MOD = 1,
+  CDB_PRE_GELU_TANH = 2,
+  CDB_PRE_CONCAT_GELU = 3 /* internal to cdb_fp8_quant_rows_concat_gelu; rejected by ..._fused */
+};
 CDB_API int cdb_fp8_quant_rows_fused(const void* x, int64_t rows, int64_t cols, int64_t ld_x, int preop,
                              const void* mod_shift, const void* mod_scale, int64_t rows_per_batch,
                              int64_t ld_mod, float eps, void* q, float* scale, void* stream);
+
+/* Quantizes the rows of the concatenation [head | gelu_tanh(tail)] without building it: the input
+ * of a parallel attention + MLP block's output projection (attention output beside the activated
+ * MLP branch).  head [rows, head_cols] and tail [rows, tail_cols] are bf16 with their own row
+ * strides; q is [rows, head_cols + tail_cols] contiguous; one scale per whole row.
+ * Column counts and strides must be multiples of 8; at most 24576 columns in total. */
+CDB_API int cdb_fp8_quant_rows_concat_gelu(const void* head, int64_t head_cols, int64_t ld_head,
+                                   const void* tail, int64_t tail_cols, int64_t ld_tail,
+                                   int64_t rows, void* q, float* scale, void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * Row-scaled FP8 GEMM.  Replaces the torch._scaled_mm call at
@@ -155,6 +169,30 @@ CDB_API int cdb_fp8_gemm_rowscaled(const void* a_q, const float* a_scale, const 
                            const float* w_scale, const void* bias, void* out, int64_t M,
                            int64_t N, int64_t K, int64_t ld_out, int32_t* status_word,
                            void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Transformer-block glue between the FP8 linears.  No counterpart in the reference: there these
+ * are eager PyTorch ops inside the diffusers transformer blocks that cache-dit wraps.  They are
+ * here because, once the linears run in FP8, these elementwise passes dominate a computed step.
+ *
+ * cdb_qk_norm_rope: per-head RMSNorm (weight [head_dim]) of a projected q or k, then the rotary
+ * embedding, written straight into a joint [batch, total_tokens, heads, head_dim] buffer.
+ *   x    [tokens, heads*head_dim] bf16, row stride ld_x (may be a column slice of a wider GEMM output)
+ *   cos/sin tables [total_tokens, head_dim] bf16; row used = pos_offset + (token index in its batch)
+ *   out  row (b, pos) starts at out + b*out_batch_stride + pos*ld_out
+ *   y = bf16(x * rsqrt(mean(x^2) + eps) * w);  out = bf16(bf16(y*cos) + bf16(rot(y)*sin)),
+ *   rot of each pair (y0, y1) = (-y1, y0).   head_dim in {64, 128, 256}; strides % 8 == 0.
+ *
+ * cdb_gated_residual: out[r, :] = x[r, :] + gate[r / rows_per_batch, :] * y[r, :]   (bf16, the
+ * product rounded before the add).  x and out contiguous [rows, cols]; y row stride ld_y.
+ * ---------------------------------------------------------------------------------------- */
+CDB_API int cdb_qk_norm_rope(const void* x, int64_t ld_x, const void* norm_weight, const void* cos_table,
+                     const void* sin_table, void* out, int64_t ld_out, int64_t out_batch_stride,
+                     int64_t tokens, int64_t tokens_per_batch, int pos_offset, int heads,
+                     int head_dim, float eps, void* stream);
+CDB_API int cdb_gated_residual(const void* x, const void* y, int64_t ld_y, const void* gate,
+                       int64_t ld_gate, void* out, int64_t rows, int64_t rows_per_batch,
+                       int64_t cols, void* stream);
 
 #ifdef __cplusplus
 }
