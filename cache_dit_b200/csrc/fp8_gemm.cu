@@ -7,7 +7,9 @@
 //     elected thread, fp32 accumulators in tensor memory (TMEM);
 //   * two 256-column TMEM accumulators so the epilogue of tile i overlaps the main loop of tile i+1;
 //   * epilogue: tcgen05.ld (32 lanes x 32 columns per warp), per-row x per-column scale, optional
-//     bias, bf16 pack, 16-byte stores;
+//     bias, bf16 pack into a swizzled shared-memory staging block, TMA store (cp.async.bulk.tensor
+//     shared -> global) of 32 x 64 blocks: whole 128-byte lines leave the SM, instead of one
+//     16-byte piece per thread and row, which kept the L1 data path as busy as the operand loads;
 //   * persistent grid (one CTA per SM), static tile order with M fastest so the CTAs of a wave
 //     share weight tiles in L2.
 // Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
@@ -54,10 +56,19 @@ struct __align__(8) GemmBarriers {
   volatile int abort_flag;
 };
 
-// dynamic shared memory: [<=1023 B alignment slack][STAGES x (A tile | B tile)][col scale][bias][barriers]
+// Epilogue staging: per epilogue warp two blocks of 32 rows x 64 bf16 columns (128-byte rows,
+// 128-byte swizzle, what the output tensor map's box expects).
+constexpr int OUT_BOX_COLS = 64;
+constexpr int OUT_BOX_ROWS = 32;
+constexpr int OUT_BLOCK_BYTES = OUT_BOX_ROWS * OUT_BOX_COLS * 2;  // 4096
+constexpr int OUT_STAGING_BYTES = (EPI_THREADS / 32) * 2 * OUT_BLOCK_BYTES;
+
+// dynamic shared memory:
+// [<=1023 B alignment slack][STAGES x (A tile | B tile)][output staging][col scale f32][bias bf16][barriers]
 constexpr int SMEM_TILE_BYTES = STAGES * STAGE_BYTES;
-constexpr int SMEM_EXTRA_BYTES = BN * 4 * 2 + (int)sizeof(GemmBarriers);
+constexpr int SMEM_EXTRA_BYTES = OUT_STAGING_BYTES + BN * 4 + BN * 2 + (int)sizeof(GemmBarriers);
 constexpr int SMEM_TOTAL_BYTES = 1024 + SMEM_TILE_BYTES + SMEM_EXTRA_BYTES;
+static_assert(SMEM_TOTAL_BYTES <= 232448, "exceeds the 227 KB of shared memory a CTA can opt in to");
 
 // ---- PTX wrappers ------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -189,18 +200,81 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// TMA store of one staged block: shared (this CTA) -> global through the output tensor map.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map),
+               "r"(smem_u32(src)), "r"(c0), "r"(c1)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Wait until at most N of this thread's bulk groups still READ their shared-memory source.
+template <int N>
+__device__ __forceinline__ void bulk_wait_group_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void bulk_wait_group_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// One epilogue warp's share of a tile: 32 accumulator rows (TMEM lanes) x BN columns.  Per block of
+// 64 columns: two tcgen05.ld, scale + bias, bf16 pack, 16-byte shared stores at the 128-byte-swizzled
+// position (chunk ^ (row % 8)): conflict-free, then one TMA store.  The tensor map clips rows >= M
+// and columns >= N.  `blocks_done` counts this warp's stores so the two staging blocks alternate.
+__device__ __forceinline__ void epilogue_rows(const CUtensorMap* map_out, uint8_t* staging, uint32_t taddr, float rs,
+                                              const float* s_colscale, const __nv_bfloat16* s_bias, int row0,
+                                              int n0, int M, int N, int lane, uint32_t& blocks_done) {
+  if (row0 >= M) return;  // the whole 32-row slice is padding
+#pragma unroll 1
+  for (int cblk = 0; cblk < BN; cblk += OUT_BOX_COLS) {
+    if (n0 + cblk >= N) break;
+    uint32_t acc[2][32];
+    tmem_ld_32x32b_x32(taddr + cblk, acc[0]);
+    tmem_ld_32x32b_x32(taddr + cblk + 32, acc[1]);
+    uint8_t* block = staging + (blocks_done & 1u) * OUT_BLOCK_BYTES;
+    if (lane == 0) bulk_wait_group_read<1>();  // the store that used this block two blocks ago is done reading
+    __syncwarp();
+    tmem_ld_wait();
+    uint8_t* rowp = block + lane * (OUT_BOX_COLS * 2);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {  // 8 columns = one 16-byte chunk
+        const int cb = cblk + h * 32 + g * 8;
+        uint32_t w[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int c = cb + 2 * j;
+          const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(s_bias + c));
+          const float v0 = __uint_as_float(acc[h][g * 8 + 2 * j]) * rs * s_colscale[c] + b.x;
+          const float v1 = __uint_as_float(acc[h][g * 8 + 2 * j + 1]) * rs * s_colscale[c + 1] + b.y;
+          w[j] = pack_bf16x2(v0, v1);
+        }
+        const int chunk = (h * 4 + g) ^ (lane & 7);
+        *reinterpret_cast<uint4*>(rowp + chunk * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    }
+    fence_async_smem();  // make the generic-proxy writes visible to the bulk-copy engine
+    __syncwarp();
+    if (lane == 0) {
+      tma_store_2d(map_out, block, n0 + cblk, row0);
+      bulk_commit_group();
+    }
+    ++blocks_done;
+  }
+}
+
 // ---- kernel --------------------------------------------------------------------------------
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
     fp8_gemm_rowscaled_kernel(const __grid_constant__ CUtensorMap map_a,
-                              const __grid_constant__ CUtensorMap map_w, const float* __restrict__ sa,
-                              const float* __restrict__ sw, const __nv_bfloat16* __restrict__ bias,
-                              __nv_bfloat16* __restrict__ out, int M, int N, int K, int64_t ld_out,
-                              int32_t* status_word) {
+                              const __grid_constant__ CUtensorMap map_w,
+                              const __grid_constant__ CUtensorMap map_out, const float* __restrict__ sa,
+                              const float* __restrict__ sw, const __nv_bfloat16* __restrict__ bias, int M, int N,
+                              int K, int32_t* status_word) {
   extern __shared__ uint8_t smem_raw[];
   // 128-byte swizzle needs 1024-byte aligned tiles.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  float* s_colscale = reinterpret_cast<float*>(smem + SMEM_TILE_BYTES);
-  float* s_bias = s_colscale + BN;
+  uint8_t* s_staging = smem + SMEM_TILE_BYTES;  // 1024-byte aligned: the tile ring is a multiple of 1024
+  float* s_colscale = reinterpret_cast<float*>(s_staging + OUT_STAGING_BYTES);
+  __nv_bfloat16* s_bias = reinterpret_cast<__nv_bfloat16*>(s_colscale + BN);
   GemmBarriers* gb = reinterpret_cast<GemmBarriers*>(s_bias + BN);
 
   const int warp = threadIdx.x >> 5;
@@ -307,7 +381,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     // ---------------- epilogue (warps 2..5) ----------------
     const int quarter = warp & 3;            // TMEM lanes [32*quarter, 32*quarter + 32)
     const int et = threadIdx.x - EPI_WARP0 * 32;  // 0..127
-    uint32_t local_tile = 0;
+    uint32_t local_tile = 0, blocks_done = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
       const int m0 = (tile % m_tiles) * BM;
@@ -319,7 +393,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       for (int c = et; c < BN; c += EPI_THREADS) {
         const int col = n0 + c;
         s_colscale[c] = col < N ? __ldg(sw + col) : 0.f;
-        s_bias[c] = (bias != nullptr && col < N) ? __bfloat162float(bias[col]) : 0.f;
+        s_bias[c] = (bias != nullptr && col < N) ? bias[col] : __float2bfloat16(0.f);
       }
       ok = mbar_wait(&gb->acc_full[buf], use & 1u, gb, status_word, 4);
       // (2) one barrier publishes the staged scales AND makes the continue/abort decision uniform
@@ -330,35 +404,15 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 
       const int row = m0 + quarter * 32 + lane;
       const float rs = row < M ? __ldg(sa + row) : 0.f;
-      __nv_bfloat16* orow = out + (int64_t)row * ld_out + n0;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        uint32_t acc[32];
-        tmem_ld_32x32b_x32(taddr + c0, acc);
-        tmem_ld_wait();
-        if (row < M) {
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {  // 8 columns = one 16-byte store
-            const int cb = c0 + g * 8;
-            if (n0 + cb < N) {  // N % 8 == 0: a group is entirely inside or outside
-              uint32_t w[4];
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const int c = cb + 2 * j;
-                float v0 = __uint_as_float(acc[g * 8 + 2 * j]) * rs * s_colscale[c] + s_bias[c];
-                float v1 = __uint_as_float(acc[g * 8 + 2 * j + 1]) * rs * s_colscale[c + 1] + s_bias[c + 1];
-                w[j] = pack_bf16x2(v0, v1);
-              }
-              *reinterpret_cast<uint4*>(orow + cb) = make_uint4(w[0], w[1], w[2], w[3]);
-            }
-          }
-        }
-      }
+      epilogue_rows(&map_out, s_staging + quarter * 2 * OUT_BLOCK_BYTES, taddr, rs, s_colscale, s_bias,
+                    m0 + quarter * 32, n0, M, N, lane, blocks_done);
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&gb->acc_empty[buf]);
     }
+    if (lane == 0) bulk_wait_group_all();  // staged blocks are read and written out before the CTA retires
+    __syncwarp();
   }
 
   tcgen05_fence_before();
@@ -394,7 +448,9 @@ struct __align__(8) PairBarriers {
   volatile int abort_flag;
 };
 constexpr int P_SMEM_TILE_BYTES = P_STAGES * P_STAGE_BYTES;
-constexpr int P_SMEM_TOTAL_BYTES = 1024 + P_SMEM_TILE_BYTES + BN * 4 * 2 + (int)sizeof(PairBarriers);
+constexpr int P_SMEM_TOTAL_BYTES =
+    1024 + P_SMEM_TILE_BYTES + OUT_STAGING_BYTES + BN * 4 + BN * 2 + (int)sizeof(PairBarriers);
+static_assert(P_SMEM_TOTAL_BYTES <= 232448, "exceeds the 227 KB of shared memory a CTA can opt in to");
 constexpr uint32_t IDESC_E4M3_F32_M256 =
     (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(P_BM >> 4) << 24);
 
@@ -459,14 +515,15 @@ __device__ __forceinline__ bool pair_wait(uint64_t* bar, uint32_t parity, PairBa
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
     fp8_gemm_rowscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
-                                   const __grid_constant__ CUtensorMap map_w, const float* __restrict__ sa,
-                                   const float* __restrict__ sw, const __nv_bfloat16* __restrict__ bias,
-                                   __nv_bfloat16* __restrict__ out, int M, int N, int K, int64_t ld_out,
-                                   int32_t* status_word) {
+                                   const __grid_constant__ CUtensorMap map_w,
+                                   const __grid_constant__ CUtensorMap map_out, const float* __restrict__ sa,
+                                   const float* __restrict__ sw, const __nv_bfloat16* __restrict__ bias, int M,
+                                   int N, int K, int32_t* status_word) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  float* s_colscale = reinterpret_cast<float*>(smem + P_SMEM_TILE_BYTES);
-  float* s_bias = s_colscale + BN;
+  uint8_t* s_staging = smem + P_SMEM_TILE_BYTES;
+  float* s_colscale = reinterpret_cast<float*>(s_staging + OUT_STAGING_BYTES);
+  __nv_bfloat16* s_bias = reinterpret_cast<__nv_bfloat16*>(s_colscale + BN);
   PairBarriers* gb = reinterpret_cast<PairBarriers*>(s_bias + BN);
 
   const int warp = threadIdx.x >> 5;
@@ -582,7 +639,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
     // ---------------- epilogue (warps 2..5 of both CTAs): this CTA's 128 rows x 256 columns ----------------
     const int quarter = warp & 3;
     const int et = threadIdx.x - EPI_WARP0 * 32;
-    uint32_t local_tile = 0;
+    uint32_t local_tile = 0, blocks_done = 0;
     bool ok = true;
     for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs, ++local_tile) {
       const int m0 = (tile % m_tiles) * P_BM + (int)rank * 128;
@@ -593,7 +650,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
       for (int c = et; c < BN; c += EPI_THREADS) {
         const int col = n0 + c;
         s_colscale[c] = col < N ? __ldg(sw + col) : 0.f;
-        s_bias[c] = (bias != nullptr && col < N) ? __bfloat162float(bias[col]) : 0.f;
+        s_bias[c] = (bias != nullptr && col < N) ? bias[col] : __float2bfloat16(0.f);
       }
       ok = pair_wait(&gb->acc_full[buf], use & 1u, gb, status_word, 14);
       ok = epi_all(ok);
@@ -602,35 +659,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 
       const int row = m0 + quarter * 32 + lane;
       const float rs = row < M ? __ldg(sa + row) : 0.f;
-      __nv_bfloat16* orow = out + (int64_t)row * ld_out + n0;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        uint32_t acc[32];
-        tmem_ld_32x32b_x32(taddr + c0, acc);
-        tmem_ld_wait();
-        if (row < M) {
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            const int cb = c0 + g * 8;
-            if (n0 + cb < N) {
-              uint32_t w[4];
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const int c = cb + 2 * j;
-                float v0 = __uint_as_float(acc[g * 8 + 2 * j]) * rs * s_colscale[c] + s_bias[c];
-                float v1 = __uint_as_float(acc[g * 8 + 2 * j + 1]) * rs * s_colscale[c + 1] + s_bias[c + 1];
-                w[j] = pack_bf16x2(v0, v1);
-              }
-              *reinterpret_cast<uint4*>(orow + cb) = make_uint4(w[0], w[1], w[2], w[3]);
-            }
-          }
-        }
-      }
+      epilogue_rows(&map_out, s_staging + quarter * 2 * OUT_BLOCK_BYTES, taddr, rs, s_colscale, s_bias,
+                    m0 + quarter * 32, n0, M, N, lane, blocks_done);
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&gb->acc_empty[buf]), 0));
     }
+    if (lane == 0) bulk_wait_group_all();
+    __syncwarp();
   }
 
   tcgen05_fence_before();
@@ -662,40 +699,42 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// [rows, K] bytes, row-major; box = (128 bytes of K) x box_rows, 128-byte swizzle, zero fill.
-static bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t k, uint32_t box_rows) {
+// Row-major 2-D tensor map with the 128-byte swizzle.  Operands: [rows, K] bytes, box = 128 bytes
+// of K x box_rows, zero fill.  Output: [M, N] bf16 with a row pitch, box = 64 columns x 32 rows.
+static bool make_map(CUtensorMap* map, CUtensorMapDataType type, uint32_t elem_bytes, const void* base,
+                     uint64_t rows, uint64_t inner, uint64_t pitch_elems, uint32_t box_inner, uint32_t box_rows) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
-  cuuint64_t dims[2] = {k, rows};
-  cuuint64_t strides[1] = {k};
-  cuuint32_t box[2] = {(cuuint32_t)BK, box_rows};
+  cuuint64_t dims[2] = {inner, rows};
+  cuuint64_t strides[1] = {pitch_elems * elem_bytes};
+  cuuint32_t box[2] = {box_inner, box_rows};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r = fn(map, type, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }
 
 struct MapKey {
   const void* p;
-  uint64_t rows, k;
-  uint32_t box_rows;
+  uint64_t rows, inner, pitch;
+  uint32_t box_rows, elem_bytes;
   bool operator==(const MapKey& o) const {
-    return p == o.p && rows == o.rows && k == o.k && box_rows == o.box_rows;
+    return p == o.p && rows == o.rows && inner == o.inner && pitch == o.pitch && box_rows == o.box_rows &&
+           elem_bytes == o.elem_bytes;
   }
 };
 struct MapKeyHash {
   size_t operator()(const MapKey& k) const {
-    return std::hash<const void*>()(k.p) ^ (k.rows * 0x9E3779B97F4A7C15ull) ^ (k.k << 20) ^ k.box_rows;
+    return std::hash<const void*>()(k.p) ^ (k.rows * 0x9E3779B97F4A7C15ull) ^ (k.inner << 20) ^ (k.pitch << 40) ^
+           k.box_rows ^ ((uint64_t)k.elem_bytes << 12);
   }
 };
 
 // Encoding a tensor map costs a few microseconds of host time; weights keep their address for the
 // life of the model, activations come from a caching allocator, so a small cache hits almost always.
-static bool cached_map(CUtensorMap* out, const void* base, uint64_t rows, uint64_t k, uint32_t box_rows) {
+static bool cached_map(CUtensorMap* out, const MapKey& key) {
   static std::mutex mu;
   static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
-  MapKey key{base, rows, k, box_rows};
   std::lock_guard<std::mutex> lock(mu);
   auto it = cache.find(key);
   if (it != cache.end()) {
@@ -703,11 +742,22 @@ static bool cached_map(CUtensorMap* out, const void* base, uint64_t rows, uint64
     return true;
   }
   CUtensorMap m;
-  if (!make_map(&m, base, rows, k, box_rows)) return false;
+  const bool ok = key.elem_bytes == 1
+                      ? make_map(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, key.p, key.rows, key.inner, key.pitch, BK,
+                                 key.box_rows)
+                      : make_map(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, key.p, key.rows, key.inner, key.pitch,
+                                 OUT_BOX_COLS, key.box_rows);
+  if (!ok) return false;
   if (cache.size() > 4096) cache.clear();
   cache.emplace(key, m);
   *out = m;
   return true;
+}
+static bool operand_map(CUtensorMap* out, const void* base, uint64_t rows, uint64_t k, uint32_t box_rows) {
+  return cached_map(out, MapKey{base, rows, k, k, box_rows, 1});
+}
+static bool output_map(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch) {
+  return cached_map(out, MapKey{base, rows, cols, pitch, (uint32_t)OUT_BOX_ROWS, 2});
 }
 
 }  // namespace cdb
@@ -741,29 +791,33 @@ extern "C" int cdb_fp8_gemm_rowscaled(const void* a_q, const float* a_scale, con
   const int sms = sm_count();
   const bool pair = mode == 2 || (mode == 0 && M > 512 && CDB_GEMM_DEFAULT_PAIR);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  CUtensorMap map_a, map_w;
+  CUtensorMap map_a, map_w, map_out;
+  if (!output_map(&map_out, out, (uint64_t)M, (uint64_t)N, (uint64_t)ld_out)) {
+    set_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled");
+    return CDB_ERR_CUDA;
+  }
   if (pair) {
-    if (!cached_map(&map_a, a_q, (uint64_t)M, (uint64_t)K, 128) ||
-        !cached_map(&map_w, w_q, (uint64_t)N, (uint64_t)K, 128)) {
+    if (!operand_map(&map_a, a_q, (uint64_t)M, (uint64_t)K, 128) ||
+        !operand_map(&map_w, w_q, (uint64_t)N, (uint64_t)K, 128)) {
       set_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled");
       return CDB_ERR_CUDA;
     }
     const int64_t tiles = ((M + P_BM - 1) / P_BM) * ((N + BN - 1) / BN);
     const int64_t pairs = tiles < sms / 2 ? tiles : sms / 2;
     fp8_gemm_rowscaled_pair_kernel<<<(unsigned)(2 * pairs), GEMM_THREADS, P_SMEM_TOTAL_BYTES, st>>>(
-        map_a, map_w, a_scale, w_scale, static_cast<const __nv_bfloat16*>(bias),
-        static_cast<__nv_bfloat16*>(out), (int)M, (int)N, (int)K, ld_out, status_word);
+        map_a, map_w, map_out, a_scale, w_scale, static_cast<const __nv_bfloat16*>(bias), (int)M, (int)N, (int)K,
+        status_word);
   } else {
-    if (!cached_map(&map_a, a_q, (uint64_t)M, (uint64_t)K, BM) ||
-        !cached_map(&map_w, w_q, (uint64_t)N, (uint64_t)K, BN)) {
+    if (!operand_map(&map_a, a_q, (uint64_t)M, (uint64_t)K, BM) ||
+        !operand_map(&map_w, w_q, (uint64_t)N, (uint64_t)K, BN)) {
       set_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled");
       return CDB_ERR_CUDA;
     }
     const int64_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
     const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
     fp8_gemm_rowscaled_kernel<<<grid, GEMM_THREADS, SMEM_TOTAL_BYTES, st>>>(
-        map_a, map_w, a_scale, w_scale, static_cast<const __nv_bfloat16*>(bias),
-        static_cast<__nv_bfloat16*>(out), (int)M, (int)N, (int)K, ld_out, status_word);
+        map_a, map_w, map_out, a_scale, w_scale, static_cast<const __nv_bfloat16*>(bias), (int)M, (int)N, (int)K,
+        status_word);
   }
   CDB_CUDA_CHECK(cudaGetLastError());
   return CDB_OK;
