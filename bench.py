@@ -194,7 +194,21 @@ def fp8_library_peak(device):
       torch.cuda.synchronize()
       if i >= 3:
         best = min(best, s.elapsed_time(e))
-    return 2.0 * n**3 / (best * 1e-3) / 1e12
+    burst = 2.0 * n**3 / (best * 1e-3) / 1e12
+    # sustained: the same product back to back for ~2 s (power-capped clocks, like a GEMM inside a long step)
+    reps, elapsed, done = 50, 0.0, 0
+    while elapsed < 2000.0 and done < 5000:
+      s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+      s.record()
+      for _ in range(reps):
+        torch._scaled_mm(a, b, scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+      e.record()
+      torch.cuda.synchronize()
+      last = s.elapsed_time(e)
+      elapsed += last
+      done += reps
+    sustained = 2.0 * n**3 * reps / (last * 1e-3) / 1e12  # the last chunk, after the clocks settled
+    return burst, sustained
   except Exception:
     return None
 
@@ -269,6 +283,8 @@ def run_ours(args):
                   calibrator_config=cd.TaylorSeerCalibratorConfig(taylorseer_order=1),
                   parallelism_config=cd.ParallelismConfig(ulysses_size=world) if world > 1 else None,
                   quantize_config=cd.QuantizeConfig(quant_type="float8_per_row"))
+  if not args.no_graphs:
+    cd.enable_cuda_graphs(model)  # block segments between the cache decisions replay as CUDA graphs
   host = host_inputs()
   dev_inputs = {k: v.to(device) for k, v in host.items()}
   stepper = Stepper(cd, model, dev_inputs)
@@ -305,12 +321,18 @@ def run_ours(args):
   h2d = sum(v.numel() * v.element_size() for v in host.values())
   d2h = host_out.numel() * host_out.element_size()
   # -------- instrumented repeat of region 1: per-launch durations of the dominant kernel (FP8 GEMM)
+  # (eager launches: events cannot bracket single kernels inside a graph replay)
+  runners = cd.graph_runners(model)
+  for r in runners:
+    r.enabled = False
   stepper.i = STEPS_PER_GENERATION
   nat.gemm_timer = []
   for _ in range(min(args.steps, STEPS_PER_GENERATION)):
     stepper.step()
   torch.cuda.synchronize()
   records, nat.gemm_timer = nat.gemm_timer, None
+  for r in runners:
+    r.enabled = True
   gemm_ms = sum(s.elapsed_time(e) for s, e, _ in records)
   gemm_flops = sum(f for _, _, f in records)
 
@@ -325,21 +347,25 @@ def run_ours(args):
   peaks, peak_kind = load_measured_peaks()
   fp8_lib = fp8_library_peak(device) if not args.skip_extras else None
   achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
-  peak = (fp8_lib * 1000.0 / 1000.0) if fp8_lib else FP8_NOMINAL_TFLOPS
+  # the GEMM launches are timed inside long steps under the power cap: the sustained library figure
+  # is the like-for-like denominator, the burst figure is reported beside it
+  peak = fp8_lib[1] if fp8_lib else FP8_NOMINAL_TFLOPS
   line = {
     "metric": METRIC, "value": args.steps / (ms * 1e-3), "unit": "steps/s", "n_gpus": world, "steps": args.steps,
     "warmup": warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
     "vs_baseline": None, "dtype": "bf16 activations, fp8 e4m3 linears (fp32 accumulate)", "data": "synthetic",
     "config": {"workload": WORKLOAD, "parallelism": f"ulysses{world}" if world > 1 else "single",
                "l2_policy": "inputs larger than L2: ~12 GB of FP8 weights streamed per computed step",
-               "cached_steps_per_generation": masks[:2]},
+               "cuda_graphs": (not args.no_graphs), "cached_steps_per_generation": masks[:2]},
     "e2e": {"value": args.steps / (ms_e2e * 1e-3), "unit": "steps/s", "h2d_bytes_per_step": h2d,
             "d2h_bytes_per_step": d2h},
     "gpu_launches": launches, "clocks": clocks,
     "roofline": {"bound": "tensor", "kernel": "fp8_gemm_rowscaled_kernel", "achieved": round(achieved, 1),
                  "peak": round(peak, 1), "unit": "TFLOP/s", "frac": round(achieved / peak, 3),
-                 "peak_source": "torch._scaled_mm e4m3 8192^3 per-tensor, best of 10, measured in this run"
-                 if fp8_lib else "nominal dense FP8",
+                 "peak_source": "torch._scaled_mm e4m3 8192^3 per-tensor back to back for 2 s (sustained), "
+                 "measured in this run" if fp8_lib else "nominal dense FP8",
+                 "peak_burst": round(fp8_lib[0], 1) if fp8_lib else None,
+                 "frac_of_burst": round(achieved / fp8_lib[0], 3) if fp8_lib else None,
                  "frac_of_nominal_4500": round(achieved / FP8_NOMINAL_TFLOPS, 3), "launches": len(records),
                  "timing": "CUDA events around every GEMM launch in an instrumented repeat of the timed steps",
                  "traffic": None},
@@ -433,6 +459,7 @@ def main():
   ap.add_argument("--steps", type=int, default=2 * STEPS_PER_GENERATION)
   ap.add_argument("--warmup", type=int, default=STEPS_PER_GENERATION)
   ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+  ap.add_argument("--no-graphs", action="store_true", help="issue every kernel from Python instead of replaying CUDA graphs")
   ap.add_argument("--profile-timed-region", action="store_true",
                   help="bracket the first timed region with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
   ap.add_argument("--skip-extras", action="store_true",

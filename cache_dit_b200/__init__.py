@@ -10,7 +10,8 @@
 The names exported here are those of the reference package (src/cache_dit/__init__.py:19-82) that
 belong to the DBCache / TaylorSeer / FP8-linear / Ulysses path.
 """
-from .caching import (BasicCacheConfig, BlockAdapter, BlockAdapterRegister, CachedAdapter, CachedBlocks,
+from .caching import (BasicCacheConfig, BlockAdapter, BlockGraphRunner, disable_cuda_graphs, enable_cuda_graphs,
+                      graph_runners, BlockAdapterRegister, CachedAdapter, CachedBlocks,
                       CachedContext, CachedContextManager, CacheType, Calibrator, CalibratorBase,
                       CalibratorConfig, ContextNotExistError, DBCacheConfig, ExtraCacheConfig,
                       FakeDiffusionPipeline, ForwardPattern, LazyResidual, ParamsModifier, TaylorSeerCalibrator,

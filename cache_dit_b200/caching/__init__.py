@@ -1,4 +1,5 @@
 from .block_adapters import (BlockAdapter, BlockAdapterRegister, FakeDiffusionPipeline, ParamsModifier)
+from .block_graphs import BlockGraphRunner, disable_cuda_graphs, enable_cuda_graphs, graph_runners
 from .cache_adapter import CachedAdapter
 from .cache_blocks import CachedBlocks, UnifiedBlocks, apply_stats, remove_stats
 from .cache_config import BasicCacheConfig, DBCacheConfig, ExtraCacheConfig

@@ -210,6 +210,8 @@ class CachedAdapter:
     swaps += [(name, empty) for name in dummy_blocks_names]
     transformer._context_manager = manager
     transformer._context_names = list(unique_blocks_name)
+    # kept reachable so that tools working on the runners (CUDA-graph capture) can find them
+    transformer.__dict__["_unified_blocks"] = unified_blocks
 
     def new_forward(*args, **kwargs):
       modules = transformer._modules
@@ -310,7 +312,7 @@ class CachedAdapter:
       if isinstance(manager, CachedContextManager):
         manager.clear_contexts()
       for attr in ("_is_cached", "_context_manager", "_context_names", "_forward_pattern", "_has_separate_cfg",
-                   "_context_kwargs"):
+                   "_context_kwargs", "_unified_blocks"):
         if attr in vars(transformer):
           delattr(transformer, attr)
       remove_stats(transformer)

@@ -54,6 +54,8 @@ class CachedBlocks(torch.nn.Module):
     self.cache_context = cache_context
     self.context_manager = context_manager
     self.cache_type = cache_type
+    # optional CUDA-graph replay of the block segments (block_graphs.enable_cuda_graphs)
+    self.graph_runner = None
     self._check_forward_pattern()
 
   # ---------------------------------------------------------------- checks
@@ -109,6 +111,14 @@ class CachedBlocks(torch.nn.Module):
     return (a, b) if self.forward_pattern.Return_H_First else (b, a)
 
   def _run(self, blocks, hidden, encoder, args, kwargs):
+    runner = self.graph_runner
+    if runner is None or len(blocks) == 0:
+      return self._run_eager(blocks, hidden, encoder, args, kwargs)
+    tag = (id(blocks[0]), len(blocks))
+    return runner.run(tag, lambda h, e, a, k: self._run_eager(blocks, h, e, a, k),
+                      (hidden, encoder, tuple(args), dict(kwargs)))
+
+  def _run_eager(self, blocks, hidden, encoder, args, kwargs):
     h_only = self.forward_pattern.Forward_H_only
     if h_only:
       encoder = None
