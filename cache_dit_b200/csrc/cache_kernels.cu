@@ -39,11 +39,14 @@ constexpr int RL_CLUSTER = 2;        // CTA pair: always fits (SMs come in TPC p
 constexpr int RL_MAX_CLUSTERS = 1024;
 constexpr int RL_UNROLL = 2;
 
+constexpr int RL_SLOTS = 16;         // accumulator slots, one 128-byte line each
 struct RelL1Scratch {
   unsigned int ticket;  // clusters finished in the current launch; self-resetting
-  unsigned int pad;
-  double sum[2];        // fp64 accumulators of the two sums; self-resetting
-  double reserved;
+  unsigned int pad[31];
+  // fp64 accumulators of the two sums, self-resetting.  Clusters add into slot (cluster id % 16):
+  // all clusters finish within a microsecond of each other, and ~1800 atomics on one line would
+  // queue in a single L2 slice for longer than the last CTA's stream takes.
+  struct __align__(128) Slot { double sum[2]; double pad[14]; } slot[RL_SLOTS];
 };
 
 template <class A, int U, bool HAS_BASE, bool HAS_PREV, bool WRITE_RES>
@@ -119,33 +122,47 @@ __global__ void __cluster_dims__(RL_CLUSTER, 1, 1) __launch_bounds__(RL_THREADS)
   cluster.sync();  // hardware cluster barrier: every CTA of the pair arrives exactly once
   if (rank != 0) return;
 
-  // One thread per cluster adds the pair's sums to two fp64 accumulators (each addend is an fp32
+  // One thread per cluster adds the pair's sums to its slot's two fp64 accumulators (each addend is an fp32
   // value, so the order of the additions changes the fp64 total by ~1e-16 relative at most, far
   // below the final rounding to the storage dtype), then takes a ticket.  Whoever draws the last
   // ticket publishes the means and leaves the scratch zeroed for the next launch.  The whole tail
   // is two L2 round trips; nothing waits on anything.
-  if (threadIdx.x == 0) {
-    const unsigned nclusters = gridDim.x / RL_CLUSTER;
+  if (warp != 0) return;
+  const unsigned nclusters = gridDim.x / RL_CLUSTER;
+  unsigned t = 0;
+  if (lane == 0) {
     double td = 0.0, tp = 0.0;
 #pragma unroll
     for (int r = 0; r < RL_CLUSTER; ++r) {
       td += s_cta[r][0];
       tp += s_cta[r][1];
     }
-    atomicAdd(&scratch->sum[0], td);
-    atomicAdd(&scratch->sum[1], tp);
+    RelL1Scratch::Slot* mine = &scratch->slot[(blockIdx.x / RL_CLUSTER) % RL_SLOTS];
+    atomicAdd(&mine->sum[0], td);
+    atomicAdd(&mine->sum[1], tp);
     __threadfence();
-    const unsigned t = atomicAdd(&scratch->ticket, 1u);
-    if (t == nclusters - 1) {
-      __threadfence();
-      const double sd_all = __longlong_as_double(
-          (long long)atomicExch(reinterpret_cast<unsigned long long*>(&scratch->sum[0]), 0ull));
-      const double sp_all = __longlong_as_double(
-          (long long)atomicExch(reinterpret_cast<unsigned long long*>(&scratch->sum[1]), 0ull));
-      means[0] = A::round1((float)(sd_all / (double)n));
-      means[1] = A::round1((float)(sp_all / (double)n));
-      scratch->ticket = 0;
-    }
+    t = atomicAdd(&scratch->ticket, 1u);
+  }
+  t = __shfl_sync(0xffffffffu, t, 0);
+  if (t != nclusters - 1) return;
+  // last cluster: lanes 0..15 fetch-and-clear one slot each, fp64 butterfly, lane 0 publishes
+  __threadfence();
+  double sd_all = 0.0, sp_all = 0.0;
+  if (lane < RL_SLOTS) {
+    sd_all = __longlong_as_double(
+        (long long)atomicExch(reinterpret_cast<unsigned long long*>(&scratch->slot[lane].sum[0]), 0ull));
+    sp_all = __longlong_as_double(
+        (long long)atomicExch(reinterpret_cast<unsigned long long*>(&scratch->slot[lane].sum[1]), 0ull));
+  }
+#pragma unroll
+  for (int o = RL_SLOTS / 2; o > 0; o >>= 1) {
+    sd_all += __shfl_xor_sync(0xffffffffu, sd_all, o);
+    sp_all += __shfl_xor_sync(0xffffffffu, sp_all, o);
+  }
+  if (lane == 0) {
+    means[0] = A::round1((float)(sd_all / (double)n));
+    means[1] = A::round1((float)(sp_all / (double)n));
+    scratch->ticket = 0;
   }
 }
 
@@ -407,6 +424,7 @@ extern "C" int cdb_rel_l1(const void* cur, const void* base, const void* prev, v
   if (!prev && !residual_out) return CDB_ERR_BAD_ARGUMENT;
   if (prev && (!means || !scratch)) return CDB_ERR_BAD_ARGUMENT;
   if (prev && scratch_bytes < sizeof(RelL1Scratch)) return CDB_ERR_SCRATCH_TOO_SMALL;
+  if (prev && (reinterpret_cast<uintptr_t>(scratch) & 127u)) return CDB_ERR_UNSUPPORTED;
   if (residual_out && !base && residual_out == cur) residual_out = nullptr;  // nothing to copy
   if (!prev && !residual_out) return CDB_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);

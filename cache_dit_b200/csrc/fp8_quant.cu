@@ -28,14 +28,17 @@ struct QuantFuse {
   int head_packs;
 };
 
-// tanh-GELU as x * sigmoid(2u), u = sqrt(2/pi) (x + 0.044715 x^3): one fast exponential and one
-// fast division instead of the ~25-instruction tanhf.  Their ~1e-6 relative error disappears in
-// the rounding of the result to bf16 except for a handful of values per million that sit on a
-// rounding boundary.
+// tanh-GELU as x * sigmoid(2u), u = sqrt(2/pi) (x + 0.044715 x^3) = x / (1 + 2^(c x (1 + 0.044715 x^2))),
+// c = -2 sqrt(2/pi) log2(e): three multiply-adds, one ex2 and one fast division instead of the
+// ~25-instruction tanhf (the special-function unit is what bounds this kernel).  The ~1e-6 relative
+// error disappears in the rounding of the result to bf16 except for a handful of values per million
+// that sit on a rounding boundary.
 __device__ __forceinline__ float gelu_tanh(float x) {
-  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
-  const float u = k0 * (x + k1 * x * x * x);
-  return __fdividef(x, 1.0f + __expf(-2.0f * u));
+  constexpr float c = -2.0f * 0.7978845608028654f * 1.4426950408889634f;
+  const float p = fmaf(x * x, c * 0.044715f, c);
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * p));
+  return __fdividef(x, 1.0f + e);
 }
 
 // bf16x2 word <-> two floats (bf16 -> fp32 is a 16-bit shift: no conversion instruction)
@@ -52,7 +55,7 @@ constexpr int Q_CTA = 256;  // threads per CTA; a CTA works on Q_CTA / TPR rows 
 
 // Reduction over the TPR threads that share a row: shuffles inside the warp, then (TPR > 32)
 // one shared-memory exchange between the row's warps.  `slot` alternates so that one
-// __syncthreads per reduction is enough.
+// barrier per reduction is enough.
 template <int TPR, bool MAX>
 __device__ __forceinline__ float row_reduce(float v, float (*s_red)[Q_CTA / 32], int& slot) {
   v = MAX ? warp_max(v) : warp_sum(v);
@@ -60,7 +63,8 @@ __device__ __forceinline__ float row_reduce(float v, float (*s_red)[Q_CTA / 32],
     constexpr int WPR = TPR / 32;  // warps per row
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (lane == 0) s_red[slot][warp] = v;
-    __syncthreads();
+    // only the warps of this row wait for each other (named barrier 1 + row group)
+    asm volatile("bar.sync %0, %1;" ::"r"(1 + (int)threadIdx.x / TPR), "n"(TPR) : "memory");
     const int first = (warp / WPR) * WPR;
     float r = s_red[slot][first];
 #pragma unroll
@@ -85,66 +89,116 @@ __global__ void __launch_bounds__(Q_CTA)
   const int npack = cols >> 3;
   const int group = threadIdx.x / TPR, tig = threadIdx.x % TPR;
   const int64_t iters = (rows + (int64_t)gridDim.x * RPC - 1) / ((int64_t)gridDim.x * RPC);
-  for (int64_t it = 0; it < iters; ++it) {  // same trip count for every thread: barriers stay aligned
-    const int64_t row = (it * gridDim.x + blockIdx.x) * RPC + group;
+  // LayerNorm variant: a thread owns the same columns in every row it sees, so its slice of
+  // round(1 + scale) and of shift stays in registers until the batch index changes.
+  constexpr int MV = PREOP == CDB_PRE_LAYERNORM_MOD ? VPT : 1;
+  uint4 m_one_plus[MV], m_shift[MV];
+  int64_t m_batch = -1;
+  // One row's packets for this thread; rows past the end and packets past the row load zeros.
+  auto load_row = [&](int64_t row, uint4 (&dst)[VPT]) {
     const bool valid = row < rows;
     const __nv_bfloat16* xr = x + (valid ? row : 0) * ld_x;
-    uint4 pk[VPT];
 #pragma unroll
     for (int k = 0; k < VPT; ++k) {
       const int p = tig + k * TPR;
+      const uint4* src = reinterpret_cast<const uint4*>(xr) + p;
       if constexpr (PREOP == CDB_PRE_CONCAT_GELU) {
-        const uint4* src = p < f.head_packs
-                               ? reinterpret_cast<const uint4*>(xr) + p
-                               : reinterpret_cast<const uint4*>(f.tail + (valid ? row : 0) * f.ld_tail) + (p - f.head_packs);
-        pk[k] = (valid && p < npack) ? __ldcs(src) : make_uint4(0, 0, 0, 0);
-      } else {
-        pk[k] = (valid && p < npack) ? __ldcs(reinterpret_cast<const uint4*>(xr) + p) : make_uint4(0, 0, 0, 0);
+        if (p >= f.head_packs)
+          src = reinterpret_cast<const uint4*>(f.tail + (valid ? row : 0) * f.ld_tail) + (p - f.head_packs);
       }
+      dst[k] = (valid && p < npack) ? __ldcs(src) : make_uint4(0, 0, 0, 0);
+    }
+  };
+  auto row_of = [&](int64_t it) { return (it * gridDim.x + blockIdx.x) * RPC + group; };
+
+  // The next row is requested while the current one is reduced and converted.  The LayerNorm
+  // variant (long dependent chain per row, 2 CTAs per SM either way) holds it in registers; the
+  // others only pull it into L2, which costs no registers and so keeps 5 CTAs per SM resident.
+  constexpr bool REG_PREFETCH = PREOP == CDB_PRE_LAYERNORM_MOD;
+  auto prefetch_row_l2 = [&](int64_t row) {
+    if (row >= rows) return;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int p = tig + k * TPR;
+      const uint4* src = reinterpret_cast<const uint4*>(x + row * ld_x) + p;
+      if constexpr (PREOP == CDB_PRE_CONCAT_GELU) {
+        if (p >= f.head_packs) src = reinterpret_cast<const uint4*>(f.tail + row * f.ld_tail) + (p - f.head_packs);
+      }
+      if (p < npack) asm volatile("prefetch.global.L2 [%0];" ::"l"(src));
+    }
+  };
+  uint4 pk[VPT], nxt[REG_PREFETCH ? VPT : 1];
+  if constexpr (REG_PREFETCH) load_row(row_of(0), nxt);
+  for (int64_t it = 0; it < iters; ++it) {  // same trip count for every thread: barriers stay aligned
+    const int64_t row = row_of(it);
+    const bool valid = row < rows;
+    if constexpr (REG_PREFETCH) {
+#pragma unroll
+      for (int k = 0; k < VPT; ++k) pk[k] = nxt[k];
+      if (it + 1 < iters) load_row(row_of(it + 1), nxt);
+    } else {
+      load_row(row, pk);
+      if (it + 1 < iters) prefetch_row_l2(row_of(it + 1));
     }
 
     if constexpr (PREOP == CDB_PRE_LAYERNORM_MOD) {
-      // LayerNorm statistics in fp32 from registers (two passes), the normalised value rounded to
-      // bf16, then y = round(round(norm * round(1 + scale)) + shift): the rounding points of the
-      // eager bf16 modulation, done with packed bf16 arithmetic.
+      // LayerNorm statistics in fp32 from registers (two passes over values unpacked once), the
+      // normalised value rounded to bf16, then y = round(round(norm * round(1 + scale)) + shift):
+      // the rounding points of the eager bf16 modulation, done with packed bf16 arithmetic.
+      float xf[VPT][8];
       float s = 0.f;
 #pragma unroll
       for (int k = 0; k < VPT; ++k) {
         const uint32_t w[4] = {pk[k].x, pk[k].y, pk[k].z, pk[k].w};
 #pragma unroll
-        for (int j = 0; j < 4; ++j) s += lo_f(w[j]) + hi_f(w[j]);
+        for (int j = 0; j < 4; ++j) {
+          xf[k][2 * j] = lo_f(w[j]);
+          xf[k][2 * j + 1] = hi_f(w[j]);
+          s += xf[k][2 * j] + xf[k][2 * j + 1];
+        }
       }
       const float mean = row_reduce<TPR, false>(s, s_red, slot) / (float)cols;
       float ss = 0.f;
 #pragma unroll
       for (int k = 0; k < VPT; ++k) {
         if (tig + k * TPR < npack) {
-          const uint32_t w[4] = {pk[k].x, pk[k].y, pk[k].z, pk[k].w};
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float a = lo_f(w[j]) - mean, b = hi_f(w[j]) - mean;
-            ss += a * a + b * b;
+          for (int j = 0; j < 8; ++j) {
+            xf[k][j] -= mean;
+            ss = fmaf(xf[k][j], xf[k][j], ss);
           }
         }
       }
       const float var = row_reduce<TPR, false>(ss, s_red, slot) / (float)cols;
       const float rstd = rsqrtf(var + f.eps);
       const int64_t bidx = (valid ? row : 0) / f.rows_per_batch;
-      const uint4* sh = reinterpret_cast<const uint4*>(f.shift + bidx * f.ld_mod);
-      const uint4* sc = reinterpret_cast<const uint4*>(f.scale + bidx * f.ld_mod);
-      const __nv_bfloat162 one = __float2bfloat162_rn(1.0f);
+      if (bidx != m_batch) {
+        m_batch = bidx;
+        const uint4* sh = reinterpret_cast<const uint4*>(f.shift + bidx * f.ld_mod);
+        const uint4* sc = reinterpret_cast<const uint4*>(f.scale + bidx * f.ld_mod);
+        const __nv_bfloat162 one = __float2bfloat162_rn(1.0f);
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) {
+          const int p = tig + k * TPR;
+          if (p < npack) {
+            const uint4 vsc = __ldg(sc + p);
+            m_shift[k] = __ldg(sh + p);
+            m_one_plus[k] = make_uint4(as_u32(__hadd2_rn(one, as_bf2(vsc.x))), as_u32(__hadd2_rn(one, as_bf2(vsc.y))),
+                                       as_u32(__hadd2_rn(one, as_bf2(vsc.z))), as_u32(__hadd2_rn(one, as_bf2(vsc.w))));
+          }
+        }
+      }
 #pragma unroll
       for (int k = 0; k < VPT; ++k) {
         const int p = tig + k * TPR;
         if (p < npack) {
-          const uint4 vsh = __ldg(sh + p), vsc = __ldg(sc + p);
-          uint32_t w[4] = {pk[k].x, pk[k].y, pk[k].z, pk[k].w};
-          const uint32_t wsh[4] = {vsh.x, vsh.y, vsh.z, vsh.w}, wsc[4] = {vsc.x, vsc.y, vsc.z, vsc.w};
+          uint32_t w[4];
+          const uint32_t wsh[4] = {m_shift[k].x, m_shift[k].y, m_shift[k].z, m_shift[k].w};
+          const uint32_t wop[4] = {m_one_plus[k].x, m_one_plus[k].y, m_one_plus[k].z, m_one_plus[k].w};
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            const __nv_bfloat162 nrm = as_bf2(pack2((lo_f(w[j]) - mean) * rstd, (hi_f(w[j]) - mean) * rstd));
-            const __nv_bfloat162 one_plus = __hadd2_rn(one, as_bf2(wsc[j]));
-            w[j] = as_u32(__hadd2_rn(__hmul2_rn(nrm, one_plus), as_bf2(wsh[j])));
+            const __nv_bfloat162 nrm = as_bf2(pack2(xf[k][2 * j] * rstd, xf[k][2 * j + 1] * rstd));
+            w[j] = as_u32(__hadd2_rn(__hmul2_rn(nrm, as_bf2(wop[j])), as_bf2(wsh[j])));
           }
           pk[k] = make_uint4(w[0], w[1], w[2], w[3]);
         }
@@ -184,14 +238,19 @@ __global__ void __launch_bounds__(Q_CTA)
     if (sc == 0.f) sc = 1.f;  // all-zero row: keep zeros exact instead of 0/0
     if (valid && tig == 0) scale[row] = sc;
 
-    // x / sc with one reciprocal per row: t = x * (1/sc) followed by one Newton correction
-    // (r = x - t*sc exactly by FMA; t += r * (1/sc)) reproduces the correctly rounded quotient;
-    // rows whose scale is so small that 1/sc would overflow take the plain division.
+    // x / sc with one reciprocal per row.  Plain variant (weights, bit-exact against the reference's
+    // division): t = x * (1/sc) followed by one Newton correction (r = x - t*sc exactly by FMA;
+    // t += r * (1/sc)) reproduces the correctly rounded quotient.  Fused variants: the producer
+    // already differs from an eager pipeline in the last bit of a few values per million, and
+    // x * (1/sc) can change an e4m3 code only when the quotient is within two fp32 ulps of a rounding
+    // midpoint (about 2^-19 of the elements), so the correction is dropped.  Rows whose scale is so
+    // small that 1/sc would overflow take the plain division.
     const bool tiny = sc < 1e-30f;
     const float inv = tiny ? 0.f : __frcp_rn(sc);
     auto quot = [&](float v) -> float {
       if (tiny) return __fdiv_rn(v, sc);
       float t = v * inv;
+      if constexpr (PREOP != CDB_PRE_NONE) return t;
       float r = fmaf(-t, sc, v);
       return fmaf(r, inv, t);
     };
@@ -252,6 +311,7 @@ static int launch_quant(const void* x, int64_t rows, int64_t cols, int64_t ld_x,
 #define CDB_QV(TPR)                                                                              \
   if (v <= 1) launch_quant_variant<TPR, 1, PREOP>(xp, rows, c, ld_x, f, qp, scale, st);         \
   else if (v <= 2) launch_quant_variant<TPR, 2, PREOP>(xp, rows, c, ld_x, f, qp, scale, st);    \
+  else if (v <= 3) launch_quant_variant<TPR, 3, PREOP>(xp, rows, c, ld_x, f, qp, scale, st);    \
   else if (v <= 4) launch_quant_variant<TPR, 4, PREOP>(xp, rows, c, ld_x, f, qp, scale, st);    \
   else if (v <= 6) launch_quant_variant<TPR, 6, PREOP>(xp, rows, c, ld_x, f, qp, scale, st);    \
   else if (v <= 8) launch_quant_variant<TPR, 8, PREOP>(xp, rows, c, ld_x, f, qp, scale, st);    \

@@ -15,67 +15,67 @@ namespace cdb {
 __device__ __forceinline__ __nv_bfloat162 u2b(uint32_t u) { return *reinterpret_cast<__nv_bfloat162*>(&u); }
 __device__ __forceinline__ uint32_t b2u(__nv_bfloat162 v) { return *reinterpret_cast<uint32_t*>(&v); }
 
-// A lane's WORDS consecutive bf16x2 words move as one 4-, 8- or 16-byte access.
-template <int WORDS> struct WordVec;
-template <> struct WordVec<1> { using type = uint32_t; };
-template <> struct WordVec<2> { using type = uint2; };
-template <> struct WordVec<4> { using type = uint4; };
+// One CTA of QK_THREADS threads per token (grid-stride).  The token's heads*head_dim values are
+// 16-byte packets of 8 elements; thread t owns packets t, t + 128, ...  A head is LPH = head_dim/8
+// consecutive packets, i.e. LPH consecutive lanes, and because 128 % LPH == 0 every packet of a
+// thread sits at the same place inside its head: the thread's slice of the norm weight and of the
+// token's cos / sin rows is loaded once and reused for all heads.  Sum of squares per head =
+// butterfly over LPH lanes.  All of a thread's packets are requested before any is used.
+constexpr int QK_THREADS = 128;
+constexpr int QK_PK = 4;  // packets per thread and pass (3 are used for 24 heads x 128)
 
-template <int WORDS, bool STREAM>
-__device__ __forceinline__ void load_words(const __nv_bfloat16* p, uint32_t (&v)[WORDS]) {
-  using V = typename WordVec<WORDS>::type;
-  V t = STREAM ? __ldcs(reinterpret_cast<const V*>(p)) : __ldg(reinterpret_cast<const V*>(p));
-  memcpy(v, &t, sizeof(V));
-}
-
-template <int WORDS>
-__device__ __forceinline__ void store_words(__nv_bfloat16* p, const uint32_t (&v)[WORDS]) {
-  using V = typename WordVec<WORDS>::type;
-  V t;
-  memcpy(&t, v, sizeof(V));
-  __stcs(reinterpret_cast<V*>(p), t);
-}
-
-// One warp per (token, head); a lane owns EPL = D / 32 consecutive elements (whole rotation pairs).
-template <int EPL>
-__global__ void __launch_bounds__(256)
+template <int LPH>
+__global__ void __launch_bounds__(QK_THREADS)
     qk_norm_rope_kernel(const __nv_bfloat16* __restrict__ x, int64_t ld_x, const __nv_bfloat16* __restrict__ w,
                         const __nv_bfloat16* __restrict__ cs, const __nv_bfloat16* __restrict__ sn,
                         __nv_bfloat16* __restrict__ out, int64_t ld_out, int64_t out_batch_stride,
                         int64_t tokens, int64_t tokens_per_batch, int pos_offset, int heads, float eps) {
-  constexpr int D = EPL * 32;
-  constexpr int WORDS = EPL / 2;  // bf16x2 words per lane
-  const int lane = threadIdx.x & 31;
-  const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
-  for (int64_t item = warp; item < tokens * heads; item += nwarps) {
-    const int64_t tok = item / heads;
-    const int head = (int)(item - tok * heads);
+  constexpr int D = LPH * 8;
+  const int npk = heads * LPH;
+  const int in_head = threadIdx.x % LPH;  // packet index inside the head, the same for all of this thread's packets
+  const uint4 wv = __ldg(reinterpret_cast<const uint4*>(w) + in_head);
+  const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+  for (int64_t tok = blockIdx.x; tok < tokens; tok += gridDim.x) {
     const int64_t b = tok / tokens_per_batch, t = tok - b * tokens_per_batch;
-    uint32_t v[WORDS], wv[WORDS], cv[WORDS], sv[WORDS], ov[WORDS];
-    load_words<WORDS, true>(x + tok * ld_x + (int64_t)head * D + lane * EPL, v);
     const int64_t pos = (int64_t)pos_offset + t;
-    load_words<WORDS, false>(w + lane * EPL, wv);
-    load_words<WORDS, false>(cs + pos * D + lane * EPL, cv);
-    load_words<WORDS, false>(sn + pos * D + lane * EPL, sv);
-    float ss = 0.f;
+    const uint4* src = reinterpret_cast<const uint4*>(x + tok * ld_x);
+    uint4* dst = reinterpret_cast<uint4*>(out + b * out_batch_stride + pos * ld_out);
+    const uint4 cv = __ldg(reinterpret_cast<const uint4*>(cs + pos * D) + in_head);
+    const uint4 sv = __ldg(reinterpret_cast<const uint4*>(sn + pos * D) + in_head);
+    const uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w}, sw[4] = {sv.x, sv.y, sv.z, sv.w};
+    for (int base = 0; base < npk; base += QK_THREADS * QK_PK) {
+      uint4 v[QK_PK];
 #pragma unroll
-    for (int i = 0; i < WORDS; ++i) {
-      const float lo = __uint_as_float(v[i] << 16), hi = __uint_as_float(v[i] & 0xffff0000u);
-      ss += lo * lo + hi * hi;
-    }
-    ss = warp_sum(ss);
-    const float rstd = rsqrtf(ss / (float)D + eps);
+      for (int j = 0; j < QK_PK; ++j) {
+        const int p = base + j * QK_THREADS + threadIdx.x;
+        v[j] = p < npk ? __ldcs(src + p) : make_uint4(0, 0, 0, 0);
+      }
 #pragma unroll
-    for (int i = 0; i < WORDS; ++i) {
-      const float lo = __uint_as_float(v[i] << 16), hi = __uint_as_float(v[i] & 0xffff0000u);
-      const float wlo = __uint_as_float(wv[i] << 16), whi = __uint_as_float(wv[i] & 0xffff0000u);
-      const __nv_bfloat162 y = __floats2bfloat162_rn(lo * rstd * wlo, hi * rstd * whi);
-      // rotation partner of the pair (y0, y1) is (-y1, y0)
-      const __nv_bfloat162 r = __halves2bfloat162(__hneg(__high2bfloat16(y)), __low2bfloat16(y));
-      ov[i] = b2u(__hadd2_rn(__hmul2_rn(y, u2b(cv[i])), __hmul2_rn(r, u2b(sv[i]))));
+      for (int j = 0; j < QK_PK; ++j) {
+        const int p = base + j * QK_THREADS + threadIdx.x;
+        const uint32_t xw[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float lo = __uint_as_float(xw[i] << 16), hi = __uint_as_float(xw[i] & 0xffff0000u);
+          ss += lo * lo + hi * hi;
+        }
+#pragma unroll
+        for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        const float rstd = rsqrtf(ss / (float)D + eps);
+        uint32_t ow[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float lo = __uint_as_float(xw[i] << 16), hi = __uint_as_float(xw[i] & 0xffff0000u);
+          const float wlo = __uint_as_float(ww[i] << 16), whi = __uint_as_float(ww[i] & 0xffff0000u);
+          const __nv_bfloat162 y = __floats2bfloat162_rn(lo * rstd * wlo, hi * rstd * whi);
+          // rotation partner of the pair (y0, y1) is (-y1, y0)
+          const __nv_bfloat162 r = __halves2bfloat162(__hneg(__high2bfloat16(y)), __low2bfloat16(y));
+          ow[i] = b2u(__hadd2_rn(__hmul2_rn(y, u2b(cw[i])), __hmul2_rn(r, u2b(sw[i]))));
+        }
+        if (p < npk) __stcs(dst + p, make_uint4(ow[0], ow[1], ow[2], ow[3]));
+      }
     }
-    store_words<WORDS>(out + b * out_batch_stride + pos * ld_out + (int64_t)head * D + lane * EPL, ov);
   }
 }
 
@@ -119,21 +119,19 @@ extern "C" int cdb_qk_norm_rope(const void* x, int64_t ld_x, const void* norm_we
       !aligned16(cos_table) || !aligned16(sin_table))
     return CDB_ERR_UNSUPPORTED;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int64_t warps = tokens * heads;
-  int64_t blocks = (warps + 7) / 8;
-  const int64_t cap = (int64_t)sm_count() * 8;
-  const unsigned grid = (unsigned)(blocks < cap ? blocks : cap);
+  const int64_t cap = (int64_t)sm_count() * 16;  // 16 CTAs of 128 threads per SM: one resident wave
+  const unsigned grid = (unsigned)(tokens < cap ? tokens : cap);
   const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
   const __nv_bfloat16* wp = static_cast<const __nv_bfloat16*>(norm_weight);
   const __nv_bfloat16* cp = static_cast<const __nv_bfloat16*>(cos_table);
   const __nv_bfloat16* sp = static_cast<const __nv_bfloat16*>(sin_table);
   __nv_bfloat16* op = static_cast<__nv_bfloat16*>(out);
-#define CDB_QK(EPL)                                                                                        \
-  qk_norm_rope_kernel<EPL><<<grid, 256, 0, st>>>(xp, ld_x, wp, cp, sp, op, ld_out, out_batch_stride, tokens, \
-                                                 tokens_per_batch, pos_offset, heads, eps)
-  if (head_dim == 64) CDB_QK(2);
-  else if (head_dim == 128) CDB_QK(4);
-  else CDB_QK(8);
+#define CDB_QK(LPH)                                                                                          \
+  qk_norm_rope_kernel<LPH><<<grid, QK_THREADS, 0, st>>>(xp, ld_x, wp, cp, sp, op, ld_out, out_batch_stride, \
+                                                        tokens, tokens_per_batch, pos_offset, heads, eps)
+  if (head_dim == 64) CDB_QK(8);
+  else if (head_dim == 128) CDB_QK(16);
+  else CDB_QK(32);
 #undef CDB_QK
   CDB_CUDA_CHECK(cudaGetLastError());
   return CDB_OK;

@@ -60,8 +60,8 @@ CDB_API const char* cdb_last_cuda_error(void);
  *             means[1] = round_dtype( sum |prev| / n )
  * `means` is two float32 on the device.  They are the two 0-dim tensors the reference
  * all-reduces (cache_manager.py:612-614) and then divides (cache_manager.py:619).
- * `scratch` is device memory of at least cdb_rel_l1_scratch_bytes() bytes that must be
- * zero-filled once before its first use; the kernel leaves it zeroed for the next launch.
+ * `scratch` is device memory of at least cdb_rel_l1_scratch_bytes() bytes, 128-byte aligned, that
+ * must be zero-filled once before its first use; the kernel leaves it zeroed for the next launch.
  * Launches that share one scratch buffer must be ordered on one stream.
  * ---------------------------------------------------------------------------------------- */
 CDB_API size_t cdb_rel_l1_scratch_bytes(void);
