@@ -7,7 +7,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import POINTER, c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_void_p
+from ctypes import POINTER, c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_uint64, c_void_p
 
 import torch
 
@@ -40,6 +40,18 @@ SIGNATURES = {
                                      c_int64, c_int64, c_int64, c_void_p, c_void_p]),
   "cdb_qk_norm_rope": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                                c_int64, c_int64, c_int, c_int, c_int, c_float, c_void_p]),
+  "cdb_peer_enable_access": (c_int, [c_int]),
+  "cdb_peer_alloc": (c_int, [c_size_t, POINTER(c_void_p)]),
+  "cdb_peer_free": (c_int, [c_void_p]),
+  "cdb_peer_export": (c_int, [c_void_p, c_char_p]),
+  "cdb_peer_import": (c_int, [c_char_p, POINTER(c_void_p)]),
+  "cdb_peer_release": (c_int, [c_void_p]),
+  "cdb_scatter_heads": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int64,
+                                c_int64, c_int64, c_int64, c_int, c_int, c_float, c_void_p]),
+  "cdb_gather_tokens": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int64, c_int64, c_int, c_int, c_void_p]),
+  "cdb_peer_sync_bytes": (c_size_t, []),
+  "cdb_peer_signal": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p]),
+  "cdb_peer_wait": (c_int, [c_void_p, c_int, c_void_p, c_uint64, c_void_p]),
   "cdb_gated_residual": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64,
                                  c_int64, c_void_p]),
 }
@@ -74,9 +86,10 @@ def lib() -> ctypes.CDLL:
   return _lib
 
 
-def check(status: int, what: str):
+def check(status: int, what: str, launch: bool = True):
   global launch_count
-  launch_count += 1
+  if launch:
+    launch_count += 1
   if status != 0:
     L = lib()
     msg = L.cdb_status_string(status).decode()
@@ -278,3 +291,74 @@ def fp8_quant_rows_concat_gelu(head2d, tail2d, q, scale):
                                             _ptr(tail2d), c2, tail2d.stride(0) if rows > 1 else max(c2, tail2d.stride(0)),
                                             rows, _ptr(q), _ptr(scale), _stream(head2d))
   check(st, "cdb_fp8_quant_rows_concat_gelu")
+
+
+# ---- Ulysses exchange over peer memory ---------------------------------------------------------
+def _ptr_array(ptrs):
+  return (c_void_p * len(ptrs))(*[int(p) for p in ptrs])
+
+
+def peer_enable_access(peer_device: int):
+  check(lib().cdb_peer_enable_access(int(peer_device)), "cdb_peer_enable_access", launch=False)
+
+
+def scatter_heads(x, norm_weight, cos, sin, table_row_offset: int, dst_ptrs, dst_batch_stride: int,
+                  dst_row_offset: int, heads: int, eps: float = 0.0):
+  """x [batch, tokens, heads*head_dim] bf16 -> head h into rank h // (heads/world)'s joint buffer
+  (see cdb_scatter_heads).  norm_weight None copies, else per-head RMSNorm + rotary embedding first."""
+  _need_cuda(x, norm_weight, cos, sin)
+  b, t, c = x.shape
+  d = c // heads
+  if x.dtype != torch.bfloat16 or x.stride(2) != 1 or (b > 1 and x.stride(0) != t * x.stride(1)):
+    raise RuntimeError("scatter_heads: x must be bf16 with unit column stride and uniformly strided rows")
+  if norm_weight is not None:
+    _need_contig(norm_weight, cos, sin)
+  st = lib().cdb_scatter_heads(_ptr(x), x.stride(1), _ptr(norm_weight), _ptr(cos), _ptr(sin), int(table_row_offset),
+                               _ptr_array(dst_ptrs), len(dst_ptrs), int(dst_batch_stride), b * t, t,
+                               int(dst_row_offset), heads, d, float(eps), _stream(x))
+  check(st, "cdb_scatter_heads")
+
+
+def gather_tokens(o, dst_ptrs, my_rank: int):
+  """o [batch, tokens_all, heads_per_rank, head_dim] contiguous -> token rows into their owners' buffers."""
+  _need_cuda(o)
+  _need_contig(o)
+  b, s, h, d = o.shape
+  st = lib().cdb_gather_tokens(_ptr(o), _ptr_array(dst_ptrs), len(dst_ptrs), int(my_rank), b, s, h, d, _stream(o))
+  check(st, "cdb_gather_tokens")
+
+
+def peer_signal(flag_ptrs, my_rank: int, sync, stream_of):
+  check(lib().cdb_peer_signal(_ptr_array(flag_ptrs), len(flag_ptrs), int(my_rank), _ptr(sync), _stream(stream_of)),
+        "cdb_peer_signal")
+
+
+def peer_wait(my_flags, world: int, sync, timeout_ns: int):
+  check(lib().cdb_peer_wait(_ptr(my_flags), int(world), _ptr(sync), int(timeout_ns), _stream(my_flags)),
+        "cdb_peer_wait")
+
+
+def peer_alloc(nbytes: int) -> int:
+  out = c_void_p()
+  check(lib().cdb_peer_alloc(int(nbytes), ctypes.byref(out)), "cdb_peer_alloc", launch=False)
+  return int(out.value)
+
+
+def peer_free(ptr: int):
+  check(lib().cdb_peer_free(c_void_p(ptr)), "cdb_peer_free", launch=False)
+
+
+def peer_export(ptr: int) -> bytes:
+  buf = ctypes.create_string_buffer(64)
+  check(lib().cdb_peer_export(c_void_p(ptr), buf), "cdb_peer_export", launch=False)
+  return buf.raw
+
+
+def peer_import(handle: bytes) -> int:
+  out = c_void_p()
+  check(lib().cdb_peer_import(ctypes.create_string_buffer(handle, 64), ctypes.byref(out)), "cdb_peer_import", launch=False)
+  return int(out.value)
+
+
+def peer_release(ptr: int):
+  check(lib().cdb_peer_release(c_void_p(ptr)), "cdb_peer_release", launch=False)

@@ -17,7 +17,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 PKG = os.path.dirname(HERE)
 LIB_NAME = "libcache_dit_b200.so"
 LIB_PATH = os.path.join(PKG, LIB_NAME)
-SOURCES = ["lib.cu", "cache_kernels.cu", "fp8_quant.cu", "fp8_gemm.cu", "glue_kernels.cu"]
+SOURCES = ["lib.cu", "cache_kernels.cu", "fp8_quant.cu", "fp8_gemm.cu", "glue_kernels.cu", "peer_kernels.cu"]
 HEADERS = ["common.cuh", os.path.join("..", "..", "include", "cache_dit_b200.h")]
 NVCC_FLAGS = [
   "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",

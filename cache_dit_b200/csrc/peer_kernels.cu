@@ -1,0 +1,325 @@
+// Ulysses head/sequence exchange around attention as plain stores into peer GPUs' memory over
+// NVLink, fused with the op that produces the data, instead of NCCL all-to-all calls.
+//
+// Before attention every rank holds q, k, v for ITS tokens and ALL heads; attention wants ALL tokens
+// for the rank's OWN heads.  The reference does this with four all-to-all collectives per block
+// (src/cache_dit/distributed/transformers/flux.py via diffusers' context-parallel hooks).  Here
+//   * scatter_heads_kernel normalises / rotates q and k (or copies v) and writes each head straight
+//     into the joint [batch, all tokens, own heads, head_dim] buffer of the rank that owns the head;
+//   * gather_tokens_kernel writes each token row of the attention output into the
+//     [batch, own tokens, all heads, head_dim] buffer of the rank that owns the token;
+//   * peer_signal / peer_wait order the two phases with one flag word per (rank, peer) pair.
+// All remote accesses are stores (peer pointers obtained through CUDA IPC by the host side); all
+// loads are local: ordinary 16-byte st.global to a mapped peer address, nothing else crosses NVLink.
+// Every launch is a fixed sequence of pointers and sizes, so whole block segments, exchange included,
+// can be captured in a CUDA graph; the barrier's epoch lives in device memory for that reason.
+#include <cstring>
+
+#include "common.cuh"
+
+namespace cdb {
+
+constexpr int PEER_MAX = 8;
+
+struct PeerPtrs {
+  void* p[PEER_MAX];
+};
+
+__device__ __forceinline__ __nv_bfloat162 pu2b(uint32_t u) { return *reinterpret_cast<__nv_bfloat162*>(&u); }
+__device__ __forceinline__ uint32_t pb2u(__nv_bfloat162 v) { return *reinterpret_cast<uint32_t*>(&v); }
+
+constexpr int SC_THREADS = 128;
+constexpr int SC_PK = 4;
+
+// One CTA per token (grid-stride).  Packets of 8 elements; LPH = head_dim / 8 packets per head.
+// Head h goes to rank h / heads_per_rank, as local head h % heads_per_rank, at joint row
+// dst_row_offset + (token index inside its batch).  NORM_ROPE = false copies (the v projection).
+template <int LPH, bool NORM_ROPE>
+__global__ void __launch_bounds__(SC_THREADS)
+    scatter_heads_kernel(const __nv_bfloat16* __restrict__ x, int64_t ld_x, const __nv_bfloat16* __restrict__ w,
+                         const __nv_bfloat16* __restrict__ cs, const __nv_bfloat16* __restrict__ sn, int table_row_offset,
+                         const PeerPtrs dst, int heads_per_rank, int64_t ld_out, int64_t out_batch_stride,
+                         int64_t tokens, int64_t tokens_per_batch, int64_t dst_row_offset, int heads, float eps) {
+  constexpr int D = LPH * 8;
+  const int npk = heads * LPH;
+  const int in_head = threadIdx.x % LPH;
+  uint32_t ww[4] = {0, 0, 0, 0};
+  if constexpr (NORM_ROPE) {
+    const uint4 wv = __ldg(reinterpret_cast<const uint4*>(w) + in_head);
+    ww[0] = wv.x; ww[1] = wv.y; ww[2] = wv.z; ww[3] = wv.w;
+  }
+  for (int64_t tok = blockIdx.x; tok < tokens; tok += gridDim.x) {
+    const int64_t b = tok / tokens_per_batch, t = tok - b * tokens_per_batch;
+    const uint4* src = reinterpret_cast<const uint4*>(x + tok * ld_x);
+    const int64_t dst_elem = b * out_batch_stride + (dst_row_offset + t) * ld_out;
+    uint32_t cw[4] = {0, 0, 0, 0}, sw[4] = {0, 0, 0, 0};
+    if constexpr (NORM_ROPE) {
+      const int64_t pos = (int64_t)table_row_offset + t;
+      const uint4 cv = __ldg(reinterpret_cast<const uint4*>(cs + pos * D) + in_head);
+      const uint4 sv = __ldg(reinterpret_cast<const uint4*>(sn + pos * D) + in_head);
+      cw[0] = cv.x; cw[1] = cv.y; cw[2] = cv.z; cw[3] = cv.w;
+      sw[0] = sv.x; sw[1] = sv.y; sw[2] = sv.z; sw[3] = sv.w;
+    }
+    for (int base = 0; base < npk; base += SC_THREADS * SC_PK) {
+      uint4 v[SC_PK];
+#pragma unroll
+      for (int j = 0; j < SC_PK; ++j) {
+        const int p = base + j * SC_THREADS + threadIdx.x;
+        v[j] = p < npk ? __ldcs(src + p) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int j = 0; j < SC_PK; ++j) {
+        const int p = base + j * SC_THREADS + threadIdx.x;
+        uint32_t ow[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+        if constexpr (NORM_ROPE) {
+          float ss = 0.f;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float lo = __uint_as_float(ow[i] << 16), hi = __uint_as_float(ow[i] & 0xffff0000u);
+            ss += lo * lo + hi * hi;
+          }
+#pragma unroll
+          for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+          const float rstd = rsqrtf(ss / (float)D + eps);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float lo = __uint_as_float(ow[i] << 16), hi = __uint_as_float(ow[i] & 0xffff0000u);
+            const float wlo = __uint_as_float(ww[i] << 16), whi = __uint_as_float(ww[i] & 0xffff0000u);
+            const __nv_bfloat162 y = __floats2bfloat162_rn(lo * rstd * wlo, hi * rstd * whi);
+            const __nv_bfloat162 r = __halves2bfloat162(__hneg(__high2bfloat16(y)), __low2bfloat16(y));
+            ow[i] = pb2u(__hadd2_rn(__hmul2_rn(y, pu2b(cw[i])), __hmul2_rn(r, pu2b(sw[i]))));
+          }
+        }
+        if (p < npk) {
+          const int head = p / LPH;
+          const int owner = head / heads_per_rank;
+          const int local_head = head - owner * heads_per_rank;
+          __nv_bfloat16* base_ptr = static_cast<__nv_bfloat16*>(dst.p[owner]);
+          uint4* out = reinterpret_cast<uint4*>(base_ptr + dst_elem + (int64_t)local_head * D) + (p - head * LPH);
+          *out = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+        }
+      }
+    }
+  }
+}
+
+// Attention output of this rank, [batch, all tokens, own heads, head_dim]: the row of token s goes
+// to rank s / tokens_per_rank, into its [batch, own tokens, all heads, head_dim] buffer at head
+// offset my_rank * heads_per_rank.  One CTA per (batch, token) row, 16-byte packets.
+__global__ void __launch_bounds__(128)
+    gather_tokens_kernel(const __nv_bfloat16* __restrict__ o, const PeerPtrs dst, int my_rank, int64_t batch,
+                         int64_t tokens_all, int64_t tokens_per_rank, int heads_per_rank, int heads_all, int head_dim) {
+  const int row_packets = heads_per_rank * head_dim / 8;
+  const int64_t rows = batch * tokens_all;
+  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+    const int64_t b = r / tokens_all, s = r - b * tokens_all;
+    const int owner = (int)(s / tokens_per_rank);
+    const int64_t local_s = s - (int64_t)owner * tokens_per_rank;
+    const uint4* src = reinterpret_cast<const uint4*>(o + r * (int64_t)heads_per_rank * head_dim);
+    __nv_bfloat16* base_ptr = static_cast<__nv_bfloat16*>(dst.p[owner]);
+    uint4* out = reinterpret_cast<uint4*>(base_ptr + ((b * tokens_per_rank + local_s) * heads_all +
+                                                      (int64_t)my_rank * heads_per_rank) * head_dim);
+    for (int p = threadIdx.x; p < row_packets; p += blockDim.x) out[p] = __ldcs(src + p);
+  }
+}
+
+// ---- cross-GPU ordering ------------------------------------------------------------------------
+// Flags: every rank owns `world` 32-bit words; word r of rank p's array is written by rank r only.
+// Each rank keeps an epoch counter in its own memory.  signal: epoch += 1, then store the epoch into
+// word `my_rank` of every rank's array (release at system scope; the data kernels before it on the
+// stream have completed, so their stores to peer memory are already performed).  wait: spin until
+// every word of the own array has reached the own epoch, bounded by a timeout; on expiry a sticky
+// status is recorded and this and all later waits return at once, so a lost peer cannot hang the GPU.
+struct PeerSync {
+  unsigned int epoch;
+  int status;  // 0 ok; 1 + peer index that was late
+};
+
+__global__ void peer_signal_kernel(const PeerPtrs flags, int my_rank, int world, PeerSync* sync) {
+  __shared__ unsigned int e;
+  if (threadIdx.x == 0) {
+    e = sync->epoch + 1;
+    sync->epoch = e;
+  }
+  __syncthreads();
+  if ((int)threadIdx.x < world) {
+    __threadfence_system();
+    unsigned int* word = static_cast<unsigned int*>(flags.p[threadIdx.x]) + my_rank;
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(word), "r"(e) : "memory");
+  }
+}
+
+__global__ void peer_wait_kernel(const unsigned int* __restrict__ my_flags, int world, PeerSync* sync,
+                                 unsigned long long timeout_ns) {
+  if ((int)threadIdx.x >= world) return;
+  if (sync->status != 0) return;  // sticky: a peer was lost earlier
+  const unsigned int want = sync->epoch;
+  const unsigned int* word = my_flags + threadIdx.x;
+  unsigned long long t0 = 0;
+  for (unsigned int it = 0;; ++it) {
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(word) : "memory");
+    if ((int)(v - want) >= 0) break;  // epochs wrap: compare as a signed difference
+    if ((it & 63u) == 63u) {
+      unsigned long long now;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > timeout_ns) {
+        atomicCAS(&sync->status, 0, 1 + (int)threadIdx.x);
+        break;
+      }
+      __nanosleep(200);
+    }
+  }
+  __threadfence_system();
+}
+
+}  // namespace cdb
+
+using namespace cdb;
+
+static bool fill_ptrs(PeerPtrs* out, void* const* ptrs, int world) {
+  if (!ptrs || world < 1 || world > PEER_MAX) return false;
+  for (int i = 0; i < PEER_MAX; ++i) out->p[i] = i < world ? ptrs[i] : nullptr;
+  for (int i = 0; i < world; ++i)
+    if (!out->p[i] || !aligned16(out->p[i])) return false;
+  return true;
+}
+
+extern "C" int cdb_peer_enable_access(int peer_device) {
+  int dev = 0;
+  CDB_CUDA_CHECK(cudaGetDevice(&dev));
+  if (peer_device == dev) return CDB_OK;
+  int can = 0;
+  CDB_CUDA_CHECK(cudaDeviceCanAccessPeer(&can, dev, peer_device));
+  if (!can) return CDB_ERR_UNSUPPORTED;
+  cudaError_t e = cudaDeviceEnablePeerAccess(peer_device, 0);
+  if (e == cudaErrorPeerAccessAlreadyEnabled) {
+    (void)cudaGetLastError();
+    return CDB_OK;
+  }
+  CDB_CUDA_CHECK(e);
+  return CDB_OK;
+}
+
+// ---- buffers that peers can map ------------------------------------------------------------------
+// Plain cudaMalloc allocations (one IPC handle = one buffer, offset 0), zero-filled.
+extern "C" int cdb_peer_alloc(size_t bytes, void** out) {
+  if (!out || bytes == 0) return CDB_ERR_BAD_ARGUMENT;
+  void* p = nullptr;
+  CDB_CUDA_CHECK(cudaMalloc(&p, bytes));
+  cudaError_t e = cudaMemset(p, 0, bytes);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) {
+    cudaFree(p);
+    CDB_CUDA_CHECK(e);
+  }
+  *out = p;
+  return CDB_OK;
+}
+
+extern "C" int cdb_peer_free(void* p) {
+  if (p) CDB_CUDA_CHECK(cudaFree(p));
+  return CDB_OK;
+}
+
+extern "C" int cdb_peer_export(const void* p, unsigned char* handle64) {
+  if (!p || !handle64) return CDB_ERR_BAD_ARGUMENT;
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  cudaIpcMemHandle_t h;
+  CDB_CUDA_CHECK(cudaIpcGetMemHandle(&h, const_cast<void*>(p)));
+  memcpy(handle64, &h, 64);
+  return CDB_OK;
+}
+
+extern "C" int cdb_peer_import(const unsigned char* handle64, void** out) {
+  if (!handle64 || !out) return CDB_ERR_BAD_ARGUMENT;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, 64);
+  void* p = nullptr;
+  CDB_CUDA_CHECK(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+  *out = p;
+  return CDB_OK;
+}
+
+extern "C" int cdb_peer_release(void* imported) {
+  if (imported) CDB_CUDA_CHECK(cudaIpcCloseMemHandle(imported));
+  return CDB_OK;
+}
+
+extern "C" int cdb_scatter_heads(const void* x, int64_t ld_x, const void* norm_weight, const void* cos_table,
+                                 const void* sin_table, int table_row_offset, void* const* dst_ptrs, int world,
+                                 int64_t dst_batch_stride, int64_t tokens, int64_t tokens_per_batch,
+                                 int64_t dst_row_offset, int heads, int head_dim, float eps, void* stream) {
+  PeerPtrs dst;
+  if (!x || tokens < 0 || tokens_per_batch <= 0 || heads <= 0 || !fill_ptrs(&dst, dst_ptrs, world))
+    return CDB_ERR_BAD_ARGUMENT;
+  const bool norm = norm_weight != nullptr;
+  if (norm && (!cos_table || !sin_table)) return CDB_ERR_BAD_ARGUMENT;
+  if (tokens == 0) return CDB_OK;
+  if ((head_dim != 64 && head_dim != 128 && head_dim != 256) || heads % world != 0 || ld_x % 8 != 0 ||
+      dst_batch_stride % 8 != 0 || !aligned16(x) ||
+      (norm && (!aligned16(norm_weight) || !aligned16(cos_table) || !aligned16(sin_table))))
+    return CDB_ERR_UNSUPPORTED;
+  const int hpr = heads / world;
+  const int64_t ld_out = (int64_t)hpr * head_dim;
+  const int64_t cap = (int64_t)sm_count() * 16;
+  const unsigned grid = (unsigned)(tokens < cap ? tokens : cap);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
+  const __nv_bfloat16* wp = static_cast<const __nv_bfloat16*>(norm_weight);
+  const __nv_bfloat16* cp = static_cast<const __nv_bfloat16*>(cos_table);
+  const __nv_bfloat16* sp = static_cast<const __nv_bfloat16*>(sin_table);
+#define CDB_SC(LPH, NR)                                                                                     \
+  scatter_heads_kernel<LPH, NR><<<grid, SC_THREADS, 0, st>>>(xp, ld_x, wp, cp, sp, table_row_offset, dst, hpr, \
+                                                             ld_out, dst_batch_stride, tokens, tokens_per_batch, \
+                                                             dst_row_offset, heads, eps)
+  if (norm) {
+    if (head_dim == 64) CDB_SC(8, true);
+    else if (head_dim == 128) CDB_SC(16, true);
+    else CDB_SC(32, true);
+  } else {
+    if (head_dim == 64) CDB_SC(8, false);
+    else if (head_dim == 128) CDB_SC(16, false);
+    else CDB_SC(32, false);
+  }
+#undef CDB_SC
+  CDB_CUDA_CHECK(cudaGetLastError());
+  return CDB_OK;
+}
+
+extern "C" int cdb_gather_tokens(const void* o, void* const* dst_ptrs, int world, int my_rank, int64_t batch,
+                                 int64_t tokens_all, int heads_per_rank, int head_dim, void* stream) {
+  PeerPtrs dst;
+  if (!o || batch <= 0 || tokens_all <= 0 || heads_per_rank <= 0 || my_rank < 0 || my_rank >= world ||
+      !fill_ptrs(&dst, dst_ptrs, world))
+    return CDB_ERR_BAD_ARGUMENT;
+  if (tokens_all % world != 0 || (heads_per_rank * head_dim) % 8 != 0 || !aligned16(o)) return CDB_ERR_UNSUPPORTED;
+  const int64_t rows = batch * tokens_all;
+  const int64_t cap = (int64_t)sm_count() * 16;
+  gather_tokens_kernel<<<(unsigned)(rows < cap ? rows : cap), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(o), dst, my_rank, batch, tokens_all, tokens_all / world, heads_per_rank,
+      heads_per_rank * world, head_dim);
+  CDB_CUDA_CHECK(cudaGetLastError());
+  return CDB_OK;
+}
+
+extern "C" size_t cdb_peer_sync_bytes(void) { return sizeof(PeerSync); }
+
+extern "C" int cdb_peer_signal(void* const* flag_ptrs, int world, int my_rank, void* sync, void* stream) {
+  PeerPtrs flags;
+  if (!sync || my_rank < 0 || my_rank >= world || !fill_ptrs(&flags, flag_ptrs, world)) return CDB_ERR_BAD_ARGUMENT;
+  peer_signal_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(flags, my_rank, world,
+                                                                      static_cast<PeerSync*>(sync));
+  CDB_CUDA_CHECK(cudaGetLastError());
+  return CDB_OK;
+}
+
+extern "C" int cdb_peer_wait(const void* my_flags, int world, void* sync, uint64_t timeout_ns, void* stream) {
+  if (!my_flags || !sync || world < 1 || world > PEER_MAX) return CDB_ERR_BAD_ARGUMENT;
+  peer_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const unsigned int*>(my_flags), world,
+                                                                    static_cast<PeerSync*>(sync),
+                                                                    (unsigned long long)timeout_ns);
+  CDB_CUDA_CHECK(cudaGetLastError());
+  return CDB_OK;
+}

@@ -50,6 +50,23 @@ class ParallelismConfig:
   def cp_enabled(self) -> bool:
     return (self.ulysses_size or 1) > 1
 
+  def exchange_mode(self) -> str:
+    """How attention trades heads for tokens: "peer" = stores into the other GPUs' memory fused with
+    the producing kernels (single node, NCCL process group, at most 8 ranks), "nccl" = all-to-all
+    collectives.  `parallel_kwargs["exchange"]` or CACHE_DIT_B200_ULYSSES_EXCHANGE picks one; the
+    default takes "peer" whenever it applies."""
+    import os
+    want = self.parallel_kwargs.get("exchange") or os.environ.get("CACHE_DIT_B200_ULYSSES_EXCHANGE") or "auto"
+    if want not in ("auto", "peer", "nccl"):
+      raise ValueError(f"unknown Ulysses exchange {want!r} (auto | peer | nccl)")
+    if want != "auto":
+      return want
+    if not (dist.is_available() and dist.is_initialized() and torch.cuda.is_available()):
+      return "nccl"
+    one_node = os.environ.get("LOCAL_WORLD_SIZE", os.environ.get("WORLD_SIZE", "1")) == os.environ.get("WORLD_SIZE", "1")
+    world = dist.get_world_size(self._group)
+    return "peer" if dist.get_backend(self._group) == "nccl" and one_node and 1 < world <= 8 else "nccl"
+
   def enabled(self) -> bool:
     return self.cp_enabled()
 

@@ -19,8 +19,8 @@ from torch import nn
 
 from ..caching.block_adapters import BlockAdapter, BlockAdapterRegister
 from ..caching.forward_pattern import ForwardPattern
-from .layers import (RMSNorm, TimestepMLP, UlyssesGroup, attention, concat_gelu_linear, gated_add, gelu_linear,
-                     joint_qk_norm_rope, norm_modulate, norm_modulate_linears, rope_frequencies, rope_tables,
+from .layers import (RMSNorm, TimestepMLP, UlyssesGroup, concat_gelu_linear, gated_add, gelu_linear,
+                     joint_attention, norm_modulate, norm_modulate_linears, rope_frequencies, rope_tables,
                      timestep_embedding)
 
 
@@ -87,10 +87,8 @@ class FluxTransformerBlock(nn.Module):
     q, k, v = norm_modulate_linears(hidden_states, shift, scale, (a.to_q, a.to_k, a.to_v))
     cq, ck, cv = norm_modulate_linears(encoder_hidden_states, c_shift, c_scale,
                                        (a.add_q_proj, a.add_k_proj, a.add_v_proj))
-    q = joint_qk_norm_rope(((cq, a.norm_added_q), (q, a.norm_q)), image_rotary_emb, a.heads)
-    k = joint_qk_norm_rope(((ck, a.norm_added_k), (k, a.norm_k)), image_rotary_emb, a.heads)
-    v = torch.cat([a.heads_view(cv), a.heads_view(v)], dim=1)
-    o = attention(q, k, v, self.cp)
+    o = joint_attention(((cq, a.norm_added_q), (q, a.norm_q)), ((ck, a.norm_added_k), (k, a.norm_k)), (cv, v),
+                        image_rotary_emb, a.heads, self.cp)
     n_txt = encoder_hidden_states.shape[1]
     hidden_states = gated_add(hidden_states, gate, a.to_out(o[:, n_txt:]))
     encoder_hidden_states = gated_add(encoder_hidden_states, c_gate, a.to_add_out(o[:, :n_txt]))
@@ -118,9 +116,7 @@ class FluxSingleTransformerBlock(nn.Module):
     x = torch.cat([encoder_hidden_states, hidden_states], dim=1)
     shift, scale, gate = self.norm(temb)
     q, k, v, mlp = norm_modulate_linears(x, shift, scale, (a.to_q, a.to_k, a.to_v, self.proj_mlp))
-    q = joint_qk_norm_rope(((q, a.norm_q), ), image_rotary_emb, a.heads)
-    k = joint_qk_norm_rope(((k, a.norm_k), ), image_rotary_emb, a.heads)
-    o = attention(q, k, a.heads_view(v), self.cp)
+    o = joint_attention(((q, a.norm_q), ), ((k, a.norm_k), ), (v, ), image_rotary_emb, a.heads, self.cp)
     y = concat_gelu_linear(o, mlp, self.proj_out)
     x = gated_add(x, gate, y)
     return x[:, :n_txt], x[:, n_txt:]
@@ -164,11 +160,18 @@ class FluxTransformer2DModel(nn.Module):
   # ---- context parallelism: split tokens and ids at the root, gather after proj_out
   # (the reference's plan for FLUX: src/cache_dit/distributed/transformers/flux.py:49-61)
   def enable_context_parallel(self, config):
-    self._cp = UlyssesGroup(getattr(config, "_group", None))
+    group = getattr(config, "_group", None)
+    exchange = None
+    if config.exchange_mode() == "peer":
+      from ..distributed.peer_exchange import PeerExchange
+      exchange = PeerExchange(group)
+    self._cp = UlyssesGroup(group, exchange)
     for block in list(self.transformer_blocks) + list(self.single_transformer_blocks):
       block.cp = self._cp
 
   def disable_context_parallel(self):
+    if self._cp is not None and self._cp.exchange is not None:
+      self._cp.exchange.close()
     self._cp = None
     for block in list(self.transformer_blocks) + list(self.single_transformer_blocks):
       block.cp = None

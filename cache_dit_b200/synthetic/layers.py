@@ -146,13 +146,49 @@ def gated_add(x: torch.Tensor, gate: torch.Tensor, y: torch.Tensor) -> torch.Ten
 
 
 class UlyssesGroup:
-  """What attention needs to know about context parallelism: the group and its size."""
+  """What attention needs to know about context parallelism: the group, its size, and - when the
+  ranks share one NVLink domain - the peer-memory exchange that replaces the all-to-all calls."""
 
-  def __init__(self, group=None):
+  def __init__(self, group=None, exchange=None):
     import torch.distributed as dist
     self.group = group
     self.world = dist.get_world_size(group)
     self.rank = dist.get_rank(group)
+    self.exchange = exchange
+
+
+def joint_attention(q_parts, k_parts, v_parts, rope, heads: int, cp: Optional["UlyssesGroup"] = None) -> torch.Tensor:
+  """Attention over the concatenation (text first) of the given projections.
+
+  q_parts / k_parts: sequences of (projection [B, T_i, H*D], RMSNorm module); v_parts: projections.
+  Returns [B, sum T_i, H*D] for this rank's tokens.  Per-head norm, rotary embedding and the
+  concatenation are one kernel per part; under Ulysses with a peer exchange the same kernel also does
+  the head scatter to the other GPUs."""
+  ex = cp.exchange if cp is not None and cp.world > 1 else None
+  if ex is None:
+    q = joint_qk_norm_rope(q_parts, rope, heads)
+    k = joint_qk_norm_rope(k_parts, rope, heads)
+    d = q.shape[-1]
+    vs = [v.unflatten(-1, (heads, d)) for v in v_parts]
+    return attention(q, k, vs[0] if len(vs) == 1 else torch.cat(vs, dim=1), cp)
+  x0 = q_parts[0][0]
+  d = x0.shape[-1] // heads
+  local_total = sum(p.shape[1] for p, _ in q_parts)
+  ex.ensure(x0.shape[0], local_total, heads, d, x0.dtype)
+  for name, parts in (("q", q_parts), ("k", k_parts)):
+    off = 0
+    for x, norm in parts:
+      ex.scatter(name, x, heads, off, local_total, norm.weight, rope[0], rope[1], norm.eps)
+      off += x.shape[1]
+  off = 0
+  for x in v_parts:
+    ex.scatter("v", x, heads, off, local_total)
+    off += x.shape[1]
+  ex.barrier()
+  b = ex.buffers
+  o = F.scaled_dot_product_attention(b["q"].transpose(1, 2), b["k"].transpose(1, 2), b["v"].transpose(1, 2))
+  o = o.transpose(1, 2).contiguous()  # [B, S_all, H/W, D]
+  return ex.gather_output(o).flatten(2)
 
 
 def _all_to_all(x: torch.Tensor, scatter_dim: int, gather_dim: int, cp: UlyssesGroup) -> torch.Tensor:

@@ -194,6 +194,48 @@ CDB_API int cdb_gated_residual(const void* x, const void* y, int64_t ld_y, const
                        int64_t ld_gate, void* out, int64_t rows, int64_t rows_per_batch,
                        int64_t cols, void* stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Ulysses exchange around attention as stores into peer GPUs' memory (NVLink), fused with the
+ * producer.  Replaces the four all-to-all collectives per block that the reference's context-
+ * parallel plan issues through diffusers' hooks (src/cache_dit/distributed/transformers/flux.py:49-61,
+ * src/cache_dit/distributed/core/_distributed_primitives.py all-to-all helpers).
+ * `dst_ptrs[r]` / `flag_ptrs[r]` are addresses valid on THIS device for rank r's buffer (the own
+ * buffer for r = own rank, CUDA-IPC mappings for the others); at most 8 ranks.
+ *
+ * cdb_scatter_heads: x [tokens, heads*head_dim] bf16 (row stride ld_x) holds this rank's tokens for
+ *   all heads.  Head h is written to rank h / (heads/world) as local head h % (heads/world), joint row
+ *   dst_row_offset + (token index in its batch), in a [batch, rows, heads/world, head_dim] buffer with
+ *   batch stride dst_batch_stride.  With norm_weight != NULL the per-head RMSNorm + rotary embedding of
+ *   cdb_qk_norm_rope is applied first (table row = table_row_offset + token index); with NULL it copies.
+ * cdb_gather_tokens: o [batch, tokens_all, heads_per_rank, head_dim] (this rank's heads, all tokens):
+ *   token s goes to rank s / (tokens_all/world), into its [batch, tokens_all/world, heads_per_rank*world,
+ *   head_dim] buffer at head offset my_rank*heads_per_rank.
+ * cdb_peer_signal / cdb_peer_wait: `sync` is cdb_peer_sync_bytes() of zeroed device memory per rank;
+ *   each rank owns `world` zeroed 32-bit flag words.  signal bumps the rank's epoch and stores it into
+ *   word my_rank of every rank's flags; wait returns when all words of the own flags reached the own
+ *   epoch, or after timeout_ns, in which case a status is latched in `sync` (second int32: 1 + late
+ *   peer) and every later wait returns at once.  Both are single launches and may be graph-captured.
+ * cdb_peer_enable_access: cudaDeviceEnablePeerAccess from the current device, idempotent.
+ * ---------------------------------------------------------------------------------------- */
+CDB_API int cdb_peer_enable_access(int peer_device);
+/* Buffers peers can map: cudaMalloc'd and zero-filled (alloc), exported as a 64-byte CUDA IPC handle,
+ * imported in another process on the same node (the returned address is valid on the importer's
+ * current device; peer access is enabled by the import), released before the owner frees. */
+CDB_API int cdb_peer_alloc(size_t bytes, void** out);
+CDB_API int cdb_peer_free(void* p);
+CDB_API int cdb_peer_export(const void* p, unsigned char* handle64);
+CDB_API int cdb_peer_import(const unsigned char* handle64, void** out);
+CDB_API int cdb_peer_release(void* imported);
+CDB_API int cdb_scatter_heads(const void* x, int64_t ld_x, const void* norm_weight, const void* cos_table,
+                      const void* sin_table, int table_row_offset, void* const* dst_ptrs, int world,
+                      int64_t dst_batch_stride, int64_t tokens, int64_t tokens_per_batch,
+                      int64_t dst_row_offset, int heads, int head_dim, float eps, void* stream);
+CDB_API int cdb_gather_tokens(const void* o, void* const* dst_ptrs, int world, int my_rank, int64_t batch,
+                      int64_t tokens_all, int heads_per_rank, int head_dim, void* stream);
+CDB_API size_t cdb_peer_sync_bytes(void);
+CDB_API int cdb_peer_signal(void* const* flag_ptrs, int world, int my_rank, void* sync, void* stream);
+CDB_API int cdb_peer_wait(const void* my_flags, int world, void* sync, uint64_t timeout_ns, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

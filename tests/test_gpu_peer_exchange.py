@@ -1,0 +1,111 @@
+"""Ulysses exchange kernels with W emulated ranks on ONE GPU: every rank's buffers are ordinary
+tensors of this process and the pointer tables are filled with their addresses, so the index
+arithmetic of the scatter / gather kernels and the flag protocol are checked without a second GPU.
+Signals are all issued before any wait (kernels that wait for each other must not be queued behind
+one another on one device)."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def nat():
+  from cache_dit_b200 import _native
+  _native.lib()
+  return _native
+
+
+def _rope(x, cos, sin):
+  cos, sin = cos[None, :, None, :], sin[None, :, None, :]
+  x1, x2 = x.unflatten(-1, (-1, 2)).unbind(-1)
+  return x * cos + torch.stack([-x2, x1], dim=-1).flatten(-2) * sin
+
+
+@pytest.mark.parametrize("world,batch,t_txt,t_img,heads,d", [(2, 1, 8, 24, 4, 64), (4, 2, 4, 12, 8, 128), (2, 1, 256, 2048, 24, 128)])
+def test_scatter_and_gather_match_all_to_all_semantics(nat, world, batch, t_txt, t_img, heads, d):
+  g = torch.Generator().manual_seed(world * 7 + d)
+  c, hpr, t_loc = heads * d, heads // world, t_txt + t_img
+  bf = torch.bfloat16
+  mk = lambda *s: torch.randn(*s, generator=g).to("cuda", bf)
+  # per-rank inputs (each rank has its own token shard and its own rotary rows)
+  txt = [mk(batch, t_txt, 3 * c) for _ in range(world)]
+  img = [mk(batch, t_img, 3 * c) for _ in range(world)]
+  w_txt, w_img = (1 + 0.1 * mk(d)), (1 + 0.1 * mk(d))
+  ang = [torch.rand(t_loc, d // 2, generator=g) * 6.28 for _ in range(world)]
+  cos = [torch.cos(a).repeat_interleave(2, dim=-1).to("cuda", bf).contiguous() for a in ang]
+  sin = [torch.sin(a).repeat_interleave(2, dim=-1).to("cuda", bf).contiguous() for a in ang]
+  qbuf = [torch.full((batch, t_loc * world, hpr, d), float("nan"), device="cuda", dtype=bf) for _ in range(world)]
+  vbuf = [torch.full((batch, t_loc * world, hpr, d), float("nan"), device="cuda", dtype=bf) for _ in range(world)]
+  qptrs, vptrs = [b.data_ptr() for b in qbuf], [b.data_ptr() for b in vbuf]
+  for r in range(world):
+    base = r * t_loc
+    nat.scatter_heads(txt[r][..., :c], w_txt, cos[r], sin[r], 0, qptrs, qbuf[0].stride(0), base, heads, 1e-6)
+    nat.scatter_heads(img[r][..., :c], w_img, cos[r], sin[r], t_txt, qptrs, qbuf[0].stride(0), base + t_txt, heads, 1e-6)
+    nat.scatter_heads(txt[r][..., 2 * c:], None, None, None, 0, vptrs, vbuf[0].stride(0), base, heads)
+    nat.scatter_heads(img[r][..., 2 * c:], None, None, None, t_txt, vptrs, vbuf[0].stride(0), base + t_txt, heads)
+  torch.cuda.synchronize()
+  # reference: the single-GPU kernel per rank, then the all-to-all's permutation done with torch ops
+  full_q, full_v = [], []
+  for r in range(world):
+    joint = torch.empty(batch, t_loc, heads, d, device="cuda", dtype=bf)
+    nat.qk_norm_rope(txt[r][..., :c], w_txt, cos[r], sin[r], joint, 0, heads, 1e-6)
+    nat.qk_norm_rope(img[r][..., :c], w_img, cos[r], sin[r], joint, t_txt, heads, 1e-6)
+    full_q.append(joint)
+    full_v.append(torch.cat([txt[r][..., 2 * c:], img[r][..., 2 * c:]], dim=1).unflatten(-1, (heads, d)))
+  all_q, all_v = torch.cat(full_q, dim=1), torch.cat(full_v, dim=1)  # [B, W*t_loc, H, D]
+  for owner in range(world):
+    hs = slice(owner * hpr, (owner + 1) * hpr)
+    assert torch.equal(qbuf[owner], all_q[:, :, hs])
+    assert torch.equal(vbuf[owner], all_v[:, :, hs])
+  # the per-rank kernel itself against fp32 math
+  ref = _rope(F.rms_norm(txt[0][..., :c].float().unflatten(-1, (heads, d)), (d, ), w_txt.float(), 1e-6),
+              cos[0][:t_txt].float(), sin[0][:t_txt].float())
+  got = full_q[0][:, :t_txt].float()
+  assert ((got - ref).abs() <= 3 * 2.0**-8 * ref.abs() + 2e-2).all().item()
+
+  # gather: attention outputs [B, all tokens, own heads, D] back to [B, own tokens, all heads, D]
+  o_loc = [mk(batch, t_loc * world, hpr, d) for _ in range(world)]
+  obuf = [torch.full((batch, t_loc, heads, d), float("nan"), device="cuda", dtype=bf) for _ in range(world)]
+  optrs = [b.data_ptr() for b in obuf]
+  for r in range(world):
+    nat.gather_tokens(o_loc[r], optrs, r)
+  torch.cuda.synchronize()
+  for r in range(world):
+    want = torch.cat([o_loc[gk][:, r * t_loc:(r + 1) * t_loc] for gk in range(world)], dim=2)
+    assert torch.equal(obuf[r], want)
+
+
+def test_flag_protocol_and_bounded_wait(nat):
+  world = 3
+  nwords = nat.lib().cdb_peer_sync_bytes() // 4
+  flags = [torch.zeros(64, dtype=torch.int32, device="cuda") for _ in range(world)]
+  sync = [torch.zeros(nwords, dtype=torch.int32, device="cuda") for _ in range(world)]
+  fptrs = [f.data_ptr() for f in flags]
+  for epoch in (1, 2, 3):
+    for r in range(world):
+      nat.peer_signal(fptrs, r, sync[r], flags[r])
+    for r in range(world):
+      nat.peer_wait(flags[r], world, sync[r], 1_000_000_000)
+    torch.cuda.synchronize()
+    for r in range(world):
+      assert flags[r][:world].tolist() == [epoch] * world
+      assert sync[r].tolist()[:2] == [epoch, 0]
+  # a peer that never signals: the wait gives up after its limit and latches which peer was late
+  nat.peer_signal(fptrs[:2] + [torch.zeros(64, dtype=torch.int32, device="cuda").data_ptr()], 0, sync[0], flags[0])
+  nat.peer_signal(fptrs[:2] + [torch.zeros(64, dtype=torch.int32, device="cuda").data_ptr()], 1, sync[1], flags[1])
+  t0 = torch.cuda.Event(enable_timing=True)
+  t1 = torch.cuda.Event(enable_timing=True)
+  t0.record()
+  nat.peer_wait(flags[0], world, sync[0], 20_000_000)  # 20 ms
+  t1.record()
+  torch.cuda.synchronize()
+  assert sync[0][1].item() == 1 + 2  # rank 2 was late
+  assert 10.0 < t0.elapsed_time(t1) < 2000.0
+  # latched: later waits return at once
+  t0.record()
+  nat.peer_wait(flags[0], world, sync[0], 5_000_000_000)
+  t1.record()
+  torch.cuda.synchronize()
+  assert t0.elapsed_time(t1) < 100.0
