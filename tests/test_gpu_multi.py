@@ -1,0 +1,40 @@
+"""Two GPUs: the peer-memory Ulysses exchange against the NCCL all-to-all path, eager and under CUDA
+graphs (child processes, one per GPU; skipped on a single-GPU machine)."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+@pytest.fixture(scope="module")
+def reports(tmp_path_factory):
+  if torch.cuda.device_count() < 2:
+    pytest.skip("needs two GPUs")
+  out = tmp_path_factory.mktemp("peer")
+  cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+         "127.0.0.1", "--master-port", "29641", os.path.join(HERE, "peer_worker.py"), str(out)]
+  env = dict(os.environ, NCCL_NVLS_ENABLE="0", OMP_NUM_THREADS="2")
+  proc = subprocess.run(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600)
+  assert proc.returncode == 0, proc.stdout[-3000:]
+  return [json.load(open(os.path.join(out, f"rank{r}.json"))) for r in range(2)]
+
+
+def test_peer_exchange_equals_all_to_all(reports):
+  for r in reports:
+    assert r["finite"] and r["status_peer"] == 0
+    assert r["masks_peer"] == r["masks_nccl"] and r["masks_peer"][0]
+    assert r["peer_equals_nccl"]
+  assert reports[0]["masks_peer"] == reports[1]["masks_peer"]
+
+
+def test_peer_exchange_under_cuda_graphs(reports):
+  for r in reports:
+    assert r["status_graphs"] == 0 and r["replays"] > 0
+    assert r["masks_graphs"] == r["masks_peer"]
+    assert r["graphs_equal_peer"]
