@@ -20,8 +20,8 @@ from torch import nn
 from ..caching.block_adapters import BlockAdapter, BlockAdapterRegister
 from ..caching.forward_pattern import ForwardPattern
 from .layers import (RMSNorm, TimestepMLP, UlyssesGroup, concat_gelu_linear, gated_add, gelu_linear,
-                     joint_attention, norm_modulate, norm_modulate_linears, rope_frequencies, rope_tables,
-                     timestep_embedding)
+                     joint_attention, join_tokens, norm_modulate, norm_modulate_linears, rope_frequencies,
+                     rope_tables, split_tokens, timestep_embedding)
 
 
 class AdaLayerNormZero(nn.Module):
@@ -113,13 +113,12 @@ class FluxSingleTransformerBlock(nn.Module):
   def forward(self, hidden_states, encoder_hidden_states, temb, image_rotary_emb):
     a = self.attn
     n_txt = encoder_hidden_states.shape[1]
-    x = torch.cat([encoder_hidden_states, hidden_states], dim=1)
+    x = join_tokens(encoder_hidden_states, hidden_states)
     shift, scale, gate = self.norm(temb)
     q, k, v, mlp = norm_modulate_linears(x, shift, scale, (a.to_q, a.to_k, a.to_v, self.proj_mlp))
     o = joint_attention(((q, a.norm_q), ), ((k, a.norm_k), ), (v, ), image_rotary_emb, a.heads, self.cp)
     y = concat_gelu_linear(o, mlp, self.proj_out)
-    x = gated_add(x, gate, y)
-    return x[:, :n_txt], x[:, n_txt:]
+    return split_tokens(gated_add(x, gate, y), n_txt)
 
 
 class FluxTransformer2DModel(nn.Module):

@@ -137,6 +137,25 @@ def joint_qk_norm_rope(parts: Sequence[Tuple[torch.Tensor, "RMSNorm"]], rope, he
   return apply_rope(normed[0] if len(normed) == 1 else torch.cat(normed, dim=1), rope)
 
 
+def split_tokens(x: torch.Tensor, n_first: int) -> Tuple[torch.Tensor, torch.Tensor]:
+  """x[:, :n_first], x[:, n_first:] as views that remember the tensor they were cut from, so that
+  `join_tokens` on the same pair returns it instead of copying (single-stream blocks hand the joint
+  [text; image] sequence to each other as two views)."""
+  a, b = x[:, :n_first], x[:, n_first:]
+  a._joint_parent = x
+  b._joint_parent = x
+  return a, b
+
+
+def join_tokens(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+  """cat([a, b], dim=1), without the copy when a and b are the two `split_tokens` views of one tensor."""
+  parent = getattr(a, "_joint_parent", None)
+  if parent is not None and parent is getattr(b, "_joint_parent", None) and a.shape[1] + b.shape[1] == parent.shape[1] \
+      and a.data_ptr() == parent.data_ptr():
+    return parent
+  return torch.cat([a, b], dim=1)
+
+
 def gated_add(x: torch.Tensor, gate: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
   """x + gate[:, None] * y  (x, y [B, S, C]; gate [B, C])."""
   if _glue_kernels_apply(x) and x.is_contiguous() and x.shape[-1] % 8 == 0 and y.stride(-1) == 1 \
@@ -169,8 +188,18 @@ def joint_attention(q_parts, k_parts, v_parts, rope, heads: int, cp: Optional["U
     q = joint_qk_norm_rope(q_parts, rope, heads)
     k = joint_qk_norm_rope(k_parts, rope, heads)
     d = q.shape[-1]
-    vs = [v.unflatten(-1, (heads, d)) for v in v_parts]
-    return attention(q, k, vs[0] if len(vs) == 1 else torch.cat(vs, dim=1), cp)
+    if len(v_parts) == 1:
+      v = v_parts[0].unflatten(-1, (heads, d))
+    elif _glue_kernels_apply(q) and d in (64, 128, 256):
+      # the same kernel that scatters heads across ranks, with one destination: a strided-row copy
+      v = torch.empty_like(q)
+      off = 0
+      for part in v_parts:
+        _native.scatter_heads(part, None, None, None, 0, [v.data_ptr()], v.stride(0), off, heads)
+        off += part.shape[1]
+    else:
+      v = torch.cat([part.unflatten(-1, (heads, d)) for part in v_parts], dim=1)
+    return attention(q, k, v, cp)
   x0 = q_parts[0][0]
   d = x0.shape[-1] // heads
   local_total = sum(p.shape[1] for p, _ in q_parts)

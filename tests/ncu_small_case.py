@@ -1,34 +1,73 @@
-"""Small launches of every kernel for an ncu --set full capture (a few hundred MB on the device)."""
-import sys, torch
-sys.path.insert(0, __import__('os').path.dirname(__import__('os').path.dirname(__import__('os').path.abspath(__file__))))
-from cache_dit_b200 import _native as nat
+"""Small launches of every kernel of the package for an `ncu --set full` capture (about 1 GB on the device).
+
+Run as a script.  Each kernel is launched twice (the first pass pays one-time set-up); a 256 MB buffer
+is overwritten before every launch so that DRAM counters are not flattered by L2 hits."""
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from cache_dit_b200 import _native as nat  # noqa: E402
+
 nat.lib()
-dev = 'cuda'
-S, C = 8192, 3072            # bf16 [1, 8192, 3072] = 50 MB per tensor: 2-5 tensors per kernel > L2
-mk = lambda: torch.randn(1, S, C, device=dev).to(torch.bfloat16)
-h, h0, p, d = mk(), mk(), mk(), mk()
+dev = "cuda"
+bf = torch.bfloat16
+S, C = 8192, 3072  # bf16 [1, 8192, 3072] = 50 MB per tensor: 2-5 tensors per kernel > L2
+mk = lambda *s: torch.randn(*s, device=dev).to(bf)
+h, h0, p, d = mk(1, S, C), mk(1, S, C), mk(1, S, C), mk(1, S, C)
 o, o2 = torch.empty_like(h), torch.empty_like(h)
 means = torch.zeros(2, device=dev)
 flush = torch.empty(1 << 28, dtype=torch.uint8, device=dev)
 M, K, N = 4608, 3072, 12288
-x = torch.randn(M, K, device=dev).to(torch.bfloat16)
-w = (0.02 * torch.randn(N, K, device=dev)).to(torch.bfloat16)
-aq = torch.empty(M, K, device=dev, dtype=torch.float8_e4m3fn); sa = torch.empty(M, device=dev)
-wq = torch.empty(N, K, device=dev, dtype=torch.float8_e4m3fn); sw = torch.empty(N, device=dev)
-out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+x = mk(M, K)
+w = (0.02 * torch.randn(N, K, device=dev)).to(bf)
+aq = torch.empty(M, K, device=dev, dtype=torch.float8_e4m3fn)
+sa = torch.empty(M, device=dev)
+wq = torch.empty(N, K, device=dev, dtype=torch.float8_e4m3fn)
+sw = torch.empty(N, device=dev)
+out = torch.empty(M, N, device=dev, dtype=bf)
 nat.fp8_quant_rows(w, wq, sw)
+# small-M GEMM (single-CTA kernel), text stream of a double block
+xs = mk(512, K)
+aqs = torch.empty(512, K, device=dev, dtype=torch.float8_e4m3fn)
+sas = torch.empty(512, device=dev)
+outs = torch.empty(512, N, device=dev, dtype=bf)
+nat.fp8_quant_rows(xs, aqs, sas)
+# producer-fused quantization inputs
+mod = mk(1, 6 * K)
+wide = mk(M, 21504)  # fused q/k/v + MLP-in output of a single-stream block
+attn = mk(M, K)
+aq2 = torch.empty(M, K + 12288, device=dev, dtype=torch.float8_e4m3fn)
+aq3 = torch.empty(M, 12288, device=dev, dtype=torch.float8_e4m3fn)
+# glue
+H, D = 24, 128
+cos, sin, wn = mk(M, D), mk(M, D), mk(D)
+joint = torch.empty(1, M, H, D, device=dev, dtype=bf)
+xg, yg = mk(1, M, K), mk(1, M, K)
+
+
+def launch_all():
+  steps = [
+    lambda: nat.rel_l1(h, None, p, None, means),
+    lambda: nat.rel_l1(h, h0, p, o, means),
+    lambda: nat.taylor_apply(h, [p, d], [1.0, 1.0], [1.0, 2.0], True, o),
+    lambda: nat.taylor_update(h, h0, [p], [o, o2], 1, 3.0),
+    lambda: nat.fp8_quant_rows(x, aq, sa),
+    lambda: nat.fp8_quant_rows(x, aq, sa, nat.PRE_LAYERNORM_MOD, mod[:, :K], mod[:, K:2 * K], M, 1e-6),
+    lambda: nat.fp8_quant_rows(wide[:, 9216:], aq3, sa, nat.PRE_GELU_TANH),
+    lambda: nat.fp8_quant_rows_concat_gelu(attn, wide[:, 9216:], aq2, sa),
+    lambda: nat.qk_norm_rope(wide[None, :, :K], wn, cos, sin, joint, 0, H, 1e-6),
+    lambda: nat.gated_residual(xg, mod[:, 2 * K:3 * K], yg),
+    lambda: nat.fp8_gemm_rowscaled(aq, sa, wq, sw, None, out),
+    lambda: nat.fp8_gemm_rowscaled(aqs, sas, wq, sw, None, outs),
+  ]
+  for step in steps:
+    flush.zero_()
+    step()
+
+
 for rep in range(2):
-    flush.zero_()
-    nat.rel_l1(h, None, p, None, means)
-    flush.zero_()
-    nat.rel_l1(h, h0, p, o, means)
-    flush.zero_()
-    nat.taylor_apply(h, [p, d], [1.0, 1.0], [1.0, 2.0], True, o)
-    flush.zero_()
-    nat.taylor_update(h, h0, [p], [o, o2], 1, 3.0)
-    flush.zero_()
-    nat.fp8_quant_rows(x, aq, sa)
-    flush.zero_()
-    nat.fp8_gemm_rowscaled(aq, sa, wq, sw, None, out)
+  launch_all()
 torch.cuda.synchronize()
-print('ok', means.tolist(), nat.gemm_device_status(torch.device('cuda:0')))
+print("ok", means.tolist(), nat.gemm_device_status(torch.device("cuda:0")))
