@@ -258,6 +258,95 @@ def cache_kernel_rooflines(device, hbm_peak, S=4096, C=3072, nsets=8):
   return out
 
 
+def _graph_us(fn, n=4, reps=5):
+  """Median time of one call of fn, from a CUDA graph of n back-to-back calls."""
+  for _ in range(2):
+    fn()
+  torch.cuda.synchronize()
+  g = torch.cuda.CUDAGraph()
+  with torch.cuda.graph(g):
+    for _ in range(n):
+      fn()
+  g.replay()
+  torch.cuda.synchronize()
+  ts = []
+  for _ in range(reps):
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    g.replay()
+    b.record()
+    torch.cuda.synchronize()
+    ts.append(a.elapsed_time(b) / n)
+  ts.sort()
+  return ts[len(ts) // 2] * 1e3
+
+
+def fp8_linear_sweep(device):
+  """The FP8 w8a8 per-token linear on the sweep shapes (activations N(0,1) with 0.1 % outliers x20,
+  weights N(0, 0.02) quantized per output row): TFLOP/s of the whole linear (activation quantization
+  + GEMM), of the GEMM alone, and of the library's row-wise `torch._scaled_mm` on the same operands."""
+  from cache_dit_b200 import _native as nat
+  out = {}
+  g = torch.Generator(device=device).manual_seed(0)
+  for M in (4608, 16384):
+    for K, N in ((3072, 3072), (3072, 12288), (12288, 3072), (5120, 13824)):
+      x = torch.randn(M, K, device=device, generator=g)
+      x = torch.where(torch.rand(M, K, device=device, generator=g) < 1e-3, x * 20.0, x).to(torch.bfloat16)
+      w = (0.02 * torch.randn(N, K, device=device, generator=g)).to(torch.bfloat16)
+      wq = torch.empty(N, K, device=device, dtype=torch.float8_e4m3fn)
+      sw = torch.empty(N, device=device)
+      nat.fp8_quant_rows(w, wq, sw)
+      aq = torch.empty(M, K, device=device, dtype=torch.float8_e4m3fn)
+      sa = torch.empty(M, device=device)
+      y = torch.empty(M, N, device=device, dtype=torch.bfloat16)
+
+      def linear():
+        nat.fp8_quant_rows(x, aq, sa)
+        nat.fp8_gemm_rowscaled(aq, sa, wq, sw, None, y)
+
+      flops = 2.0 * M * N * K
+      t_lin = _graph_us(linear)
+      t_gemm = _graph_us(lambda: nat.fp8_gemm_rowscaled(aq, sa, wq, sw, None, y))
+      entry = {"linear_tflops": round(flops / t_lin / 1e6, 1), "gemm_tflops": round(flops / t_gemm / 1e6, 1)}
+      try:
+        sa2, sw2 = sa.view(M, 1), sw.view(1, N)
+        t_lib = _graph_us(lambda: torch._scaled_mm(aq, wq.t(), scale_a=sa2, scale_b=sw2, out_dtype=torch.bfloat16))
+        entry["library_scaled_mm_rowwise_tflops"] = round(flops / t_lib / 1e6, 1)
+      except Exception:
+        entry["library_scaled_mm_rowwise_tflops"] = None
+      out[f"M{M}_K{K}_N{N}"] = entry
+      del x, w, wq, aq, y
+  return out
+
+
+def eager_cache_ops_us(device, S=4096, C=3072):
+  """The reference's eager PyTorch op sequences for the same four steps on the GPU (the kernels to
+  beat): similarity = sub, abs, mean, abs, mean (src/cache_dit/caching/cache_contexts/cache_manager.py:609-619);
+  Taylor approximate + add (calibrators/taylorseer.py:91-104, cache_manager.py:831); update (taylorseer.py:68-89)."""
+  mk = lambda: torch.randn(1, S, C, device=device).bfloat16()
+  h, h0, p, d = mk(), mk(), mk(), mk()
+
+  def check():
+    return ((p - h).abs().mean() / p.abs().mean())
+
+  def check_fused():
+    r = h - h0
+    return ((p - r).abs().mean() / p.abs().mean())
+
+  def apply():
+    out = torch.zeros_like(p)
+    out = out + (1.0 / 1.0) * p * (1.0**0)
+    out = out + (1.0 / 1.0) * d * (2.0**1)
+    return h + out
+
+  def update():
+    y = h - h0
+    return y, (y - p) / 3.0
+
+  return {"rel_l1_check": round(_graph_us(check), 2), "rel_l1_check_fused_residual": round(_graph_us(check_fused), 2),
+          "taylor_apply_o1": round(_graph_us(apply), 2), "taylor_update_o1": round(_graph_us(update), 2)}
+
+
 def run_ours(args):
   import torch.distributed as dist
   world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -347,7 +436,9 @@ def run_ours(args):
   cache_roof = None
   if not args.skip_extras:  # before the 2-second GEMM loop below heats the part
     cache_roof = {"flux_image_stream_1x4096x3072": cache_kernel_rooflines(device, peaks["hbm_gbs"]),
-                  "wan_rank_shard_1x9450x5120": cache_kernel_rooflines(device, peaks["hbm_gbs"], 9450, 5120, 3)}
+                  "wan_rank_shard_1x9450x5120": cache_kernel_rooflines(device, peaks["hbm_gbs"], 9450, 5120, 3),
+                  "eager_torch_ops_us_1x4096x3072": eager_cache_ops_us(device)}
+    sweep = fp8_linear_sweep(device)
   fp8_lib = fp8_library_peak(device) if not args.skip_extras else None
   achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
   # the GEMM launches are timed inside long steps under the power cap: the sustained library figure
@@ -375,6 +466,7 @@ def run_ours(args):
   }
   if not args.skip_extras:
     line["roofline_cache_kernels"] = cache_roof
+    line["fp8_linear_sweep"] = sweep
     line["roofline_cache_kernels"]["peak_source"] = f"{peak_kind} copy bandwidth (1 Gi-element copy)"
     line["cpu_baseline"] = cpu_baseline(sample_only=True, hits=len(masks[0]) if masks else None)
   if world > 1:

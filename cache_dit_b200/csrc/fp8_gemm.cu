@@ -10,8 +10,8 @@
 //     bias, bf16 pack into a swizzled shared-memory staging block, TMA store (cp.async.bulk.tensor
 //     shared -> global) of 32 x 64 blocks: whole 128-byte lines leave the SM, instead of one
 //     16-byte piece per thread and row, which kept the L1 data path as busy as the operand loads;
-//   * persistent grid (one CTA per SM), static tile order with M fastest so the CTAs of a wave
-//     share weight tiles in L2.
+//   * persistent grid (one CTA per SM), static tile order: M fastest inside groups of 16 row tiles, so
+//     the CTAs of a wave share weight tiles and a bounded set of A panels in L2.
 // Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
 // warps 2..5 = epilogue (TMEM lane quarter = warp % 4).
 //
@@ -262,6 +262,21 @@ __device__ __forceinline__ void epilogue_rows(const CUtensorMap* map_out, uint8_
   }
 }
 
+// Tile order: M fastest inside groups of TILE_GROUP_M row tiles, all column tiles of a group before
+// the next group.  The CTAs of a wave then share a few weight tiles AND at most TILE_GROUP_M row
+// panels of A, so both operands are re-read from L2; with plain M-fastest order an A that does not fit
+// the L2 (M = 16384, K = 12288: 201 MB) was streamed from HBM once per column tile.
+constexpr int TILE_GROUP_M = 16;
+__device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int& mi, int& ni) {
+  const int per_group = TILE_GROUP_M * n_tiles;
+  const int group = tile / per_group;
+  const int first_m = group * TILE_GROUP_M;
+  const int rows = min(TILE_GROUP_M, m_tiles - first_m);  // the last group may be short
+  const int in_group = tile - group * per_group;
+  mi = first_m + in_group % rows;
+  ni = in_group / rows;
+}
+
 // ---- kernel --------------------------------------------------------------------------------
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
     fp8_gemm_rowscaled_kernel(const __grid_constant__ CUtensorMap map_a,
@@ -316,8 +331,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       uint32_t it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % m_tiles) * BM;
-        const int n0 = (tile / m_tiles) * BN;
+        int mi, ni;
+        tile_coords(tile, m_tiles, n_tiles, mi, ni);
+        const int m0 = mi * BM, n0 = ni * BN;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
@@ -384,8 +400,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     uint32_t local_tile = 0, blocks_done = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
-      const int m0 = (tile % m_tiles) * BM;
-      const int n0 = (tile / m_tiles) * BN;
+      int mi, ni;
+      tile_coords(tile, m_tiles, n_tiles, mi, ni);
+      const int m0 = mi * BM, n0 = ni * BN;
       const uint32_t buf = local_tile & 1u;
       const uint32_t use = local_tile >> 1;
       // (1) the previous tile's readers of the staged column scales are done
@@ -569,8 +586,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
       uint32_t it = 0;
       bool ok = true;
       for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
-        const int m0 = (tile % m_tiles) * P_BM + (int)rank * 128;
-        const int n0 = (tile / m_tiles) * BN + (int)rank * 128;
+        int mi, ni;
+        tile_coords(tile, m_tiles, n_tiles, mi, ni);
+        const int m0 = mi * P_BM + (int)rank * 128;
+        const int n0 = ni * BN + (int)rank * 128;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % P_STAGES;
           const uint32_t ph = (it / P_STAGES) & 1u;
@@ -642,8 +661,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
     uint32_t local_tile = 0, blocks_done = 0;
     bool ok = true;
     for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs, ++local_tile) {
-      const int m0 = (tile % m_tiles) * P_BM + (int)rank * 128;
-      const int n0 = (tile / m_tiles) * BN;
+      int mi, ni;
+      tile_coords(tile, m_tiles, n_tiles, mi, ni);
+      const int m0 = mi * P_BM + (int)rank * 128;
+      const int n0 = ni * BN;
       const uint32_t buf = local_tile & 1u;
       const uint32_t use = local_tile >> 1;
       asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");

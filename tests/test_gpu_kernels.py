@@ -313,3 +313,47 @@ def test_fp8_gemm_on_model_shapes(nat, M, N, K):
     want = F.scaled_mm(aq[rows].view(torch.uint8).cpu().numpy(), sa[rows].cpu().numpy(),
                        wq.view(torch.uint8).cpu().numpy(), sw.cpu().numpy())
     assert rel_fro(out[rows].float().cpu().numpy(), want) < 2e-3
+
+
+# ------------------------------------------------------------------------------ against the library ops the reference calls
+@pytest.mark.parametrize("M,N,K,bias", [(300, 264, 256, False), (4608, 3072, 3072, True), (1000, 12288, 3072, False)])
+def test_fp8_gemm_matches_library_scaled_mm(nat, M, N, K, bias):
+  """`torch._scaled_mm` with row-wise scales is the call the reference makes for this product
+  (src/cache_dit/quantization/torchao/_scaled_mm.py:72-91).  Same quantized operands in both."""
+  g = torch.Generator().manual_seed(M + N)
+  x = torch.randn(M, K, generator=g)
+  x = torch.where(torch.rand(M, K, generator=g) < 1e-3, x * 20, x).to("cuda", torch.bfloat16)
+  w = (0.02 * torch.randn(N, K, generator=g)).to("cuda", torch.bfloat16)
+  b = (0.1 * torch.randn(N, generator=g)).to("cuda", torch.bfloat16) if bias else None
+  aq = torch.empty(M, K, dtype=torch.float8_e4m3fn, device="cuda")
+  sa = torch.empty(M, dtype=torch.float32, device="cuda")
+  wq = torch.empty(N, K, dtype=torch.float8_e4m3fn, device="cuda")
+  sw = torch.empty(N, dtype=torch.float32, device="cuda")
+  nat.fp8_quant_rows(x, aq, sa)
+  nat.fp8_quant_rows(w, wq, sw)
+  out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+  nat.fp8_gemm_rowscaled(aq, sa, wq, sw, b, out)
+  try:
+    lib = torch._scaled_mm(aq, wq.t(), scale_a=sa.view(M, 1), scale_b=sw.view(1, N), bias=b, out_dtype=torch.bfloat16)
+  except Exception as e:  # the library build on this machine has no row-wise FP8 kernel
+    pytest.skip(f"torch._scaled_mm row-wise unavailable: {e}")
+  err = (out.float() - lib.float()).norm() / lib.float().norm()
+  assert err.item() < 2e-3, err.item()  # both round an fp32 accumulation to bf16; bound of the path is 2e-2
+
+
+@pytest.mark.parametrize("rows,cols", [(64, 3072), (33, 5120)])
+def test_fp8_quant_matches_torch_cast_pipeline(nat, rows, cols):
+  """Per-row dynamic quantization written with torch's own ops and its e4m3 cast, the primitives the
+  reference's torchao configuration lowers to (PerRow, e4m3: src/cache_dit/quantization/torchao/quantize_ao.py:540-558;
+  zero scale -> 1 at :43-71)."""
+  x_d, _ = activations(rows, cols, 21)
+  x_d[3].zero_()
+  q = torch.empty(rows, cols, dtype=torch.float8_e4m3fn, device="cuda")
+  s = torch.empty(rows, dtype=torch.float32, device="cuda")
+  nat.fp8_quant_rows(x_d, q, s)
+  xf = x_d.float()
+  scale = xf.abs().amax(dim=1) / 448.0
+  scale = torch.where(scale == 0, torch.ones_like(scale), scale)
+  want = (xf / scale[:, None]).clamp(-448.0, 448.0).to(torch.float8_e4m3fn)
+  assert torch.equal(s, scale)
+  assert torch.equal(q.view(torch.uint8), want.view(torch.uint8))
