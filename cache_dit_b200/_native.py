@@ -46,9 +46,10 @@ SIGNATURES = {
   "cdb_peer_export": (c_int, [c_void_p, c_char_p]),
   "cdb_peer_import": (c_int, [c_char_p, POINTER(c_void_p)]),
   "cdb_peer_release": (c_int, [c_void_p]),
-  "cdb_scatter_heads": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int64,
+  "cdb_scatter_heads": (c_int, [c_void_p, c_int64, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int64,
                                 c_int64, c_int64, c_int64, c_int, c_int, c_float, c_void_p]),
-  "cdb_gather_tokens": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int64, c_int64, c_int, c_int, c_void_p]),
+  "cdb_gather_tokens": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int64, c_int64, c_void_p, c_int64, c_int, c_int,
+                                c_void_p]),
   "cdb_peer_sync_bytes": (c_size_t, []),
   "cdb_peer_signal": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p]),
   "cdb_peer_wait": (c_int, [c_void_p, c_int, c_void_p, c_uint64, c_void_p]),
@@ -303,7 +304,7 @@ def peer_enable_access(peer_device: int):
 
 
 def scatter_heads(x, norm_weight, cos, sin, table_row_offset: int, dst_ptrs, dst_batch_stride: int,
-                  dst_row_offset: int, heads: int, eps: float = 0.0):
+                  dst_row_offset: int, heads: int, eps: float = 0.0, across_heads: bool = False):
   """x [batch, tokens, heads*head_dim] bf16 -> head h into rank h // (heads/world)'s joint buffer
   (see cdb_scatter_heads).  norm_weight None copies, else per-head RMSNorm + rotary embedding first."""
   _need_cuda(x, norm_weight, cos, sin)
@@ -313,18 +314,27 @@ def scatter_heads(x, norm_weight, cos, sin, table_row_offset: int, dst_ptrs, dst
     raise RuntimeError("scatter_heads: x must be bf16 with unit column stride and uniformly strided rows")
   if norm_weight is not None:
     _need_contig(norm_weight, cos, sin)
-  st = lib().cdb_scatter_heads(_ptr(x), x.stride(1), _ptr(norm_weight), _ptr(cos), _ptr(sin), int(table_row_offset),
+  if norm_weight is not None and norm_weight.numel() != (c if across_heads else d):
+    raise RuntimeError("scatter_heads: norm weight is [head_dim] per head or [heads*head_dim] across heads")
+  st = lib().cdb_scatter_heads(_ptr(x), x.stride(1), _ptr(norm_weight), int(bool(across_heads)), _ptr(cos), _ptr(sin),
+                               int(table_row_offset),
                                _ptr_array(dst_ptrs), len(dst_ptrs), int(dst_batch_stride), b * t, t,
                                int(dst_row_offset), heads, d, float(eps), _stream(x))
   check(st, "cdb_scatter_heads")
 
 
-def gather_tokens(o, dst_ptrs, my_rank: int):
-  """o [batch, tokens_all, heads_per_rank, head_dim] contiguous -> token rows into their owners' buffers."""
+def gather_tokens(o, dst_ptrs, my_rank: int, row_starts=None, dst_token_capacity=None):
+  """o [batch, tokens_all, heads_per_rank, head_dim] contiguous -> token rows into their owners' buffers
+  ([batch, dst_token_capacity, heads, head_dim]); `row_starts` (world + 1 ints) for unequal token ranges."""
   _need_cuda(o)
   _need_contig(o)
   b, s, h, d = o.shape
-  st = lib().cdb_gather_tokens(_ptr(o), _ptr_array(dst_ptrs), len(dst_ptrs), int(my_rank), b, s, h, d, _stream(o))
+  world = len(dst_ptrs)
+  starts = None if row_starts is None else (c_int64 * (world + 1))(*[int(v) for v in row_starts])
+  if dst_token_capacity is None:
+    dst_token_capacity = s // world if row_starts is None else max(row_starts[r + 1] - row_starts[r] for r in range(world))
+  st = lib().cdb_gather_tokens(_ptr(o), _ptr_array(dst_ptrs), world, int(my_rank), b, s, starts,
+                               int(dst_token_capacity), h, d, _stream(o))
   check(st, "cdb_gather_tokens")
 
 

@@ -33,18 +33,24 @@ constexpr int SC_PK = 4;
 
 // One CTA per token (grid-stride).  Packets of 8 elements; LPH = head_dim / 8 packets per head.
 // Head h goes to rank h / heads_per_rank, as local head h % heads_per_rank, at joint row
-// dst_row_offset + (token index inside its batch).  NORM_ROPE = false copies (the v projection).
-template <int LPH, bool NORM_ROPE>
+// dst_row_offset + (token index inside its batch).
+//   MODE 0  copy (the v projection)
+//   MODE 1  RMSNorm over each head (weight [head_dim]) + rotary embedding   (FLUX, Qwen-Image)
+//   MODE 2  RMSNorm over the whole row (weight [heads * head_dim]) + rotary embedding   (Wan)
+constexpr int SCATTER_COPY = 0, SCATTER_HEAD_NORM = 1, SCATTER_ROW_NORM = 2;
+template <int LPH, int MODE>
 __global__ void __launch_bounds__(SC_THREADS)
     scatter_heads_kernel(const __nv_bfloat16* __restrict__ x, int64_t ld_x, const __nv_bfloat16* __restrict__ w,
                          const __nv_bfloat16* __restrict__ cs, const __nv_bfloat16* __restrict__ sn, int table_row_offset,
                          const PeerPtrs dst, int heads_per_rank, int64_t ld_out, int64_t out_batch_stride,
                          int64_t tokens, int64_t tokens_per_batch, int64_t dst_row_offset, int heads, float eps) {
   constexpr int D = LPH * 8;
+  constexpr bool NORM_ROPE = MODE != SCATTER_COPY;
   const int npk = heads * LPH;
   const int in_head = threadIdx.x % LPH;
+  __shared__ float s_part[SC_THREADS / 32];
   uint32_t ww[4] = {0, 0, 0, 0};
-  if constexpr (NORM_ROPE) {
+  if constexpr (MODE == SCATTER_HEAD_NORM) {
     const uint4 wv = __ldg(reinterpret_cast<const uint4*>(w) + in_head);
     ww[0] = wv.x; ww[1] = wv.y; ww[2] = wv.z; ww[3] = wv.w;
   }
@@ -60,6 +66,27 @@ __global__ void __launch_bounds__(SC_THREADS)
       cw[0] = cv.x; cw[1] = cv.y; cw[2] = cv.z; cw[3] = cv.w;
       sw[0] = sv.x; sw[1] = sv.y; sw[2] = sv.z; sw[3] = sv.w;
     }
+    float rstd_row = 0.f;
+    if constexpr (MODE == SCATTER_ROW_NORM) {  // statistic of the whole row first (the row is re-read from L2 below)
+      float ss = 0.f;
+      for (int p = threadIdx.x; p < npk; p += SC_THREADS) {
+        const uint4 q = __ldg(src + p);
+        const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float lo = __uint_as_float(qw[i] << 16), hi = __uint_as_float(qw[i] & 0xffff0000u);
+          ss += lo * lo + hi * hi;
+        }
+      }
+      ss = warp_sum(ss);
+      __syncthreads();  // the previous token's readers of s_part are done
+      if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = ss;
+      __syncthreads();
+      float tot = 0.f;
+#pragma unroll
+      for (int i = 0; i < SC_THREADS / 32; ++i) tot += s_part[i];
+      rstd_row = rsqrtf(tot / (float)(heads * D) + eps);
+    }
     for (int base = 0; base < npk; base += SC_THREADS * SC_PK) {
       uint4 v[SC_PK];
 #pragma unroll
@@ -72,15 +99,21 @@ __global__ void __launch_bounds__(SC_THREADS)
         const int p = base + j * SC_THREADS + threadIdx.x;
         uint32_t ow[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
         if constexpr (NORM_ROPE) {
-          float ss = 0.f;
+          float rstd = rstd_row;
+          if constexpr (MODE == SCATTER_HEAD_NORM) {
+            float ss = 0.f;
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const float lo = __uint_as_float(ow[i] << 16), hi = __uint_as_float(ow[i] & 0xffff0000u);
-            ss += lo * lo + hi * hi;
+            for (int i = 0; i < 4; ++i) {
+              const float lo = __uint_as_float(ow[i] << 16), hi = __uint_as_float(ow[i] & 0xffff0000u);
+              ss += lo * lo + hi * hi;
+            }
+#pragma unroll
+            for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            rstd = rsqrtf(ss / (float)D + eps);
+          } else if (p < npk) {  // row norm: the weight differs per packet
+            const uint4 wv = __ldg(reinterpret_cast<const uint4*>(w) + p);
+            ww[0] = wv.x; ww[1] = wv.y; ww[2] = wv.z; ww[3] = wv.w;
           }
-#pragma unroll
-          for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-          const float rstd = rsqrtf(ss / (float)D + eps);
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const float lo = __uint_as_float(ow[i] << 16), hi = __uint_as_float(ow[i] & 0xffff0000u);
@@ -104,20 +137,28 @@ __global__ void __launch_bounds__(SC_THREADS)
 }
 
 // Attention output of this rank, [batch, all tokens, own heads, head_dim]: the row of token s goes
-// to rank s / tokens_per_rank, into its [batch, own tokens, all heads, head_dim] buffer at head
-// offset my_rank * heads_per_rank.  One CTA per (batch, token) row, 16-byte packets.
+// to the rank whose token range [row_start[r], row_start[r+1]) holds s, into its
+// [batch, token capacity, all heads, head_dim] buffer at head offset my_rank * heads_per_rank.
+// Ranges may differ in length (token counts that do not divide by the number of ranks).
+// One CTA per (batch, token) row, 16-byte packets.
+struct PeerRows {
+  int64_t start[PEER_MAX + 1];
+};
+
 __global__ void __launch_bounds__(128)
-    gather_tokens_kernel(const __nv_bfloat16* __restrict__ o, const PeerPtrs dst, int my_rank, int64_t batch,
-                         int64_t tokens_all, int64_t tokens_per_rank, int heads_per_rank, int heads_all, int head_dim) {
+    gather_tokens_kernel(const __nv_bfloat16* __restrict__ o, const PeerPtrs dst, const PeerRows rows_of, int world,
+                         int my_rank, int64_t batch, int64_t tokens_all, int64_t dst_token_capacity,
+                         int heads_per_rank, int heads_all, int head_dim) {
   const int row_packets = heads_per_rank * head_dim / 8;
   const int64_t rows = batch * tokens_all;
   for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
     const int64_t b = r / tokens_all, s = r - b * tokens_all;
-    const int owner = (int)(s / tokens_per_rank);
-    const int64_t local_s = s - (int64_t)owner * tokens_per_rank;
+    int owner = 0;
+    while (owner + 1 < world && s >= rows_of.start[owner + 1]) ++owner;
+    const int64_t local_s = s - rows_of.start[owner];
     const uint4* src = reinterpret_cast<const uint4*>(o + r * (int64_t)heads_per_rank * head_dim);
     __nv_bfloat16* base_ptr = static_cast<__nv_bfloat16*>(dst.p[owner]);
-    uint4* out = reinterpret_cast<uint4*>(base_ptr + ((b * tokens_per_rank + local_s) * heads_all +
+    uint4* out = reinterpret_cast<uint4*>(base_ptr + ((b * dst_token_capacity + local_s) * heads_all +
                                                       (int64_t)my_rank * heads_per_rank) * head_dim);
     for (int p = threadIdx.x; p < row_packets; p += blockDim.x) out[p] = __ldcs(src + p);
   }
@@ -247,8 +288,9 @@ extern "C" int cdb_peer_release(void* imported) {
   return CDB_OK;
 }
 
-extern "C" int cdb_scatter_heads(const void* x, int64_t ld_x, const void* norm_weight, const void* cos_table,
-                                 const void* sin_table, int table_row_offset, void* const* dst_ptrs, int world,
+extern "C" int cdb_scatter_heads(const void* x, int64_t ld_x, const void* norm_weight, int norm_across_heads,
+                                 const void* cos_table, const void* sin_table, int table_row_offset,
+                                 void* const* dst_ptrs, int world,
                                  int64_t dst_batch_stride, int64_t tokens, int64_t tokens_per_batch,
                                  int64_t dst_row_offset, int heads, int head_dim, float eps, void* stream) {
   PeerPtrs dst;
@@ -270,36 +312,49 @@ extern "C" int cdb_scatter_heads(const void* x, int64_t ld_x, const void* norm_w
   const __nv_bfloat16* wp = static_cast<const __nv_bfloat16*>(norm_weight);
   const __nv_bfloat16* cp = static_cast<const __nv_bfloat16*>(cos_table);
   const __nv_bfloat16* sp = static_cast<const __nv_bfloat16*>(sin_table);
-#define CDB_SC(LPH, NR)                                                                                     \
-  scatter_heads_kernel<LPH, NR><<<grid, SC_THREADS, 0, st>>>(xp, ld_x, wp, cp, sp, table_row_offset, dst, hpr, \
-                                                             ld_out, dst_batch_stride, tokens, tokens_per_batch, \
-                                                             dst_row_offset, heads, eps)
-  if (norm) {
-    if (head_dim == 64) CDB_SC(8, true);
-    else if (head_dim == 128) CDB_SC(16, true);
-    else CDB_SC(32, true);
-  } else {
-    if (head_dim == 64) CDB_SC(8, false);
-    else if (head_dim == 128) CDB_SC(16, false);
-    else CDB_SC(32, false);
-  }
+#define CDB_SC(LPH, MODE)                                                                                     \
+  scatter_heads_kernel<LPH, MODE><<<grid, SC_THREADS, 0, st>>>(xp, ld_x, wp, cp, sp, table_row_offset, dst, hpr, \
+                                                               ld_out, dst_batch_stride, tokens, tokens_per_batch, \
+                                                               dst_row_offset, heads, eps)
+#define CDB_SC_DIM(MODE)                  \
+  if (head_dim == 64) CDB_SC(8, MODE);    \
+  else if (head_dim == 128) CDB_SC(16, MODE); \
+  else CDB_SC(32, MODE)
+  if (!norm) { CDB_SC_DIM(SCATTER_COPY); }
+  else if (norm_across_heads) { CDB_SC_DIM(SCATTER_ROW_NORM); }
+  else { CDB_SC_DIM(SCATTER_HEAD_NORM); }
+#undef CDB_SC_DIM
 #undef CDB_SC
   CDB_CUDA_CHECK(cudaGetLastError());
   return CDB_OK;
 }
 
 extern "C" int cdb_gather_tokens(const void* o, void* const* dst_ptrs, int world, int my_rank, int64_t batch,
-                                 int64_t tokens_all, int heads_per_rank, int head_dim, void* stream) {
+                                 int64_t tokens_all, const int64_t* row_starts, int64_t dst_token_capacity,
+                                 int heads_per_rank, int head_dim, void* stream) {
   PeerPtrs dst;
   if (!o || batch <= 0 || tokens_all <= 0 || heads_per_rank <= 0 || my_rank < 0 || my_rank >= world ||
       !fill_ptrs(&dst, dst_ptrs, world))
     return CDB_ERR_BAD_ARGUMENT;
-  if (tokens_all % world != 0 || (heads_per_rank * head_dim) % 8 != 0 || !aligned16(o)) return CDB_ERR_UNSUPPORTED;
+  if ((heads_per_rank * head_dim) % 8 != 0 || !aligned16(o)) return CDB_ERR_UNSUPPORTED;
+  PeerRows rows_of{};
+  if (row_starts) {
+    for (int r = 0; r <= world; ++r) rows_of.start[r] = row_starts[r];
+    if (rows_of.start[0] != 0 || rows_of.start[world] != tokens_all) return CDB_ERR_BAD_ARGUMENT;
+    for (int r = 0; r < world; ++r) {
+      const int64_t len = rows_of.start[r + 1] - rows_of.start[r];
+      if (len < 0 || len > dst_token_capacity) return CDB_ERR_BAD_ARGUMENT;
+    }
+  } else {  // equal ranges
+    if (tokens_all % world != 0) return CDB_ERR_BAD_ARGUMENT;
+    for (int r = 0; r <= world; ++r) rows_of.start[r] = tokens_all / world * r;
+    if (dst_token_capacity < tokens_all / world) return CDB_ERR_BAD_ARGUMENT;
+  }
   const int64_t rows = batch * tokens_all;
   const int64_t cap = (int64_t)sm_count() * 16;
   gather_tokens_kernel<<<(unsigned)(rows < cap ? rows : cap), 128, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(o), dst, my_rank, batch, tokens_all, tokens_all / world, heads_per_rank,
-      heads_per_rank * world, head_dim);
+      static_cast<const __nv_bfloat16*>(o), dst, rows_of, world, my_rank, batch, tokens_all, dst_token_capacity,
+      heads_per_rank, heads_per_rank * world, head_dim);
   CDB_CUDA_CHECK(cudaGetLastError());
   return CDB_OK;
 }

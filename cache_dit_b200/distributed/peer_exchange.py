@@ -78,6 +78,8 @@ class PeerExchange:
     return own, ptrs
 
   def ensure(self, batch: int, tokens_local: int, heads: int, head_dim: int, dtype: torch.dtype):
+    """Allocate (first call, collective) the exchange buffers for this attention shape.  Ranks may hold
+    different numbers of tokens; everyone learns all counts here."""
     key = (batch, tokens_local, heads, head_dim, dtype)
     if key == self._shape_key:
       return
@@ -86,25 +88,33 @@ class PeerExchange:
                          f"(have {self._shape_key}, asked for {key})")
     if heads % self.world:
       raise ValueError(f"heads ({heads}) must divide by the Ulysses degree ({self.world})")
+    counts = [None] * self.world
+    dist.all_gather_object(counts, int(tokens_local), group=self.group)
+    self.row_starts = [0]
+    for c in counts:
+      self.row_starts.append(self.row_starts[-1] + c)
+    self.tokens_local = tokens_local
+    self.capacity = max(counts)
+    self.uneven = len(set(counts)) > 1
     esz = torch.empty((), dtype=dtype).element_size()
-    hpr, all_tokens = heads // self.world, tokens_local * self.world
+    hpr, all_tokens = heads // self.world, self.row_starts[-1]
     for name in ("q", "k", "v"):
       shape = (batch, all_tokens, hpr, head_dim)
       own, self.ptrs[name] = self._alloc_shared(batch * all_tokens * hpr * head_dim * esz)
       self.buffers[name] = _as_tensor(own, shape, dtype, self.device)
-    shape = (batch, tokens_local, heads, head_dim)
-    own, self.ptrs["o"] = self._alloc_shared(batch * tokens_local * heads * head_dim * esz)
+    shape = (batch, self.capacity, heads, head_dim)
+    own, self.ptrs["o"] = self._alloc_shared(batch * self.capacity * heads * head_dim * esz)
     self.buffers["o"] = _as_tensor(own, shape, dtype, self.device)
     self._shape_key = key
     dist.barrier(group=self.group)
 
   # ---- launches
-  def scatter(self, name: str, x: torch.Tensor, heads: int, row_offset_local: int, tokens_local_total: int,
-              norm_weight=None, cos=None, sin=None, eps: float = 0.0):
+  def scatter(self, name: str, x: torch.Tensor, heads: int, row_offset_local: int, norm_weight=None, cos=None,
+              sin=None, eps: float = 0.0, across_heads: bool = False):
     """x [batch, t, heads*head_dim]: this rank's rows [row_offset_local, +t) of its token shard."""
     buf = self.buffers[name]
     _native.scatter_heads(x, norm_weight, cos, sin, row_offset_local, self.ptrs[name], buf.stride(0),
-                          self.rank * tokens_local_total + row_offset_local, heads, eps)
+                          self.row_starts[self.rank] + row_offset_local, heads, eps, across_heads)
 
   def barrier(self):
     _native.peer_signal(self.flag_ptrs, self.rank, self.sync, self.flags)
@@ -112,9 +122,10 @@ class PeerExchange:
 
   def gather_output(self, o_local: torch.Tensor) -> torch.Tensor:
     """o_local [batch, tokens_all, heads / W, head_dim] -> this rank's `o` buffer after the exchange."""
-    _native.gather_tokens(o_local, self.ptrs["o"], self.rank)
+    _native.gather_tokens(o_local, self.ptrs["o"], self.rank, self.row_starts, self.capacity)
     self.barrier()
-    return self.buffers["o"]
+    out = self.buffers["o"]
+    return out if self.tokens_local == self.capacity else out[:, :self.tokens_local]
 
   def status(self) -> int:
     """0, or 1 + the index of a peer whose signal did not arrive within the timeout (synchronises)."""

@@ -5,4 +5,6 @@ flow so that the cache engine, the FP8 linears and the context-parallel plan can
 Importing this package registers their block adapters.
 """
 from .flux import FluxSingleTransformerBlock, FluxTransformer2DModel, FluxTransformerBlock
+from .qwen_image import QwenImageTransformer2DModel, QwenImageTransformerBlock
+from .wan import WanTransformer3DModel, WanTransformerBlock
 from .pipeline import DenoisePipeline, FluxDenoisePipeline, QwenImageDenoisePipeline, WanDenoisePipeline

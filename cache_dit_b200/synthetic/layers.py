@@ -118,11 +118,13 @@ def _glue_kernels_apply(x: torch.Tensor) -> bool:
   return x.is_cuda and x.dtype == torch.bfloat16
 
 
-def joint_qk_norm_rope(parts: Sequence[Tuple[torch.Tensor, "RMSNorm"]], rope, heads: int) -> torch.Tensor:
-  """RoPE(concat over tokens of per-head RMSNorm(part)) -> [B, S_total, H, D].
+def joint_qk_norm_rope(parts: Sequence[Tuple[torch.Tensor, "RMSNorm"]], rope, heads: int,
+                       across_heads: bool = False) -> torch.Tensor:
+  """RoPE(concat over tokens of RMSNorm(part)) -> [B, S_total, H, D].
 
-  `parts` are the projections [B, T_i, H*D] in sequence order (text first), each with its norm.  On
-  the GPU this is one kernel per part writing straight into the joint buffer; elsewhere the eager ops."""
+  `parts` are the projections [B, T_i, H*D] in sequence order (text first), each with its norm: per
+  head with weight [D], or (`across_heads`) over the whole row with weight [H*D].  On the GPU this is one
+  kernel per part writing straight into the joint buffer; elsewhere the eager ops."""
   x0 = parts[0][0]
   d = x0.shape[-1] // heads
   total = sum(p.shape[1] for p, _ in parts)
@@ -130,10 +132,14 @@ def joint_qk_norm_rope(parts: Sequence[Tuple[torch.Tensor, "RMSNorm"]], rope, he
     out = torch.empty(x0.shape[0], total, heads, d, device=x0.device, dtype=x0.dtype)
     off = 0
     for x, norm in parts:
-      _native.qk_norm_rope(x, norm.weight, rope[0], rope[1], out, off, heads, norm.eps)
+      _native.scatter_heads(x, norm.weight, rope[0], rope[1], off, [out.data_ptr()], out.stride(0), off, heads,
+                            norm.eps, across_heads)
       off += x.shape[1]
     return out
-  normed = [norm(x.unflatten(-1, (heads, d))) for x, norm in parts]
+  if across_heads:
+    normed = [norm(x).unflatten(-1, (heads, d)) for x, norm in parts]
+  else:
+    normed = [norm(x.unflatten(-1, (heads, d))) for x, norm in parts]
   return apply_rope(normed[0] if len(normed) == 1 else torch.cat(normed, dim=1), rope)
 
 
@@ -176,7 +182,8 @@ class UlyssesGroup:
     self.exchange = exchange
 
 
-def joint_attention(q_parts, k_parts, v_parts, rope, heads: int, cp: Optional["UlyssesGroup"] = None) -> torch.Tensor:
+def joint_attention(q_parts, k_parts, v_parts, rope, heads: int, cp: Optional["UlyssesGroup"] = None,
+                    across_heads: bool = False) -> torch.Tensor:
   """Attention over the concatenation (text first) of the given projections.
 
   q_parts / k_parts: sequences of (projection [B, T_i, H*D], RMSNorm module); v_parts: projections.
@@ -185,8 +192,8 @@ def joint_attention(q_parts, k_parts, v_parts, rope, heads: int, cp: Optional["U
   the head scatter to the other GPUs."""
   ex = cp.exchange if cp is not None and cp.world > 1 else None
   if ex is None:
-    q = joint_qk_norm_rope(q_parts, rope, heads)
-    k = joint_qk_norm_rope(k_parts, rope, heads)
+    q = joint_qk_norm_rope(q_parts, rope, heads, across_heads)
+    k = joint_qk_norm_rope(k_parts, rope, heads, across_heads)
     d = q.shape[-1]
     if len(v_parts) == 1:
       v = v_parts[0].unflatten(-1, (heads, d))
@@ -207,11 +214,11 @@ def joint_attention(q_parts, k_parts, v_parts, rope, heads: int, cp: Optional["U
   for name, parts in (("q", q_parts), ("k", k_parts)):
     off = 0
     for x, norm in parts:
-      ex.scatter(name, x, heads, off, local_total, norm.weight, rope[0], rope[1], norm.eps)
+      ex.scatter(name, x, heads, off, norm.weight, rope[0], rope[1], norm.eps, across_heads)
       off += x.shape[1]
   off = 0
   for x in v_parts:
-    ex.scatter("v", x, heads, off, local_total)
+    ex.scatter("v", x, heads, off)
     off += x.shape[1]
   ex.barrier()
   b = ex.buffers
@@ -220,29 +227,56 @@ def joint_attention(q_parts, k_parts, v_parts, rope, heads: int, cp: Optional["U
   return ex.gather_output(o).flatten(2)
 
 
-def _all_to_all(x: torch.Tensor, scatter_dim: int, gather_dim: int, cp: UlyssesGroup) -> torch.Tensor:
-  """Split `scatter_dim` over the ranks and concatenate what arrives along `gather_dim`."""
+def _all_to_all(x: torch.Tensor, scatter_dim: int, gather_dim: int, cp: UlyssesGroup, counts=None) -> torch.Tensor:
+  """Split `scatter_dim` over the ranks and concatenate what arrives along `gather_dim`.
+
+  x is [B, tokens, heads, D].  `counts` = token counts of all ranks when they differ (None: equal):
+  scattering heads (dim 2) then receives `counts[r]` tokens from rank r; scattering tokens (dim 1)
+  splits them by `counts`."""
   import torch.distributed as dist
   w = cp.world
-  chunks = [c.contiguous() for c in x.chunk(w, dim=scatter_dim)]
+
+  def split(t):
+    parts = t.split(list(counts), dim=1) if counts is not None and scatter_dim == 1 else t.chunk(w, dim=scatter_dim)
+    return [c.contiguous() for c in parts]
+
+  send = split(x)
   if dist.get_backend(cp.group) == "gloo":
-    # gloo has no all-to-all: gather everything and keep this rank's slices (CPU tests only)
-    everything = [torch.empty_like(x) for _ in range(w)]
-    dist.all_gather(everything, x.contiguous(), group=cp.group)
-    recv = [e.chunk(w, dim=scatter_dim)[cp.rank] for e in everything]
+    # gloo has no all-to-all: every rank publishes its tensor and keeps its slices (CPU tests only)
+    everything = [None] * w
+    dist.all_gather_object(everything, x.contiguous(), group=cp.group)
+    recv = [split(e)[cp.rank] for e in everything]
   else:
-    recv = [torch.empty_like(chunks[0]) for _ in range(w)]
-    dist.all_to_all(recv, chunks, group=cp.group)
+    recv = []
+    for r in range(w):
+      shape = list(send[cp.rank].shape)
+      if counts is not None and scatter_dim == 2:
+        shape[1] = counts[r]
+      recv.append(torch.empty(shape, dtype=x.dtype, device=x.device))
+    dist.all_to_all(recv, send, group=cp.group)
   return torch.cat(recv, dim=gather_dim)
+
+
+def _token_counts(local_tokens: int, cp: UlyssesGroup):
+  """Token counts of all ranks, or None when they are equal (cached per local count)."""
+  import torch.distributed as dist
+  cache = cp.__dict__.setdefault("_token_counts", {})
+  if local_tokens not in cache:
+    counts = [None] * cp.world
+    dist.all_gather_object(counts, int(local_tokens), group=cp.group)
+    cache[local_tokens] = None if len(set(counts)) == 1 else counts
+  return cache[local_tokens]
 
 
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cp: Optional[UlyssesGroup] = None) -> torch.Tensor:
   """q, k, v [B, S_local, H, D] -> [B, S_local, H*D].  Under Ulysses the heads are exchanged for the
   full sequence before the attention kernel and back after it (four all-to-alls)."""
+  counts = None
   if cp is not None and cp.world > 1:
-    q, k, v = (_all_to_all(t, 2, 1, cp) for t in (q, k, v))  # [B, S, H/W, D]
+    counts = _token_counts(q.shape[1], cp)
+    q, k, v = (_all_to_all(t, 2, 1, cp, counts) for t in (q, k, v))  # [B, S, H/W, D]
   o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2))
   o = o.transpose(1, 2)  # [B, S, H(/W), D]
   if cp is not None and cp.world > 1:
-    o = _all_to_all(o.contiguous(), 1, 2, cp)  # [B, S/W, H, D]
+    o = _all_to_all(o.contiguous(), 1, 2, cp, counts)  # [B, S/W, H, D]
   return o.flatten(2)

@@ -207,9 +207,12 @@ CDB_API int cdb_gated_residual(const void* x, const void* y, int64_t ld_y, const
  *   dst_row_offset + (token index in its batch), in a [batch, rows, heads/world, head_dim] buffer with
  *   batch stride dst_batch_stride.  With norm_weight != NULL the per-head RMSNorm + rotary embedding of
  *   cdb_qk_norm_rope is applied first (table row = table_row_offset + token index); with NULL it copies.
+ *   norm_across_heads != 0: the RMS statistic is taken over the whole row and norm_weight is
+ *   [heads*head_dim] (Wan's q / k normalisation) instead of per head with weight [head_dim].
  * cdb_gather_tokens: o [batch, tokens_all, heads_per_rank, head_dim] (this rank's heads, all tokens):
- *   token s goes to rank s / (tokens_all/world), into its [batch, tokens_all/world, heads_per_rank*world,
- *   head_dim] buffer at head offset my_rank*heads_per_rank.
+ *   token s goes to the rank r with row_starts[r] <= s < row_starts[r+1] (host array of world+1 entries;
+ *   NULL = equal ranges), into its [batch, dst_token_capacity, heads_per_rank*world, head_dim] buffer
+ *   at token s - row_starts[r] and head offset my_rank*heads_per_rank.  Ranges may differ in length.
  * cdb_peer_signal / cdb_peer_wait: `sync` is cdb_peer_sync_bytes() of zeroed device memory per rank;
  *   each rank owns `world` zeroed 32-bit flag words.  signal bumps the rank's epoch and stores it into
  *   word my_rank of every rank's flags; wait returns when all words of the own flags reached the own
@@ -226,12 +229,14 @@ CDB_API int cdb_peer_free(void* p);
 CDB_API int cdb_peer_export(const void* p, unsigned char* handle64);
 CDB_API int cdb_peer_import(const unsigned char* handle64, void** out);
 CDB_API int cdb_peer_release(void* imported);
-CDB_API int cdb_scatter_heads(const void* x, int64_t ld_x, const void* norm_weight, const void* cos_table,
-                      const void* sin_table, int table_row_offset, void* const* dst_ptrs, int world,
+CDB_API int cdb_scatter_heads(const void* x, int64_t ld_x, const void* norm_weight, int norm_across_heads,
+                      const void* cos_table, const void* sin_table, int table_row_offset,
+                      void* const* dst_ptrs, int world,
                       int64_t dst_batch_stride, int64_t tokens, int64_t tokens_per_batch,
                       int64_t dst_row_offset, int heads, int head_dim, float eps, void* stream);
 CDB_API int cdb_gather_tokens(const void* o, void* const* dst_ptrs, int world, int my_rank, int64_t batch,
-                      int64_t tokens_all, int heads_per_rank, int head_dim, void* stream);
+                      int64_t tokens_all, const int64_t* row_starts, int64_t dst_token_capacity,
+                      int heads_per_rank, int head_dim, void* stream);
 CDB_API size_t cdb_peer_sync_bytes(void);
 CDB_API int cdb_peer_signal(void* const* flag_ptrs, int world, int my_rank, void* sync, void* stream);
 CDB_API int cdb_peer_wait(const void* my_flags, int world, void* sync, uint64_t timeout_ns, void* stream);

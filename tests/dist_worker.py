@@ -64,11 +64,58 @@ def flux_case(rank, world):
               cached_sharded=s2.cached_steps, diffs_single=s1.residual_diffs, diffs_sharded=s2.residual_diffs)
 
 
+def _sharded_vs_single(world, build, pipe_cls, threshold):
+  def run(parallel):
+    torch.manual_seed(0)
+    model, inputs = build()
+    pipe = pipe_cls(model, inputs, separate_cfg=False)
+    cd.enable_cache(pipe, cache_config=cd.DBCacheConfig(Fn_compute_blocks=1, max_warmup_steps=2,
+                                                        residual_diff_threshold=threshold, enable_separate_cfg=False),
+                    calibrator_config=cd.TaylorSeerCalibratorConfig(),
+                    parallelism_config=cd.ParallelismConfig(ulysses_size=world) if parallel else None)
+    out = pipe(num_inference_steps=8)
+    stats = cd.summary(pipe, logging=False)[-1]
+    cd.disable_cache(pipe)
+    return out, stats
+
+  single, s1 = run(False)
+  sharded, s2 = run(True)
+  return dict(rel=float((single - sharded).norm() / single.norm()), cached_single=s1.cached_steps,
+              cached_sharded=s2.cached_steps, diffs_single=s1.residual_diffs, diffs_sharded=s2.residual_diffs)
+
+
+def qwen_case(rank, world):
+  """49 image + 5 text tokens on 2 ranks: 25 / 24 and 3 / 2, the uneven split of `ulysses_anything`."""
+  from cache_dit_b200.synthetic import QwenImageDenoisePipeline, QwenImageTransformer2DModel
+
+  def build():
+    model = QwenImageTransformer2DModel(num_layers=4, dim=64, heads=4, in_channels=8, joint_attention_dim=16,
+                                        axes_dims_rope=(4, 6, 6), time_scale=1.0, modulation_init_std=0.02)
+    return model, QwenImageTransformer2DModel.example_inputs(height=112, width=112, text_tokens=5, device="cpu",
+                                                             dtype=torch.float32, in_channels=8, joint_attention_dim=16)
+
+  return _sharded_vs_single(world, build, QwenImageDenoisePipeline, 0.3)
+
+
+def wan_case(rank, world):
+  """Video tokens sharded, text whole on every rank; blocks return hidden states only (Pattern_2)."""
+  from cache_dit_b200.synthetic import WanDenoisePipeline, WanTransformer3DModel
+
+  def build():
+    model = WanTransformer3DModel(num_layers=3, dim=64, heads=4, ffn_dim=96, in_channels=8, text_dim=16,
+                                  axes_dims_rope=(4, 6, 6), time_scale=1.0, modulation_init_std=0.02)
+    return model, WanTransformer3DModel.example_inputs(frames=3, height=4, width=5, text_tokens=6, device="cpu",
+                                                       dtype=torch.float32, in_channels=8, text_dim=16)
+
+  return _sharded_vs_single(world, build, WanDenoisePipeline, 0.3)
+
+
 def main():
   dist.init_process_group("gloo")
   rank, world = dist.get_rank(), dist.get_world_size()
   step_ops.set_ops(OracleStepOps())
-  result = dict(rank=rank, decision=decision_case(rank, world), flux=flux_case(rank, world))
+  result = dict(rank=rank, decision=decision_case(rank, world), flux=flux_case(rank, world),
+                qwen=qwen_case(rank, world), wan=wan_case(rank, world))
   with open(os.path.join(sys.argv[1], f"rank{rank}.json"), "w") as f:
     json.dump(result, f)
   dist.barrier()

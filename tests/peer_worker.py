@@ -57,6 +57,43 @@ def generation(world, exchange, graphs, steps=10):
   return result, status, replays
 
 
+def other_model(world, which, exchange, graphs, steps=8):
+  """Qwen-Image-shape (289 image + 33 text tokens: uneven shards) or Wan-shape (105 video tokens, text whole)."""
+  from cache_dit_b200.synthetic import (QwenImageDenoisePipeline, QwenImageTransformer2DModel, WanDenoisePipeline,
+                                        WanTransformer3DModel)
+  torch.manual_seed(0)
+  if which == "qwen":
+    with torch.device("cuda"):
+      model = QwenImageTransformer2DModel(num_layers=4, dim=256, heads=4, in_channels=16, joint_attention_dim=64,
+                                          axes_dims_rope=(8, 28, 28), time_scale=1.0, modulation_init_std=0.02)
+    inputs = QwenImageTransformer2DModel.example_inputs(height=272, width=272, text_tokens=33, in_channels=16,
+                                                        joint_attention_dim=64)
+    pipe = QwenImageDenoisePipeline(model, inputs)
+  else:
+    with torch.device("cuda"):
+      model = WanTransformer3DModel(num_layers=3, dim=256, heads=2, ffn_dim=512, in_channels=16, text_dim=64,
+                                    axes_dims_rope=(44, 42, 42), time_scale=1.0, modulation_init_std=0.02)
+    inputs = WanTransformer3DModel.example_inputs(frames=3, height=5, width=7, text_tokens=16, in_channels=16,
+                                                  text_dim=64)
+    pipe = WanDenoisePipeline(model, inputs)
+  model.to(torch.bfloat16).eval().requires_grad_(False)
+  cd.enable_cache(pipe, cache_config=cd.DBCacheConfig(Fn_compute_blocks=1, max_warmup_steps=3, residual_diff_threshold=0.15),
+                  calibrator_config=cd.TaylorSeerCalibratorConfig(taylorseer_order=1),
+                  parallelism_config=cd.ParallelismConfig(ulysses_size=world, parallel_kwargs={"exchange": exchange}),
+                  quantize_config=cd.QuantizeConfig(quant_type="float8_per_row"))
+  if graphs:
+    cd.enable_cuda_graphs(pipe, warmup_calls=1)
+  out = pipe(num_inference_steps=steps)
+  if graphs:
+    out = pipe(num_inference_steps=steps)
+  stats = cd.summary(pipe, logging=False)[-1]
+  torch.cuda.synchronize()
+  cp = getattr(model, "_cp", None)
+  status = cp.exchange.status() if cp is not None and cp.exchange is not None else 0
+  cd.disable_cache(pipe)
+  return out.clone(), list(stats.cached_steps), status
+
+
 def main():
   out_dir = sys.argv[1]
   rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
@@ -65,7 +102,16 @@ def main():
   nccl, _, _ = generation(world, "nccl", False)
   peer, st_peer, _ = generation(world, "peer", False)
   graphed, st_graph, replays = generation(world, "peer", True)
-  report = dict(
+  others = {}
+  for which in ("qwen", "wan"):
+    o_nccl, m_nccl, _ = other_model(world, which, "nccl", False)
+    o_peer, m_peer, st = other_model(world, which, "peer", False)
+    o_graph, m_graph, st_g = other_model(world, which, "peer", True)
+    others[which] = dict(masks=[m_nccl, m_peer, m_graph], status=[st, st_g],
+                         peer_equals_nccl=bool(torch.equal(o_nccl, o_peer)),
+                         graphs_equal_peer=bool(torch.equal(o_peer, o_graph)),
+                         finite=bool(torch.isfinite(o_peer).all().item()))
+  report = dict(others=others,
     masks_nccl=[m for _, m in nccl], masks_peer=[m for _, m in peer], masks_graphs=[m for _, m in graphed],
     peer_equals_nccl=all(torch.equal(a, b) for (a, _), (b, _) in zip(nccl, peer)),
     graphs_equal_peer=all(torch.equal(a, b) for (a, _), (b, _) in zip(peer, graphed)),

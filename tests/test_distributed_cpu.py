@@ -41,3 +41,17 @@ def test_context_parallel_matches_single_rank(results):
       # equal shards: mean of local means equals the global mean up to float rounding
       assert abs(f["diffs_sharded"][k] - v) <= 2e-3 * abs(v) + 1e-9
   assert results[0]["flux"]["cached_sharded"] == results[1]["flux"]["cached_sharded"]
+
+
+@pytest.mark.parametrize("model", ["qwen", "wan"])
+def test_other_model_plans_match_single_rank(results, model):
+  """Qwen-Image-shape: uneven token split (25/24 image, 3/2 text); Wan-shape: video sharded, text whole."""
+  for r in results:
+    f = r[model]
+    assert f["cached_single"] == f["cached_sharded"] and f["cached_single"]
+    assert f["rel"] < 2e-3
+    for k, v in f["diffs_single"].items():
+      # mean of local means vs global mean: equal up to float rounding for equal shards, and within
+      # the shard-size imbalance (1 token in 25) times the spread of per-token means otherwise
+      assert abs(f["diffs_sharded"][k] - v) <= 2e-2 * abs(v) + 1e-9
+  assert results[0][model]["cached_sharded"] == results[1][model]["cached_sharded"]

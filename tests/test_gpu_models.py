@@ -1,0 +1,113 @@
+"""Qwen-Image- and Wan-shape stand-ins on a B200: the product path (kernels, FP8 linears, separate CFG)
+against the numpy oracle plugged into the same runner, CUDA-graph replay against eager launches,
+and the row-norm mode of the head-scatter kernel against eager PyTorch."""
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as F
+
+import cache_dit_b200 as cd
+from cache_dit_b200.caching import step_ops
+from tests.fake_ops import OracleStepOps
+
+pytestmark = pytest.mark.gpu
+
+
+def _qwen():
+  from cache_dit_b200.synthetic import QwenImageDenoisePipeline, QwenImageTransformer2DModel
+  with torch.device("cuda"):
+    model = QwenImageTransformer2DModel(num_layers=5, dim=256, heads=4, in_channels=16, joint_attention_dim=64,
+                                        axes_dims_rope=(8, 28, 28), time_scale=1.0, modulation_init_std=0.02)
+  inputs = QwenImageTransformer2DModel.example_inputs(height=272, width=272, text_tokens=33, in_channels=16,
+                                                      joint_attention_dim=64)
+  return model, inputs, QwenImageDenoisePipeline
+
+
+def _wan():
+  from cache_dit_b200.synthetic import WanDenoisePipeline, WanTransformer3DModel
+  with torch.device("cuda"):
+    model = WanTransformer3DModel(num_layers=4, dim=256, heads=2, ffn_dim=512, in_channels=16, text_dim=64,
+                                  axes_dims_rope=(44, 42, 42), time_scale=1.0, modulation_init_std=0.02)
+  inputs = WanTransformer3DModel.example_inputs(frames=3, height=5, width=7, text_tokens=16, in_channels=16, text_dim=64)
+  return model, inputs, WanDenoisePipeline
+
+
+def _generate(build, ops, graphs=False, threshold=0.15, steps=10):
+  step_ops.set_ops(ops)
+  try:
+    torch.manual_seed(0)
+    model, inputs, pipe_cls = build()
+    model = model.to(torch.bfloat16).eval().requires_grad_(False)
+    pipe = pipe_cls(model, inputs)
+    cd.enable_cache(pipe, cache_config=cd.DBCacheConfig(Fn_compute_blocks=1, max_warmup_steps=3,
+                                                        residual_diff_threshold=threshold),
+                    calibrator_config=cd.TaylorSeerCalibratorConfig(taylorseer_order=1),
+                    quantize_config=cd.QuantizeConfig(quant_type="float8_per_row"))
+    if graphs:
+      assert cd.enable_cuda_graphs(pipe, warmup_calls=1) >= 1
+    out = pipe(num_inference_steps=steps)
+    if graphs:  # a second generation replays every segment from its first step
+      out = pipe(num_inference_steps=steps)
+    stats = cd.summary(pipe, logging=False)[-1]
+    replays = sum(r.replays for r in cd.graph_runners(pipe))
+    fp8 = model._quantize_stats
+    cd.disable_cache(pipe)
+    return out.float().cpu().numpy(), stats, replays, fp8
+  finally:
+    step_ops.set_ops(None)
+
+
+@pytest.mark.parametrize("build", [_qwen, _wan], ids=["qwen_image", "wan"])
+def test_model_kernels_vs_oracle_ops(build):
+  got, s_k, _, fp8 = _generate(build, None)
+  want, s_o, _, _ = _generate(build, OracleStepOps())
+  assert fp8["quantized"] > 0
+  assert s_k.cached_steps == s_o.cached_steps and s_k.cached_steps  # bit-exact masks, both CFG branches
+  assert s_k.cfg_cached_steps == s_o.cfg_cached_steps and s_k.cfg_cached_steps
+  for k, v in s_o.residual_diffs.items():
+    assert abs(s_k.residual_diffs[k] - v) <= 1e-3 * abs(v) + 1e-12
+  rel = np.linalg.norm(got - want) / np.linalg.norm(want)
+  assert rel < 2e-2, rel
+
+
+def test_qwen_modulation_linears_stay_bf16():
+  """The name filter of the reference (`mod` is an excluded pattern) keeps img_mod / txt_mod in bf16."""
+  model, _, _ = _qwen()
+  model = model.to(torch.bfloat16)
+  cd.quantize(model, cd.QuantizeConfig(quant_type="float8_per_row"))
+  block = model.transformer_blocks[0]
+  assert isinstance(block.img_mod[1], torch.nn.Linear) and not isinstance(block.img_mod[1], cd.Float8RowwiseLinear)
+  assert isinstance(block.attn.to_q, cd.Float8RowwiseLinear)
+  assert isinstance(block.img_mlp.net[0].proj, cd.Float8RowwiseLinear)
+
+
+@pytest.mark.parametrize("build", [_qwen, _wan], ids=["qwen_image", "wan"])
+def test_model_graph_replay_equals_eager(build):
+  eager, s_e, _, _ = _generate(build, None)
+  graphed, s_g, replays, _ = _generate(build, None, graphs=True)
+  assert replays > 0
+  assert s_g.cached_steps == s_e.cached_steps
+  np.testing.assert_array_equal(graphed, eager)
+
+
+@pytest.mark.parametrize("heads,d,tokens", [(2, 128, 37), (40, 128, 9), (5, 64, 130)])
+def test_row_norm_rope_matches_eager(heads, d, tokens):
+  """RMSNorm over the whole row (Wan's q / k normalisation) + rotary embedding in the scatter kernel."""
+  from cache_dit_b200 import _native as nat
+  g = torch.Generator().manual_seed(heads * d)
+  c = heads * d
+  wide = torch.randn(1, tokens, 2 * c, generator=g).to("cuda", torch.bfloat16)
+  x = wide[..., c:]
+  w = (1 + 0.1 * torch.randn(c, generator=g)).to("cuda", torch.bfloat16)
+  ang = torch.rand(tokens, d // 2, generator=g) * 6.28
+  cos = torch.cos(ang).repeat_interleave(2, dim=-1).to("cuda", torch.bfloat16).contiguous()
+  sin = torch.sin(ang).repeat_interleave(2, dim=-1).to("cuda", torch.bfloat16).contiguous()
+  out = torch.full((1, tokens, heads, d), float("nan"), device="cuda", dtype=torch.bfloat16)
+  nat.scatter_heads(x, w, cos, sin, 0, [out.data_ptr()], out.stride(0), 0, heads, 1e-6, across_heads=True)
+  torch.cuda.synchronize()
+  y = F.rms_norm(x.float(), (c, ), w.float(), 1e-6).unflatten(-1, (heads, d))
+  cs, sn = cos.float()[None, :, None, :], sin.float()[None, :, None, :]
+  y1, y2 = y.unflatten(-1, (-1, 2)).unbind(-1)
+  ref = y * cs + torch.stack([-y2, y1], dim=-1).flatten(-2) * sn
+  assert torch.isfinite(out).all().item()
+  assert ((out.float() - ref).abs() <= 3 * 2.0**-8 * ref.abs() + 2e-2).all().item()

@@ -38,3 +38,14 @@ def test_peer_exchange_under_cuda_graphs(reports):
     assert r["status_graphs"] == 0 and r["replays"] > 0
     assert r["masks_graphs"] == r["masks_peer"]
     assert r["graphs_equal_peer"]
+
+
+@pytest.mark.parametrize("model", ["qwen", "wan"])
+def test_other_models_peer_exchange(reports, model):
+  """Qwen-Image-shape with uneven token shards and Wan-shape (row-norm q / k, local cross-attention)."""
+  for r in reports:
+    o = r["others"][model]
+    assert o["finite"] and o["status"] == [0, 0]
+    assert o["masks"][0] == o["masks"][1] == o["masks"][2] and o["masks"][0]
+    assert o["peer_equals_nccl"] and o["graphs_equal_peer"]
+  assert reports[0]["others"][model]["masks"] == reports[1]["others"][model]["masks"]
