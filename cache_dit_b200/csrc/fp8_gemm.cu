@@ -19,6 +19,8 @@
 // flag, records a code in the caller's status word, all roles drain, TMEM is released and the
 // kernel returns, so a logic error cannot wedge the device.
 #include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
 
 #include <cstdlib>
 #include <cstring>
@@ -701,6 +703,87 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
   }
 }
 
+// ---- few-row product (M <= 4): weight streaming on the CUDA cores ------------------------------------
+// The adaLN modulation linears see one row per image (M = batch).  A 128-row tensor-core tile would be
+// 99 % padding and the tile grid (N / 256 CTAs) too small to pull the weights at HBM speed, so these
+// products stream the weight matrix once with every SM: a warp owns output columns, lanes read 16-byte
+// pieces of the weight row, e4m3 -> f16 (exact) -> fp32 multiply-add against the activation rows staged
+// in shared memory as f16, one shuffle reduction per column.  HBM-bound: N*K bytes.
+constexpr int GEMV_MAX_M = 4;
+constexpr int GEMV_THREADS = 256;
+
+__device__ __forceinline__ void e4m3x4_to_float4(uint32_t w, float (&f)[4]) {
+  const __half2_raw lo = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w & 0xffffu), __NV_E4M3);
+  const __half2_raw hi = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w >> 16), __NV_E4M3);
+  const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&lo));
+  const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&hi));
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+}
+
+template <int TM>
+__global__ void __launch_bounds__(GEMV_THREADS)
+    fp8_gemv_rowscaled_kernel(const uint8_t* __restrict__ a_q, const float* __restrict__ sa,
+                              const uint8_t* __restrict__ w_q, const float* __restrict__ sw,
+                              const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ out, int N, int K,
+                              int64_t ld_out) {
+  extern __shared__ __half s_a[];  // [TM][K]
+  for (int i = threadIdx.x; i < TM * K / 4; i += GEMV_THREADS) {
+    float f[4];
+    e4m3x4_to_float4(reinterpret_cast<const uint32_t*>(a_q)[i], f);
+    reinterpret_cast<__half2*>(s_a)[2 * i] = __floats2half2_rn(f[0], f[1]);
+    reinterpret_cast<__half2*>(s_a)[2 * i + 1] = __floats2half2_rn(f[2], f[3]);
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const int warp = (blockIdx.x * GEMV_THREADS + threadIdx.x) >> 5;
+  const int nwarps = (gridDim.x * GEMV_THREADS) >> 5;
+  const int chunks = K >> 4;  // 16-byte pieces per weight row
+  for (int n = warp; n < N; n += nwarps) {
+    const uint4* wrow = reinterpret_cast<const uint4*>(w_q + (int64_t)n * K);
+    float acc[TM];
+#pragma unroll
+    for (int m = 0; m < TM; ++m) acc[m] = 0.f;
+    for (int c0 = lane; c0 < chunks; c0 += 32 * 4) {  // four independent loads in flight per lane
+      uint4 wv[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int c = c0 + j * 32;
+        wv[j] = c < chunks ? __ldcs(wrow + c) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int c = c0 + j * 32;
+        if (c < chunks) {
+          const uint32_t words[4] = {wv[j].x, wv[j].y, wv[j].z, wv[j].w};
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            float wf[4];
+            e4m3x4_to_float4(words[q], wf);
+#pragma unroll
+            for (int m = 0; m < TM; ++m) {
+              const __half2* ap = reinterpret_cast<const __half2*>(s_a + (int64_t)m * K + c * 16 + q * 4);
+              const float2 a01 = __half22float2(ap[0]), a23 = __half22float2(ap[1]);
+              acc[m] = fmaf(wf[0], a01.x, acc[m]);
+              acc[m] = fmaf(wf[1], a01.y, acc[m]);
+              acc[m] = fmaf(wf[2], a23.x, acc[m]);
+              acc[m] = fmaf(wf[3], a23.y, acc[m]);
+            }
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int m = 0; m < TM; ++m) acc[m] = warp_sum(acc[m]);
+    if (lane == 0) {
+      const float cs = __ldg(sw + n);
+      const float b = bias != nullptr ? __bfloat162float(bias[n]) : 0.f;
+#pragma unroll
+      for (int m = 0; m < TM; ++m)
+        out[(int64_t)m * ld_out + n] = __float2bfloat16_rn(acc[m] * __ldg(sa + m) * cs + b);
+    }
+  }
+}
+
 // ---- host side -----------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
@@ -810,6 +893,25 @@ extern "C" int cdb_fp8_gemm_rowscaled(const void* a_q, const float* a_scale, con
   });
   CDB_CUDA_CHECK(attr_err);
   const int sms = sm_count();
+  cudaStream_t st_gemv = static_cast<cudaStream_t>(stream);
+  if (mode == 0 && M <= GEMV_MAX_M && M * K * 2 <= 48 * 1024 && !(reinterpret_cast<uintptr_t>(a_q) & 3u)) {
+    const uint8_t* ap = static_cast<const uint8_t*>(a_q);
+    const uint8_t* wp = static_cast<const uint8_t*>(w_q);
+    const __nv_bfloat16* bp = static_cast<const __nv_bfloat16*>(bias);
+    __nv_bfloat16* op = static_cast<__nv_bfloat16*>(out);
+    const int64_t want = (N + GEMV_THREADS / 32 - 1) / (GEMV_THREADS / 32);
+    const unsigned grid = (unsigned)(want < (int64_t)sms * 4 ? want : (int64_t)sms * 4);
+    const size_t smem = (size_t)M * K * 2;
+#define CDB_GEMV(TM) \
+  fp8_gemv_rowscaled_kernel<TM><<<grid, GEMV_THREADS, smem, st_gemv>>>(ap, a_scale, wp, w_scale, bp, op, (int)N, (int)K, ld_out)
+    if (M == 1) CDB_GEMV(1);
+    else if (M == 2) CDB_GEMV(2);
+    else if (M == 3) CDB_GEMV(3);
+    else CDB_GEMV(4);
+#undef CDB_GEMV
+    CDB_CUDA_CHECK(cudaGetLastError());
+    return CDB_OK;
+  }
   // CTA pairs pay off on tall problems; below ~4096 rows (rank shards of a context-parallel run: 2304,
   // 1152, 576) the single-CTA kernel's 128-row tiles waste less and measured 4-25 % faster
   const bool pair = mode == 2 || (mode == 0 && M >= 4096 && CDB_GEMM_DEFAULT_PAIR);
