@@ -177,7 +177,7 @@ def timed(fn, steps, barrier):
   return start.elapsed_time(end)  # ms
 
 
-def fp8_library_peak(device):
+def fp8_library_peak(device, sustained=True):
   """Dense FP8 throughput of the vendor library on this GPU (8192^3, per-tensor scales, best of 10):
   the measured denominator for the tensor-core roofline, next to the nominal 4.5 PFLOP/s."""
   try:
@@ -195,6 +195,8 @@ def fp8_library_peak(device):
       if i >= 3:
         best = min(best, s.elapsed_time(e))
     burst = 2.0 * n**3 / (best * 1e-3) / 1e12
+    if not sustained:
+      return burst, None
     # sustained: the same product back to back for ~2 s (power-capped clocks, like a GEMM inside a long step)
     reps, elapsed, done = 50, 0.0, 0
     while elapsed < 2000.0 and done < 5000:
@@ -434,12 +436,15 @@ def run_ours(args):
     return
   peaks, peak_kind = load_measured_peaks()
   cache_roof = None
+  fp8_burst = fp8_library_peak(device, sustained=False) if not args.skip_extras else None
   if not args.skip_extras:  # before the 2-second GEMM loop below heats the part
     cache_roof = {"flux_image_stream_1x4096x3072": cache_kernel_rooflines(device, peaks["hbm_gbs"]),
                   "wan_rank_shard_1x9450x5120": cache_kernel_rooflines(device, peaks["hbm_gbs"], 9450, 5120, 3),
                   "eager_torch_ops_us_1x4096x3072": eager_cache_ops_us(device)}
     sweep = fp8_linear_sweep(device)
   fp8_lib = fp8_library_peak(device) if not args.skip_extras else None
+  if fp8_lib and fp8_burst:
+    fp8_lib = (max(fp8_lib[0], fp8_burst[0]), fp8_lib[1])
   achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
   # the GEMM launches are timed inside long steps under the power cap: the sustained library figure
   # is the like-for-like denominator, the burst figure is reported beside it

@@ -234,7 +234,8 @@ __global__ void __launch_bounds__(Q_CTA, PREOP == CDB_PRE_LAYERNORM_MOD ? 3 : 1)
     }
     const uint32_t mu = as_u32(m2);
     const float amax = row_reduce<TPR, true>(fmaxf(lo_f(mu), hi_f(mu)), s_red, slot);
-    float sc = __fdiv_rn(amax, E4M3_MAX);
+    // amax / 448 the way PyTorch's CUDA division by a Python scalar computes it: times fl32(1/448)
+    float sc = __fmul_rn(amax, 1.0f / E4M3_MAX);
     if (sc == 0.f) sc = 1.f;  // all-zero row: keep zeros exact instead of 0/0
     if (valid && tig == 0) scale[row] = sc;
 

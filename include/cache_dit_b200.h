@@ -123,7 +123,8 @@ CDB_API int cdb_taylor_update(const void* after, const void* before, const void*
  * Per-row dynamic FP8 (e4m3fn) quantization.  Replaces torchao's dynamic activation
  * quantization selected by the reference at
  *   src/cache_dit/quantization/torchao/quantize_ao.py:540-558  (PerRow, e4m3, zero scale -> 1 at :43-71)
- *   scale[r] = amax_r / 448 (1 if the row is all zero); q = saturate_e4m3(x / scale[r])
+ *   scale[r] = amax_r * fl32(1/448) (PyTorch's CUDA `amax / 448.0`; 1 if the row is all zero);
+ *   q = saturate_e4m3(x / scale[r])
  * x is [rows, cols] bf16 row-major with row stride `ld_x` elements; q is [rows, cols] bytes,
  * contiguous; scale is [rows] float32.  Also used once per weight at load time ([N, K] rows).
  * ---------------------------------------------------------------------------------------- */

@@ -15,7 +15,10 @@ anchored on the reference's own call sites:
   * which layers are quantized ........................... src/cache_dit/quantization/torchao/quantize_ao.py:666-775
 
 Algorithm (torchao float8 dynamic quantization, row-wise granularity):
-  scale_r = max_k |x[r,k]| / 448        (float32; 1 when the row is all zero)
+  scale_r = max_k |x[r,k]| / 448        (float32; 1 when the row is all zero).  On a GPU PyTorch divides a
+            tensor by a Python scalar as a multiplication by the float32 reciprocal of the scalar (ATen's
+            true-division kernel for a CPU-scalar divisor), so the value the reference gets there is
+            amax * fl32(1/448), which can differ from amax / 448 in the last bit; that form is used here
   q[r,k]  = e4m3fn( clamp(x[r,k] / scale_r, -448, 448) )     round-to-nearest-even
   out     = bf16( (q_a @ q_w^T) * scale_a[:,None] * scale_w[None,:] + bias )   fp32 accumulate
 """
@@ -71,7 +74,7 @@ def quantize_rows(x: np.ndarray) -> Tuple[np.ndarray, np.ndarray]:
   """x [rows, cols] (float32 holding bf16 values) -> (e4m3 byte codes, float32 scales)."""
   x = np.asarray(x, dtype=np.float32)
   amax = np.max(np.abs(x), axis=1).astype(np.float32)
-  scale = (amax / E4M3_MAX).astype(np.float32)
+  scale = (amax * (np.float32(1.0) / E4M3_MAX)).astype(np.float32)
   scale = np.where(scale == 0, np.float32(1.0), scale).astype(np.float32)
   q = e4m3_round((x / scale[:, None]).astype(np.float32))
   return e4m3_encode(q), scale

@@ -316,7 +316,7 @@ def test_fp8_gemm_on_model_shapes(nat, M, N, K):
 
 
 # ------------------------------------------------------------------------------ against the library ops the reference calls
-@pytest.mark.parametrize("M,N,K,bias", [(300, 264, 256, False), (4608, 3072, 3072, True), (1000, 12288, 3072, False)])
+@pytest.mark.parametrize("M,N,K,bias", [(300, 272, 256, False), (4608, 3072, 3072, True), (1000, 12288, 3072, False)])
 def test_fp8_gemm_matches_library_scaled_mm(nat, M, N, K, bias):
   """`torch._scaled_mm` with row-wise scales is the call the reference makes for this product
   (src/cache_dit/quantization/torchao/_scaled_mm.py:72-91).  Same quantized operands in both."""
