@@ -48,6 +48,8 @@ SIGNATURES = {
   "cdb_peer_release": (c_int, [c_void_p]),
   "cdb_scatter_heads": (c_int, [c_void_p, c_int64, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int64,
                                 c_int64, c_int64, c_int64, c_int, c_int, c_float, c_void_p]),
+  "cdb_scatter_heads_multi": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
+  "cdb_peer_barrier": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_uint64, c_void_p]),
   "cdb_gather_tokens": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int64, c_int64, c_void_p, c_int64, c_int, c_int,
                                 c_void_p]),
   "cdb_peer_sync_bytes": (c_size_t, []),
@@ -372,3 +374,51 @@ def peer_import(handle: bytes) -> int:
 
 def peer_release(ptr: int):
   check(lib().cdb_peer_release(c_void_p(ptr)), "cdb_peer_release", launch=False)
+
+
+class ScatterJob(ctypes.Structure):
+  """ctypes image of `cdb_scatter_job`."""
+  _fields_ = [("x", c_void_p), ("ld_x", c_int64), ("tokens", c_int64), ("tokens_per_batch", c_int64),
+              ("norm_weight", c_void_p), ("norm_across_heads", c_int), ("eps", c_float), ("cos_table", c_void_p),
+              ("sin_table", c_void_p), ("table_row_offset", c_int), ("dst_ptrs", c_void_p),
+              ("dst_batch_stride", c_int64), ("dst_row_offset", c_int64)]
+
+
+def scatter_heads_multi(jobs, heads: int):
+  """Several `scatter_heads` calls as one launch.  jobs: dicts with x [batch, tokens, heads*head_dim],
+  norm_weight / cos / sin (None: copy), table_row_offset, dst_ptrs, dst_batch_stride, dst_row_offset,
+  eps, across_heads.  All jobs share heads, head_dim and the number of destinations."""
+  if not 1 <= len(jobs) <= 6:
+    raise RuntimeError("scatter_heads_multi: 1 to 6 jobs per launch")
+  arr = (ScatterJob * len(jobs))()
+  keep = []
+  world = len(jobs[0]["dst_ptrs"])
+  x0 = jobs[0]["x"]
+  d = x0.shape[-1] // heads
+  for slot, j in zip(arr, jobs):
+    x, w = j["x"], j.get("norm_weight")
+    _need_cuda(x, w, j.get("cos"), j.get("sin"))
+    b, t, c = x.shape
+    if x.dtype != torch.bfloat16 or x.stride(2) != 1 or (b > 1 and x.stride(0) != t * x.stride(1)) or c != heads * d \
+        or len(j["dst_ptrs"]) != world:
+      raise RuntimeError("scatter_heads_multi: bf16 projections of one head layout, uniformly strided rows")
+    across = bool(j.get("across_heads", False))
+    if w is not None and w.numel() != (c if across else d):
+      raise RuntimeError("scatter_heads_multi: norm weight is [head_dim] per head or [heads*head_dim] across heads")
+    ptrs = _ptr_array(j["dst_ptrs"])
+    keep.append(ptrs)
+    slot.x, slot.ld_x, slot.tokens, slot.tokens_per_batch = x.data_ptr(), x.stride(1), b * t, t
+    slot.norm_weight = None if w is None else w.data_ptr()
+    slot.norm_across_heads, slot.eps = int(across), float(j.get("eps", 0.0))
+    slot.cos_table = None if w is None else j["cos"].data_ptr()
+    slot.sin_table = None if w is None else j["sin"].data_ptr()
+    slot.table_row_offset = int(j.get("table_row_offset", 0))
+    slot.dst_ptrs = ctypes.cast(ptrs, c_void_p)
+    slot.dst_batch_stride, slot.dst_row_offset = int(j["dst_batch_stride"]), int(j["dst_row_offset"])
+  st = lib().cdb_scatter_heads_multi(ctypes.cast(arr, c_void_p), len(jobs), world, heads, d, _stream(x0))
+  check(st, "cdb_scatter_heads_multi")
+
+
+def peer_barrier(flag_ptrs, my_flags, my_rank: int, sync, timeout_ns: int):
+  check(lib().cdb_peer_barrier(_ptr_array(flag_ptrs), _ptr(my_flags), len(flag_ptrs), int(my_rank), _ptr(sync),
+                               int(timeout_ns), _stream(my_flags)), "cdb_peer_barrier")

@@ -39,16 +39,16 @@ constexpr int SC_PK = 4;
 //   MODE 2  RMSNorm over the whole row (weight [heads * head_dim]) + rotary embedding   (Wan)
 constexpr int SCATTER_COPY = 0, SCATTER_HEAD_NORM = 1, SCATTER_ROW_NORM = 2;
 template <int LPH, int MODE>
-__global__ void __launch_bounds__(SC_THREADS)
-    scatter_heads_kernel(const __nv_bfloat16* __restrict__ x, int64_t ld_x, const __nv_bfloat16* __restrict__ w,
-                         const __nv_bfloat16* __restrict__ cs, const __nv_bfloat16* __restrict__ sn, int table_row_offset,
-                         const PeerPtrs dst, int heads_per_rank, int64_t ld_out, int64_t out_batch_stride,
-                         int64_t tokens, int64_t tokens_per_batch, int64_t dst_row_offset, int heads, float eps) {
+__device__ __forceinline__ void scatter_heads_body(const __nv_bfloat16* __restrict__ x, int64_t ld_x,
+                                                   const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ cs,
+                                                   const __nv_bfloat16* __restrict__ sn, int table_row_offset,
+                                                   const PeerPtrs& dst, int heads_per_rank, int64_t ld_out,
+                                                   int64_t out_batch_stride, int64_t tokens, int64_t tokens_per_batch,
+                                                   int64_t dst_row_offset, int heads, float eps, float* s_part) {
   constexpr int D = LPH * 8;
   constexpr bool NORM_ROPE = MODE != SCATTER_COPY;
   const int npk = heads * LPH;
   const int in_head = threadIdx.x % LPH;
-  __shared__ float s_part[SC_THREADS / 32];
   uint32_t ww[4] = {0, 0, 0, 0};
   if constexpr (MODE == SCATTER_HEAD_NORM) {
     const uint4 wv = __ldg(reinterpret_cast<const uint4*>(w) + in_head);
@@ -136,6 +136,55 @@ __global__ void __launch_bounds__(SC_THREADS)
   }
 }
 
+template <int LPH, int MODE>
+__global__ void __launch_bounds__(SC_THREADS)
+    scatter_heads_kernel(const __nv_bfloat16* __restrict__ x, int64_t ld_x, const __nv_bfloat16* __restrict__ w,
+                         const __nv_bfloat16* __restrict__ cs, const __nv_bfloat16* __restrict__ sn, int table_row_offset,
+                         const PeerPtrs dst, int heads_per_rank, int64_t ld_out, int64_t out_batch_stride,
+                         int64_t tokens, int64_t tokens_per_batch, int64_t dst_row_offset, int heads, float eps) {
+  __shared__ float s_part[SC_THREADS / 32];
+  scatter_heads_body<LPH, MODE>(x, ld_x, w, cs, sn, table_row_offset, dst, heads_per_rank, ld_out, out_batch_stride,
+                                tokens, tokens_per_batch, dst_row_offset, heads, eps, s_part);
+}
+
+// Several scatter jobs in one launch (blockIdx.y = job): the q, k and v projections of the text and the
+// image stream of one block are up to six jobs, and at small per-rank token counts their launch cost
+// exceeded their run time.
+constexpr int SCATTER_MAX_JOBS = 6;
+struct ScatterJob {
+  const __nv_bfloat16* x;
+  const __nv_bfloat16* w;
+  const __nv_bfloat16* cs;
+  const __nv_bfloat16* sn;
+  PeerPtrs dst;
+  int64_t ld_x, out_batch_stride, tokens, tokens_per_batch, dst_row_offset;
+  int table_row_offset, mode;
+  float eps;
+};
+struct ScatterJobs {
+  ScatterJob job[SCATTER_MAX_JOBS];
+};
+
+template <int LPH>
+__global__ void __launch_bounds__(SC_THREADS)
+    scatter_heads_multi_kernel(const __grid_constant__ ScatterJobs jobs, int heads_per_rank, int64_t ld_out, int heads) {
+  __shared__ float s_part[SC_THREADS / 32];
+  const ScatterJob& j = jobs.job[blockIdx.y];
+  if ((int64_t)blockIdx.x >= j.tokens) return;
+  if (j.mode == SCATTER_COPY)
+    scatter_heads_body<LPH, SCATTER_COPY>(j.x, j.ld_x, j.w, j.cs, j.sn, j.table_row_offset, j.dst, heads_per_rank, ld_out,
+                                          j.out_batch_stride, j.tokens, j.tokens_per_batch, j.dst_row_offset, heads,
+                                          j.eps, s_part);
+  else if (j.mode == SCATTER_HEAD_NORM)
+    scatter_heads_body<LPH, SCATTER_HEAD_NORM>(j.x, j.ld_x, j.w, j.cs, j.sn, j.table_row_offset, j.dst, heads_per_rank,
+                                               ld_out, j.out_batch_stride, j.tokens, j.tokens_per_batch,
+                                               j.dst_row_offset, heads, j.eps, s_part);
+  else
+    scatter_heads_body<LPH, SCATTER_ROW_NORM>(j.x, j.ld_x, j.w, j.cs, j.sn, j.table_row_offset, j.dst, heads_per_rank,
+                                              ld_out, j.out_batch_stride, j.tokens, j.tokens_per_batch,
+                                              j.dst_row_offset, heads, j.eps, s_part);
+}
+
 // Attention output of this rank, [batch, all tokens, own heads, head_dim]: the row of token s goes
 // to the rank whose token range [row_start[r], row_start[r+1]) holds s, into its
 // [batch, token capacity, all heads, head_dim] buffer at head offset my_rank * heads_per_rank.
@@ -201,6 +250,40 @@ __global__ void peer_wait_kernel(const unsigned int* __restrict__ my_flags, int 
     unsigned int v;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(word) : "memory");
     if ((int)(v - want) >= 0) break;  // epochs wrap: compare as a signed difference
+    if ((it & 63u) == 63u) {
+      unsigned long long now;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > timeout_ns) {
+        atomicCAS(&sync->status, 0, 1 + (int)threadIdx.x);
+        break;
+      }
+      __nanosleep(200);
+    }
+  }
+  __threadfence_system();
+}
+
+// signal + wait in one launch (what a rank runs between the phases of the exchange).
+__global__ void peer_barrier_kernel(const PeerPtrs flags, const unsigned int* __restrict__ my_flags, int my_rank,
+                                    int world, PeerSync* sync, unsigned long long timeout_ns) {
+  __shared__ unsigned int e;
+  if (threadIdx.x == 0) {
+    e = sync->epoch + 1;
+    sync->epoch = e;
+  }
+  __syncthreads();
+  if ((int)threadIdx.x >= world) return;
+  __threadfence_system();
+  unsigned int* word = static_cast<unsigned int*>(flags.p[threadIdx.x]) + my_rank;
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(word), "r"(e) : "memory");
+  if (sync->status != 0) return;
+  const unsigned int* mine = my_flags + threadIdx.x;
+  unsigned long long t0 = 0;
+  for (unsigned int it = 0;; ++it) {
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+    if ((int)(v - e) >= 0) break;
     if ((it & 63u) == 63u) {
       unsigned long long now;
       asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
@@ -325,6 +408,75 @@ extern "C" int cdb_scatter_heads(const void* x, int64_t ld_x, const void* norm_w
   else { CDB_SC_DIM(SCATTER_HEAD_NORM); }
 #undef CDB_SC_DIM
 #undef CDB_SC
+  CDB_CUDA_CHECK(cudaGetLastError());
+  return CDB_OK;
+}
+
+struct cdb_scatter_job_abi {  // mirrors `cdb_scatter_job` of the public header
+  const void* x;
+  int64_t ld_x, tokens, tokens_per_batch;
+  const void* norm_weight;
+  int norm_across_heads;
+  float eps;
+  const void* cos_table;
+  const void* sin_table;
+  int table_row_offset;
+  void* const* dst_ptrs;
+  int64_t dst_batch_stride, dst_row_offset;
+};
+
+extern "C" int cdb_scatter_heads_multi(const void* jobs_v, int njobs, int world, int heads, int head_dim, void* stream) {
+  const cdb_scatter_job_abi* jobs = static_cast<const cdb_scatter_job_abi*>(jobs_v);
+  if (!jobs || njobs < 1 || njobs > SCATTER_MAX_JOBS || heads <= 0 || world < 1 || world > PEER_MAX)
+    return CDB_ERR_BAD_ARGUMENT;
+  if ((head_dim != 64 && head_dim != 128 && head_dim != 256) || heads % world != 0) return CDB_ERR_UNSUPPORTED;
+  ScatterJobs packed{};
+  int64_t max_tokens = 0;
+  for (int i = 0; i < njobs; ++i) {
+    const cdb_scatter_job_abi& in = jobs[i];
+    ScatterJob& o = packed.job[i];
+    if (!in.x || in.tokens < 0 || in.tokens_per_batch <= 0 || !fill_ptrs(&o.dst, in.dst_ptrs, world))
+      return CDB_ERR_BAD_ARGUMENT;
+    const bool norm = in.norm_weight != nullptr;
+    if (norm && (!in.cos_table || !in.sin_table)) return CDB_ERR_BAD_ARGUMENT;
+    if (in.ld_x % 8 != 0 || in.dst_batch_stride % 8 != 0 || !aligned16(in.x) ||
+        (norm && (!aligned16(in.norm_weight) || !aligned16(in.cos_table) || !aligned16(in.sin_table))))
+      return CDB_ERR_UNSUPPORTED;
+    o.x = static_cast<const __nv_bfloat16*>(in.x);
+    o.w = static_cast<const __nv_bfloat16*>(in.norm_weight);
+    o.cs = static_cast<const __nv_bfloat16*>(in.cos_table);
+    o.sn = static_cast<const __nv_bfloat16*>(in.sin_table);
+    o.ld_x = in.ld_x;
+    o.out_batch_stride = in.dst_batch_stride;
+    o.tokens = in.tokens;
+    o.tokens_per_batch = in.tokens_per_batch;
+    o.dst_row_offset = in.dst_row_offset;
+    o.table_row_offset = in.table_row_offset;
+    o.mode = !norm ? SCATTER_COPY : (in.norm_across_heads ? SCATTER_ROW_NORM : SCATTER_HEAD_NORM);
+    o.eps = in.eps;
+    max_tokens = in.tokens > max_tokens ? in.tokens : max_tokens;
+  }
+  if (max_tokens == 0) return CDB_OK;
+  const int hpr = heads / world;
+  const int64_t ld_out = (int64_t)hpr * head_dim;
+  const int64_t cap = (int64_t)sm_count() * 16 / njobs + 1;
+  const dim3 grid((unsigned)(max_tokens < cap ? max_tokens : cap), (unsigned)njobs);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (head_dim == 64) scatter_heads_multi_kernel<8><<<grid, SC_THREADS, 0, st>>>(packed, hpr, ld_out, heads);
+  else if (head_dim == 128) scatter_heads_multi_kernel<16><<<grid, SC_THREADS, 0, st>>>(packed, hpr, ld_out, heads);
+  else scatter_heads_multi_kernel<32><<<grid, SC_THREADS, 0, st>>>(packed, hpr, ld_out, heads);
+  CDB_CUDA_CHECK(cudaGetLastError());
+  return CDB_OK;
+}
+
+extern "C" int cdb_peer_barrier(void* const* flag_ptrs, const void* my_flags, int world, int my_rank, void* sync,
+                                uint64_t timeout_ns, void* stream) {
+  PeerPtrs flags;
+  if (!sync || !my_flags || my_rank < 0 || my_rank >= world || !fill_ptrs(&flags, flag_ptrs, world))
+    return CDB_ERR_BAD_ARGUMENT;
+  peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      flags, static_cast<const unsigned int*>(my_flags), my_rank, world, static_cast<PeerSync*>(sync),
+      (unsigned long long)timeout_ns);
   CDB_CUDA_CHECK(cudaGetLastError());
   return CDB_OK;
 }

@@ -116,9 +116,19 @@ class PeerExchange:
     _native.scatter_heads(x, norm_weight, cos, sin, row_offset_local, self.ptrs[name], buf.stride(0),
                           self.row_starts[self.rank] + row_offset_local, heads, eps, across_heads)
 
+  def scatter_job(self, name: str, x: torch.Tensor, row_offset_local: int, norm_weight=None, cos=None, sin=None,
+                  eps: float = 0.0, across_heads: bool = False) -> dict:
+    """The same scatter as a job description for `scatter_jobs` (several in one launch)."""
+    return dict(x=x, norm_weight=norm_weight, cos=cos, sin=sin, table_row_offset=row_offset_local,
+                dst_ptrs=self.ptrs[name], dst_batch_stride=self.buffers[name].stride(0),
+                dst_row_offset=self.row_starts[self.rank] + row_offset_local, eps=eps, across_heads=across_heads)
+
+  def scatter_jobs(self, jobs, heads: int):
+    for i in range(0, len(jobs), 6):
+      _native.scatter_heads_multi(jobs[i:i + 6], heads)
+
   def barrier(self):
-    _native.peer_signal(self.flag_ptrs, self.rank, self.sync, self.flags)
-    _native.peer_wait(self.flags, self.world, self.sync, self.timeout_ns)
+    _native.peer_barrier(self.flag_ptrs, self.flags, self.rank, self.sync, self.timeout_ns)
 
   def gather_output(self, o_local: torch.Tensor) -> torch.Tensor:
     """o_local [batch, tokens_all, heads / W, head_dim] -> this rank's `o` buffer after the exchange."""

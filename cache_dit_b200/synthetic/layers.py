@@ -191,35 +191,39 @@ def joint_attention(q_parts, k_parts, v_parts, rope, heads: int, cp: Optional["U
   concatenation are one kernel per part; under Ulysses with a peer exchange the same kernel also does
   the head scatter to the other GPUs."""
   ex = cp.exchange if cp is not None and cp.world > 1 else None
-  if ex is None:
-    q = joint_qk_norm_rope(q_parts, rope, heads, across_heads)
-    k = joint_qk_norm_rope(k_parts, rope, heads, across_heads)
-    d = q.shape[-1]
-    if len(v_parts) == 1:
-      v = v_parts[0].unflatten(-1, (heads, d))
-    elif _glue_kernels_apply(q) and d in (64, 128, 256):
-      # the same kernel that scatters heads across ranks, with one destination: a strided-row copy
-      v = torch.empty_like(q)
-      off = 0
-      for part in v_parts:
-        _native.scatter_heads(part, None, None, None, 0, [v.data_ptr()], v.stride(0), off, heads)
-        off += part.shape[1]
-    else:
-      v = torch.cat([part.unflatten(-1, (heads, d)) for part in v_parts], dim=1)
-    return attention(q, k, v, cp)
   x0 = q_parts[0][0]
   d = x0.shape[-1] // heads
   local_total = sum(p.shape[1] for p, _ in q_parts)
+  if ex is None:
+    if _glue_kernels_apply(x0) and d in (64, 128, 256) and rope[0].dtype == x0.dtype and rope[0].is_contiguous():
+      # one launch: q and k of every part normalised, rotated and placed; v parts placed
+      q, k = (torch.empty(x0.shape[0], local_total, heads, d, device=x0.device, dtype=x0.dtype) for _ in range(2))
+      # a single v projection is used where it lies (a strided view); several are gathered into one buffer
+      v = v_parts[0].unflatten(-1, (heads, d)) if len(v_parts) == 1 else torch.empty_like(q)
+      jobs, off = [], 0
+      for (xq, nq), (xk, nk), xv in zip(q_parts, k_parts, v_parts):
+        for x, norm, buf in ((xq, nq, q), (xk, nk, k)):
+          jobs.append(dict(x=x, norm_weight=norm.weight, cos=rope[0], sin=rope[1], table_row_offset=off,
+                           dst_ptrs=[buf.data_ptr()], dst_batch_stride=buf.stride(0), dst_row_offset=off,
+                           eps=norm.eps, across_heads=across_heads))
+        if len(v_parts) > 1:
+          jobs.append(dict(x=xv, dst_ptrs=[v.data_ptr()], dst_batch_stride=v.stride(0), dst_row_offset=off))
+        off += xq.shape[1]
+      for i in range(0, len(jobs), 6):
+        _native.scatter_heads_multi(jobs[i:i + 6], heads)
+      return attention(q, k, v, cp)
+    q = joint_qk_norm_rope(q_parts, rope, heads, across_heads)
+    k = joint_qk_norm_rope(k_parts, rope, heads, across_heads)
+    vs = [part.unflatten(-1, (heads, d)) for part in v_parts]
+    return attention(q, k, vs[0] if len(vs) == 1 else torch.cat(vs, dim=1), cp)
   ex.ensure(x0.shape[0], local_total, heads, d, x0.dtype)
-  for name, parts in (("q", q_parts), ("k", k_parts)):
-    off = 0
-    for x, norm in parts:
-      ex.scatter(name, x, heads, off, norm.weight, rope[0], rope[1], norm.eps, across_heads)
-      off += x.shape[1]
-  off = 0
-  for x in v_parts:
-    ex.scatter("v", x, heads, off)
-    off += x.shape[1]
+  jobs, off = [], 0
+  for (xq, nq), (xk, nk), xv in zip(q_parts, k_parts, v_parts):
+    jobs.append(ex.scatter_job("q", xq, off, nq.weight, rope[0], rope[1], nq.eps, across_heads))
+    jobs.append(ex.scatter_job("k", xk, off, nk.weight, rope[0], rope[1], nk.eps, across_heads))
+    jobs.append(ex.scatter_job("v", xv, off))
+    off += xq.shape[1]
+  ex.scatter_jobs(jobs, heads)
   ex.barrier()
   b = ex.buffers
   o = F.scaled_dot_product_attention(b["q"].transpose(1, 2), b["k"].transpose(1, 2), b["v"].transpose(1, 2))

@@ -235,12 +235,30 @@ CDB_API int cdb_scatter_heads(const void* x, int64_t ld_x, const void* norm_weig
                       void* const* dst_ptrs, int world,
                       int64_t dst_batch_stride, int64_t tokens, int64_t tokens_per_batch,
                       int64_t dst_row_offset, int heads, int head_dim, float eps, void* stream);
+/* Up to 6 cdb_scatter_heads jobs in one launch (q, k, v of the text and image stream of a block). */
+typedef struct cdb_scatter_job {
+  const void* x;
+  int64_t ld_x, tokens, tokens_per_batch;
+  const void* norm_weight; /* NULL: copy */
+  int norm_across_heads;
+  float eps;
+  const void* cos_table;
+  const void* sin_table;
+  int table_row_offset;
+  void* const* dst_ptrs; /* `world` addresses */
+  int64_t dst_batch_stride, dst_row_offset;
+} cdb_scatter_job;
+CDB_API int cdb_scatter_heads_multi(const void* jobs /* cdb_scatter_job[njobs] */, int njobs, int world, int heads,
+                            int head_dim, void* stream);
 CDB_API int cdb_gather_tokens(const void* o, void* const* dst_ptrs, int world, int my_rank, int64_t batch,
                       int64_t tokens_all, const int64_t* row_starts, int64_t dst_token_capacity,
                       int heads_per_rank, int head_dim, void* stream);
 CDB_API size_t cdb_peer_sync_bytes(void);
 CDB_API int cdb_peer_signal(void* const* flag_ptrs, int world, int my_rank, void* sync, void* stream);
 CDB_API int cdb_peer_wait(const void* my_flags, int world, void* sync, uint64_t timeout_ns, void* stream);
+/* signal followed by wait as one launch */
+CDB_API int cdb_peer_barrier(void* const* flag_ptrs, const void* my_flags, int world, int my_rank, void* sync,
+                     uint64_t timeout_ns, void* stream);
 
 #ifdef __cplusplus
 }
