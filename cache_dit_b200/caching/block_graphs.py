@@ -152,6 +152,13 @@ def enable_cuda_graphs(module_or_pipe, warmup_calls: int = 2) -> int:
   from .cache_blocks import CachedBlocks
   n = 0
   for root in _roots(module_or_pipe):
+    cp = getattr(root, "_cp", None)
+    if cp is not None and getattr(cp, "world", 1) > 1 and getattr(cp, "exchange", None) is None:
+      # NCCL all-to-all inside a captured segment hung on two GPUs; only the peer-memory exchange
+      # (fixed addresses, plain kernels) is replayed from graphs
+      logger.warning(f"{root.__class__.__name__}: context parallelism over NCCL all-to-all is not captured in CUDA "
+                     "graphs; use the peer exchange (ParallelismConfig(parallel_kwargs={'exchange': 'peer'})).")
+      continue
     for m in _cached_blocks_of(root):
       if isinstance(m, CachedBlocks):
         m.graph_runner = BlockGraphRunner(warmup_calls)
