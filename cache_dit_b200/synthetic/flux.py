@@ -20,8 +20,8 @@ from torch import nn
 from ..caching.block_adapters import BlockAdapter, BlockAdapterRegister
 from ..caching.forward_pattern import ForwardPattern
 from .layers import (RMSNorm, TimestepMLP, UlyssesGroup, concat_gelu_linear, gated_add, gelu_linear,
-                     joint_attention, join_tokens, norm_modulate, norm_modulate_linears, rope_frequencies,
-                     rope_tables, split_tokens, timestep_embedding)
+                     joint_attention, join_tokens, norm_modulate, norm_modulate_linears, RopeCache,
+                     split_tokens, timestep_embedding)
 
 
 class AdaLayerNormZero(nn.Module):
@@ -145,6 +145,7 @@ class FluxTransformer2DModel(nn.Module):
     self.norm_out = AdaLayerNormZero(dim, 2)
     self.proj_out = nn.Linear(dim, in_channels)
     self._cp: Optional[UlyssesGroup] = None
+    self._rope_cache = RopeCache()
     if modulation_init_std is not None:
       # small adaLN modulation weights (the trained model starts from adaLN-Zero): with random
       # weights of ordinary scale the residual stream changes by ~45 % between steps and nothing
@@ -190,7 +191,7 @@ class FluxTransformer2DModel(nn.Module):
       temb = temb + self.guidance_embedder(timestep_embedding(guidance * 1000.0, 256).to(dt))
     temb = temb + self.text_embedder(pooled_projections)
     encoder_hidden_states = self.context_embedder(encoder_hidden_states)
-    rope = rope_tables(rope_frequencies(torch.cat([txt_ids, img_ids], dim=0), self.axes_dims_rope), dt)
+    rope = self._rope_cache.get((txt_ids, img_ids), self.axes_dims_rope, dt)
     for block in self.transformer_blocks:
       encoder_hidden_states, hidden_states = block(hidden_states, encoder_hidden_states, temb, rope)
     for block in self.single_transformer_blocks:

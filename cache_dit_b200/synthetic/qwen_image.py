@@ -22,7 +22,7 @@ from ..caching.block_adapters import BlockAdapter, BlockAdapterRegister
 from ..caching.forward_pattern import ForwardPattern
 from .context_parallel import ContextParallelMixin
 from .layers import (RMSNorm, TimestepMLP, UlyssesGroup, gated_add, gelu_linear, joint_attention, norm_modulate,
-                     norm_modulate_linears, rope_frequencies, rope_tables, timestep_embedding)
+                     norm_modulate_linears, RopeCache, timestep_embedding)
 
 
 class _GeluProj(nn.Module):
@@ -101,6 +101,7 @@ class QwenImageTransformer2DModel(ContextParallelMixin, nn.Module):
     self.transformer_blocks = nn.ModuleList([QwenImageTransformerBlock(dim, heads) for _ in range(num_layers)])
     self.norm_out_linear = nn.Linear(dim, 2 * dim)
     self.proj_out = nn.Linear(dim, in_channels)
+    self._rope_cache = RopeCache()
     if modulation_init_std is not None:  # see FluxTransformer2DModel: makes consecutive steps similar
       for block in self.transformer_blocks:
         for mod in (block.img_mod[1], block.txt_mod[1]):
@@ -118,7 +119,7 @@ class QwenImageTransformer2DModel(ContextParallelMixin, nn.Module):
     hidden_states = self.img_in(hidden_states)
     encoder_hidden_states = self.txt_in(self.txt_norm(encoder_hidden_states))
     temb = self.time_text_embed(timestep_embedding(timestep * self.time_scale, 256).to(dt))
-    rope = rope_tables(rope_frequencies(torch.cat([txt_ids, img_ids], dim=0), self.axes_dims_rope), dt)
+    rope = self._rope_cache.get((txt_ids, img_ids), self.axes_dims_rope, dt)
     for block in self.transformer_blocks:
       encoder_hidden_states, hidden_states = block(hidden_states, encoder_hidden_states, temb, rope)
     scale, shift = self.norm_out_linear(F.silu(temb)).chunk(2, dim=-1)

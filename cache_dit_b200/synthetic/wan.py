@@ -24,7 +24,7 @@ from ..caching.block_adapters import BlockAdapter, BlockAdapterRegister
 from ..caching.forward_pattern import ForwardPattern
 from .context_parallel import ContextParallelMixin
 from .layers import (RMSNorm, TimestepMLP, UlyssesGroup, gated_add, gelu_linear, joint_attention, norm_modulate,
-                     norm_modulate_linears, rope_frequencies, rope_tables, timestep_embedding)
+                     norm_modulate_linears, RopeCache, timestep_embedding)
 from .qwen_image import QwenFeedForward
 
 
@@ -87,6 +87,7 @@ class WanTransformer3DModel(ContextParallelMixin, nn.Module):
     self.blocks = nn.ModuleList([WanTransformerBlock(dim, ffn_dim, heads) for _ in range(num_layers)])
     self.scale_shift_table = nn.Parameter(torch.randn(1, 2, dim) / dim**0.5)
     self.proj_out = nn.Linear(dim, in_channels)
+    self._rope_cache = RopeCache()
     if modulation_init_std is not None:  # see FluxTransformer2DModel: makes consecutive steps similar
       nn.init.normal_(self.time_proj.weight, std=modulation_init_std)
       nn.init.zeros_(self.time_proj.bias)
@@ -102,7 +103,7 @@ class WanTransformer3DModel(ContextParallelMixin, nn.Module):
     temb = self.time_embedder(timestep_embedding(timestep * self.time_scale, 256).to(dt))
     temb6 = self.time_proj(F.silu(temb)).unflatten(1, (6, -1))
     encoder_hidden_states = self.text_embedder(encoder_hidden_states)
-    rope = rope_tables(rope_frequencies(video_ids, self.axes_dims_rope), dt)
+    rope = self._rope_cache.get((video_ids, ), self.axes_dims_rope, dt)
     for block in self.blocks:
       hidden_states = block(hidden_states, encoder_hidden_states, temb6, rope)
     shift, scale = (self.scale_shift_table.to(dt) + temb[:, None]).unbind(dim=1)
