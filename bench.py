@@ -8,8 +8,15 @@ rdt 0.08 + TaylorSeer order 1, FP8 w8a8 linears, bf16 activations.  A "step" is 
 (one transformer call through `cache_dit_b200.enable_cache`); steps are taken from consecutive
 28-step generations, each started with `refresh_context`.
 
-For N > 1 (torchrun, one rank per GPU) the sequence is sharded by Ulysses context parallelism:
-total work is fixed, so scaling is "strong".  Prints ONE JSON line on rank 0.
+For N > 1 (torchrun, one rank per GPU) the sequence is sharded by Ulysses context parallelism
+(head / token exchange by stores into peer memory on one node): total work is fixed, so scaling is
+"strong".  The block segments between the cache decisions replay as CUDA graphs unless --no-graphs.
+Prints ONE JSON line on rank 0:
+  value / e2e ........ steps/s with inputs resident in HBM / with per-step host<->device copies
+  roofline ........... every FP8 product of the timed steps (CUDA events, eager repeat) against the
+                       library's sustained FP8 rate measured in the same run
+  roofline_cache_kernels, fp8_linear_sweep, cpu_baseline ... the other two parts of the metric
+                       (cache-check HBM GB/s, FP8 linear TFLOP/s) and the host-core baseline
 
 `--impl reference` times the CPU restatement of the same path (the numpy oracle under oracle/) on
 the host cores, on a bounded sample of the step, and prints the same line with "impl": "reference".

@@ -111,3 +111,39 @@ def test_row_norm_rope_matches_eager(heads, d, tokens):
   ref = y * cs + torch.stack([-y2, y1], dim=-1).flatten(-2) * sn
   assert torch.isfinite(out).all().item()
   assert ((out.float() - ref).abs() <= 3 * 2.0**-8 * ref.abs() + 2e-2).all().item()
+
+
+def test_flux_full_size_generation_kernels_vs_oracle_ops():
+  """The benchmark's own workload at full size (19 + 38 blocks, hidden 3072, 4096 + 512 tokens, 28 steps,
+  F8B0, threshold 0.08, TaylorSeer order 1, FP8 linears): hit / miss mask and counters bit-exact, diffs
+  within 1e-3, final latents within 2e-2 relative L2 of the run whose cache arithmetic is the numpy oracle."""
+  from cache_dit_b200.synthetic import FluxDenoisePipeline, FluxTransformer2DModel
+  torch.manual_seed(0)
+  with torch.device("cuda"):
+    model = FluxTransformer2DModel(time_scale=1.0, modulation_init_std=0.02).to(torch.bfloat16)
+  model.eval().requires_grad_(False)
+  cd.quantize(model, cd.QuantizeConfig(quant_type="float8_per_row"))
+  inputs = FluxTransformer2DModel.example_inputs()
+  pipe = FluxDenoisePipeline(model, inputs)
+
+  def run(ops):
+    step_ops.set_ops(ops)
+    try:
+      cd.enable_cache(pipe, cache_config=cd.DBCacheConfig(Fn_compute_blocks=8, Bn_compute_blocks=0,
+                                                          residual_diff_threshold=0.08, max_warmup_steps=8),
+                      calibrator_config=cd.TaylorSeerCalibratorConfig(taylorseer_order=1))
+      out = pipe(num_inference_steps=28)
+      stats = cd.summary(pipe, logging=False)[-1]
+      cd.disable_cache(pipe)
+      return out.float().cpu().numpy(), stats
+    finally:
+      step_ops.set_ops(None)
+
+  got, s_k = run(None)
+  want, s_o = run(OracleStepOps())
+  assert s_k.cached_steps == s_o.cached_steps and len(s_k.cached_steps) >= 5
+  assert set(s_k.residual_diffs) == set(s_o.residual_diffs)
+  for k, v in s_o.residual_diffs.items():
+    assert abs(s_k.residual_diffs[k] - v) <= 1e-3 * abs(v) + 1e-12
+  rel = np.linalg.norm(got - want) / np.linalg.norm(want)
+  assert np.isfinite(got).all() and rel < 2e-2, rel

@@ -53,3 +53,31 @@ def test_config_defaults_match_reference_schema():
   c.update(Fn_compute_blocks=4, residual_diff_threshold=None)
   assert c.Fn_compute_blocks == 4 and c.residual_diff_threshold == 0.08
   assert cd.DBCacheConfig().empty(num_inference_steps=5).Fn_compute_blocks is None
+
+
+def test_ulysses_exchange_mode_selection(monkeypatch):
+  """Without a process group the attention exchange falls back to collectives; explicit choices win and
+  unknown names are refused."""
+  import cache_dit_b200 as cd
+  monkeypatch.delenv("CACHE_DIT_B200_ULYSSES_EXCHANGE", raising=False)
+  assert cd.ParallelismConfig(ulysses_size=2).exchange_mode() == "nccl"
+  assert cd.ParallelismConfig(ulysses_size=2, parallel_kwargs={"exchange": "peer"}).exchange_mode() == "peer"
+  monkeypatch.setenv("CACHE_DIT_B200_ULYSSES_EXCHANGE", "peer")
+  assert cd.ParallelismConfig(ulysses_size=2).exchange_mode() == "peer"
+  monkeypatch.setenv("CACHE_DIT_B200_ULYSSES_EXCHANGE", "carrier-pigeon")
+  import pytest
+  with pytest.raises(ValueError):
+    cd.ParallelismConfig(ulysses_size=2).exchange_mode()
+
+
+def test_token_views_rejoin_without_copy():
+  import torch
+  from cache_dit_b200.synthetic.layers import join_tokens, split_tokens
+  x = torch.arange(2 * 7 * 3, dtype=torch.float32).reshape(2, 7, 3)
+  a, b = split_tokens(x, 3)
+  assert join_tokens(a, b) is x
+  # any other pair is concatenated
+  c = b.clone()
+  y = join_tokens(a, c)
+  assert y is not x and torch.equal(y, x)
+  assert torch.equal(join_tokens(b, a), torch.cat([b, a], dim=1))
