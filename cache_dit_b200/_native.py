@@ -52,6 +52,9 @@ SIGNATURES = {
   "cdb_peer_barrier": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_uint64, c_void_p]),
   "cdb_gather_tokens": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int64, c_int64, c_void_p, c_int64, c_int, c_int,
                                 c_void_p]),
+  "cdb_gather_tokens_fp8": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int64, c_void_p, c_int64,
+                                    c_int, c_int, c_void_p]),
+  "cdb_fp8_dequant_heads": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
   "cdb_peer_sync_bytes": (c_size_t, []),
   "cdb_peer_signal": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p]),
   "cdb_peer_wait": (c_int, [c_void_p, c_int, c_void_p, c_uint64, c_void_p]),
@@ -381,7 +384,7 @@ class ScatterJob(ctypes.Structure):
   _fields_ = [("x", c_void_p), ("ld_x", c_int64), ("tokens", c_int64), ("tokens_per_batch", c_int64),
               ("norm_weight", c_void_p), ("norm_across_heads", c_int), ("eps", c_float), ("cos_table", c_void_p),
               ("sin_table", c_void_p), ("table_row_offset", c_int), ("dst_ptrs", c_void_p),
-              ("dst_batch_stride", c_int64), ("dst_row_offset", c_int64)]
+              ("dst_batch_stride", c_int64), ("dst_row_offset", c_int64), ("dst_scale_ptrs", c_void_p)]
 
 
 def scatter_heads_multi(jobs, heads: int):
@@ -415,6 +418,10 @@ def scatter_heads_multi(jobs, heads: int):
     slot.table_row_offset = int(j.get("table_row_offset", 0))
     slot.dst_ptrs = ctypes.cast(ptrs, c_void_p)
     slot.dst_batch_stride, slot.dst_row_offset = int(j["dst_batch_stride"]), int(j["dst_row_offset"])
+    if j.get("dst_scale_ptrs") is not None:  # FP8 on the wire
+      sptrs = _ptr_array(j["dst_scale_ptrs"])
+      keep.append(sptrs)
+      slot.dst_scale_ptrs = ctypes.cast(sptrs, c_void_p)
   st = lib().cdb_scatter_heads_multi(ctypes.cast(arr, c_void_p), len(jobs), world, heads, d, _stream(x0))
   check(st, "cdb_scatter_heads_multi")
 
@@ -422,3 +429,31 @@ def scatter_heads_multi(jobs, heads: int):
 def peer_barrier(flag_ptrs, my_flags, my_rank: int, sync, timeout_ns: int):
   check(lib().cdb_peer_barrier(_ptr_array(flag_ptrs), _ptr(my_flags), len(flag_ptrs), int(my_rank), _ptr(sync),
                                int(timeout_ns), _stream(my_flags)), "cdb_peer_barrier")
+
+
+def gather_tokens_fp8(o, dst_ptrs, dst_scale_ptrs, my_rank: int, row_starts=None, dst_token_capacity=None):
+  """`gather_tokens` with e4m3 bytes + one bf16 scale per (token, head) on the wire."""
+  _need_cuda(o)
+  _need_contig(o)
+  b, s, h, d = o.shape
+  world = len(dst_ptrs)
+  starts = None if row_starts is None else (c_int64 * (world + 1))(*[int(v) for v in row_starts])
+  if dst_token_capacity is None:
+    dst_token_capacity = s // world if row_starts is None else max(row_starts[r + 1] - row_starts[r] for r in range(world))
+  st = lib().cdb_gather_tokens_fp8(_ptr(o), _ptr_array(dst_ptrs), _ptr_array(dst_scale_ptrs), world, int(my_rank), b, s,
+                                   starts, int(dst_token_capacity), h, d, _stream(o))
+  check(st, "cdb_gather_tokens_fp8")
+
+
+def fp8_dequant_heads(q_list, scale_list, out_list, head_dim: int):
+  """out = bf16(float(q) * scale) per row of head_dim e4m3 bytes; scales float32 or bf16; up to 3 tensors."""
+  _need_cuda(*q_list, *scale_list, *out_list)
+  _need_contig(*q_list, *scale_list, *out_list)
+  n = len(q_list)
+  rows = (c_int64 * n)(*[q.numel() * q.element_size() // head_dim for q in q_list])
+  bf16_scales = scale_list[0].dtype == torch.bfloat16
+  st = lib().cdb_fp8_dequant_heads(_ptr_array([q.data_ptr() for q in q_list]),
+                                   _ptr_array([s.data_ptr() for s in scale_list]),
+                                   _ptr_array([o.data_ptr() for o in out_list]), rows, n, int(head_dim),
+                                   int(bf16_scales), _stream(out_list[0]))
+  check(st, "cdb_fp8_dequant_heads")

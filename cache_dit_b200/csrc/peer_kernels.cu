@@ -13,6 +13,9 @@
 // loads are local: ordinary 16-byte st.global to a mapped peer address, nothing else crosses NVLink.
 // Every launch is a fixed sequence of pointers and sizes, so whole block segments, exchange included,
 // can be captured in a CUDA graph; the barrier's epoch lives in device memory for that reason.
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+
 #include <cstring>
 
 #include "common.cuh"
@@ -44,7 +47,8 @@ __device__ __forceinline__ void scatter_heads_body(const __nv_bfloat16* __restri
                                                    const __nv_bfloat16* __restrict__ sn, int table_row_offset,
                                                    const PeerPtrs& dst, int heads_per_rank, int64_t ld_out,
                                                    int64_t out_batch_stride, int64_t tokens, int64_t tokens_per_batch,
-                                                   int64_t dst_row_offset, int heads, float eps, float* s_part) {
+                                                   int64_t dst_row_offset, int heads, float eps, float* s_part,
+                                                   const PeerPtrs* dst_scale = nullptr) {
   constexpr int D = LPH * 8;
   constexpr bool NORM_ROPE = MODE != SCATTER_COPY;
   const int npk = heads * LPH;
@@ -123,7 +127,40 @@ __device__ __forceinline__ void scatter_heads_body(const __nv_bfloat16* __restri
             ow[i] = pb2u(__hadd2_rn(__hmul2_rn(y, pu2b(cw[i])), __hmul2_rn(r, pu2b(sw[i]))));
           }
         }
-        if (p < npk) {
+        if (dst_scale != nullptr) {
+          // FP8 on the wire (the reference's `ulysses_float8`, kernels/triton/_float8_comm.py:78-124): one scale
+          // per (token, head), s = max(amax / 448, 1e-6), e4m3(clamp(x / s)); the destination holds bytes + scales.
+          __nv_bfloat162 m2 = __habs2(pu2b(ow[0]));
+#pragma unroll
+          for (int i = 1; i < 4; ++i) m2 = __hmax2(m2, __habs2(pu2b(ow[i])));
+          const uint32_t mu = pb2u(m2);
+          float amax = fmaxf(__uint_as_float(mu << 16), __uint_as_float(mu & 0xffff0000u));
+#pragma unroll
+          for (int o = LPH / 2; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+          const float sc = fmaxf(__fdiv_rn(amax, 448.0f), 1e-6f);
+          if (p < npk) {
+            uint32_t q[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const uint32_t a = ow[2 * h], b2 = ow[2 * h + 1];
+              const uint32_t lo = __nv_cvt_float2_to_fp8x2(
+                  make_float2(__fdiv_rn(__uint_as_float(a << 16), sc), __fdiv_rn(__uint_as_float(a & 0xffff0000u), sc)),
+                  __NV_SATFINITE, __NV_E4M3);
+              const uint32_t hi = __nv_cvt_float2_to_fp8x2(
+                  make_float2(__fdiv_rn(__uint_as_float(b2 << 16), sc), __fdiv_rn(__uint_as_float(b2 & 0xffff0000u), sc)),
+                  __NV_SATFINITE, __NV_E4M3);
+              q[h] = lo | (hi << 16);
+            }
+            const int head = p / LPH;
+            const int owner = head / heads_per_rank;
+            const int local_head = head - owner * heads_per_rank;
+            uint8_t* base8 = static_cast<uint8_t*>(dst.p[owner]);
+            *reinterpret_cast<uint2*>(base8 + dst_elem + (int64_t)local_head * D + (int64_t)(p - head * LPH) * 8) =
+                make_uint2(q[0], q[1]);
+            if (p == head * LPH)
+              static_cast<float*>(dst_scale->p[owner])[dst_elem / D + local_head] = sc;
+          }
+        } else if (p < npk) {
           const int head = p / LPH;
           const int owner = head / heads_per_rank;
           const int local_head = head - owner * heads_per_rank;
@@ -157,8 +194,9 @@ struct ScatterJob {
   const __nv_bfloat16* cs;
   const __nv_bfloat16* sn;
   PeerPtrs dst;
+  PeerPtrs dst_scale;  // used when fp8_out != 0
   int64_t ld_x, out_batch_stride, tokens, tokens_per_batch, dst_row_offset;
-  int table_row_offset, mode;
+  int table_row_offset, mode, fp8_out;
   float eps;
 };
 struct ScatterJobs {
@@ -171,18 +209,19 @@ __global__ void __launch_bounds__(SC_THREADS)
   __shared__ float s_part[SC_THREADS / 32];
   const ScatterJob& j = jobs.job[blockIdx.y];
   if ((int64_t)blockIdx.x >= j.tokens) return;
+  const PeerPtrs* ds = j.fp8_out ? &j.dst_scale : nullptr;
   if (j.mode == SCATTER_COPY)
     scatter_heads_body<LPH, SCATTER_COPY>(j.x, j.ld_x, j.w, j.cs, j.sn, j.table_row_offset, j.dst, heads_per_rank, ld_out,
                                           j.out_batch_stride, j.tokens, j.tokens_per_batch, j.dst_row_offset, heads,
-                                          j.eps, s_part);
+                                          j.eps, s_part, ds);
   else if (j.mode == SCATTER_HEAD_NORM)
     scatter_heads_body<LPH, SCATTER_HEAD_NORM>(j.x, j.ld_x, j.w, j.cs, j.sn, j.table_row_offset, j.dst, heads_per_rank,
                                                ld_out, j.out_batch_stride, j.tokens, j.tokens_per_batch,
-                                               j.dst_row_offset, heads, j.eps, s_part);
+                                               j.dst_row_offset, heads, j.eps, s_part, ds);
   else
     scatter_heads_body<LPH, SCATTER_ROW_NORM>(j.x, j.ld_x, j.w, j.cs, j.sn, j.table_row_offset, j.dst, heads_per_rank,
                                               ld_out, j.out_batch_stride, j.tokens, j.tokens_per_batch,
-                                              j.dst_row_offset, heads, j.eps, s_part);
+                                              j.dst_row_offset, heads, j.eps, s_part, ds);
 }
 
 // Attention output of this rank, [batch, all tokens, own heads, head_dim]: the row of token s goes
@@ -210,6 +249,94 @@ __global__ void __launch_bounds__(128)
     uint4* out = reinterpret_cast<uint4*>(base_ptr + ((b * dst_token_capacity + local_s) * heads_all +
                                                       (int64_t)my_rank * heads_per_rank) * head_dim);
     for (int p = threadIdx.x; p < row_packets; p += blockDim.x) out[p] = __ldcs(src + p);
+  }
+}
+
+// FP8 variant of the gather (the reference's per-token output quantization, _float8_comm.py:6-44 with
+// eps = 1e-4 and the scale stored as bf16): per (token, head) s = max(amax, 1e-4) / 448, e4m3(clamp(x * (1/s))),
+// the owner receives bytes and bf16 scales and multiplies by the ROUNDED scale when it unpacks.
+__global__ void __launch_bounds__(128)
+    gather_tokens_fp8_kernel(const __nv_bfloat16* __restrict__ o, const PeerPtrs dst, const PeerPtrs dst_scale,
+                             const PeerRows rows_of, int world, int my_rank, int64_t batch, int64_t tokens_all,
+                             int64_t dst_token_capacity, int heads_per_rank, int heads_all, int head_dim) {
+  const int lph = head_dim / 8;  // lanes per head: 8, 16 or 32
+  const int row_packets = heads_per_rank * lph;
+  const int64_t rows = batch * tokens_all;
+  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+    const int64_t b = r / tokens_all, s = r - b * tokens_all;
+    int owner = 0;
+    while (owner + 1 < world && s >= rows_of.start[owner + 1]) ++owner;
+    const int64_t local_s = s - rows_of.start[owner];
+    const uint4* src = reinterpret_cast<const uint4*>(o + r * (int64_t)heads_per_rank * head_dim);
+    const int64_t dst_head0 = (b * dst_token_capacity + local_s) * heads_all + (int64_t)my_rank * heads_per_rank;
+    uint8_t* out8 = static_cast<uint8_t*>(dst.p[owner]) + dst_head0 * head_dim;
+    __nv_bfloat16* out_s = static_cast<__nv_bfloat16*>(dst_scale.p[owner]) + dst_head0;
+    const int passes = (row_packets + 127) / 128;
+    for (int pass = 0; pass < passes; ++pass) {  // uniform trip count: the shuffles need whole warps
+      const int p = pass * 128 + threadIdx.x;
+      const uint4 v = p < row_packets ? __ldcs(src + p) : make_uint4(0, 0, 0, 0);
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+      __nv_bfloat162 m2 = __habs2(pu2b(w[0]));
+#pragma unroll
+      for (int i = 1; i < 4; ++i) m2 = __hmax2(m2, __habs2(pu2b(w[i])));
+      const uint32_t mu = pb2u(m2);
+      float amax = fmaxf(__uint_as_float(mu << 16), __uint_as_float(mu & 0xffff0000u));
+      for (int off = lph / 2; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+      const float sc = __fdiv_rn(fmaxf(amax, 1e-4f), 448.0f);
+      const float inv = __fdiv_rn(1.0f, sc);
+      if (p < row_packets) {
+        uint32_t q[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const uint32_t a = w[2 * h], b2 = w[2 * h + 1];
+          const uint32_t lo = __nv_cvt_float2_to_fp8x2(
+              make_float2(__fmul_rn(__uint_as_float(a << 16), inv), __fmul_rn(__uint_as_float(a & 0xffff0000u), inv)),
+              __NV_SATFINITE, __NV_E4M3);
+          const uint32_t hi = __nv_cvt_float2_to_fp8x2(
+              make_float2(__fmul_rn(__uint_as_float(b2 << 16), inv), __fmul_rn(__uint_as_float(b2 & 0xffff0000u), inv)),
+              __NV_SATFINITE, __NV_E4M3);
+          q[h] = lo | (hi << 16);
+        }
+        *reinterpret_cast<uint2*>(out8 + (int64_t)p * 8) = make_uint2(q[0], q[1]);
+        if (p % lph == 0) out_s[p / lph] = __float2bfloat16_rn(sc);
+      }
+    }
+  }
+}
+
+// Unpack e4m3 rows of `head_dim` bytes with one scale each into bf16: out = bf16(float(q) * scale).
+// SCALE_T = float (q / k / v) or __nv_bfloat16 (attention output).  Up to 3 tensors per launch.
+struct DequantJobs {
+  const uint8_t* q[3];
+  const void* scale[3];
+  __nv_bfloat16* out[3];
+  int64_t rows[3];
+};
+template <typename SCALE_T>
+__global__ void __launch_bounds__(256)
+    dequant_heads_kernel(const __grid_constant__ DequantJobs jobs, int head_dim) {
+  const int j = blockIdx.y;
+  const int pk_per_row = head_dim / 16;  // 16 bytes in, 32 bytes out per thread and step
+  const int64_t total = jobs.rows[j] * pk_per_row;
+  const uint4* src = reinterpret_cast<const uint4*>(jobs.q[j]);
+  const SCALE_T* sc = static_cast<const SCALE_T*>(jobs.scale[j]);
+  uint4* dst = reinterpret_cast<uint4*>(jobs.out[j]);
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const float s = (float)sc[i / pk_per_row];
+    const uint4 v = __ldcs(src + i);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    uint32_t o[8];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const __half2_raw lo = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w[k] & 0xffffu), __NV_E4M3);
+      const __half2_raw hi = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w[k] >> 16), __NV_E4M3);
+      const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&lo));
+      const float2 b2 = __half22float2(*reinterpret_cast<const __half2*>(&hi));
+      o[2 * k] = pb2u(__floats2bfloat162_rn(__fmul_rn(a.x, s), __fmul_rn(a.y, s)));
+      o[2 * k + 1] = pb2u(__floats2bfloat162_rn(__fmul_rn(b2.x, s), __fmul_rn(b2.y, s)));
+    }
+    dst[2 * i] = make_uint4(o[0], o[1], o[2], o[3]);
+    dst[2 * i + 1] = make_uint4(o[4], o[5], o[6], o[7]);
   }
 }
 
@@ -423,6 +550,7 @@ struct cdb_scatter_job_abi {  // mirrors `cdb_scatter_job` of the public header
   int table_row_offset;
   void* const* dst_ptrs;
   int64_t dst_batch_stride, dst_row_offset;
+  void* const* dst_scale_ptrs;  // non-NULL: FP8 bytes go to dst_ptrs, one float32 scale per (token, head) here
 };
 
 extern "C" int cdb_scatter_heads_multi(const void* jobs_v, int njobs, int world, int heads, int head_dim, void* stream) {
@@ -454,6 +582,8 @@ extern "C" int cdb_scatter_heads_multi(const void* jobs_v, int njobs, int world,
     o.table_row_offset = in.table_row_offset;
     o.mode = !norm ? SCATTER_COPY : (in.norm_across_heads ? SCATTER_ROW_NORM : SCATTER_HEAD_NORM);
     o.eps = in.eps;
+    o.fp8_out = in.dst_scale_ptrs != nullptr;
+    if (o.fp8_out && !fill_ptrs(&o.dst_scale, in.dst_scale_ptrs, world)) return CDB_ERR_BAD_ARGUMENT;
     max_tokens = in.tokens > max_tokens ? in.tokens : max_tokens;
   }
   if (max_tokens == 0) return CDB_OK;
@@ -507,6 +637,61 @@ extern "C" int cdb_gather_tokens(const void* o, void* const* dst_ptrs, int world
   gather_tokens_kernel<<<(unsigned)(rows < cap ? rows : cap), 128, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(o), dst, rows_of, world, my_rank, batch, tokens_all, dst_token_capacity,
       heads_per_rank, heads_per_rank * world, head_dim);
+  CDB_CUDA_CHECK(cudaGetLastError());
+  return CDB_OK;
+}
+
+extern "C" int cdb_gather_tokens_fp8(const void* o, void* const* dst_ptrs, void* const* dst_scale_ptrs, int world,
+                                     int my_rank, int64_t batch, int64_t tokens_all, const int64_t* row_starts,
+                                     int64_t dst_token_capacity, int heads_per_rank, int head_dim, void* stream) {
+  PeerPtrs dst, dst_scale;
+  if (!o || batch <= 0 || tokens_all <= 0 || heads_per_rank <= 0 || my_rank < 0 || my_rank >= world ||
+      !fill_ptrs(&dst, dst_ptrs, world) || !fill_ptrs(&dst_scale, dst_scale_ptrs, world))
+    return CDB_ERR_BAD_ARGUMENT;
+  if ((head_dim != 64 && head_dim != 128 && head_dim != 256) || !aligned16(o)) return CDB_ERR_UNSUPPORTED;
+  PeerRows rows_of{};
+  if (row_starts) {
+    for (int r = 0; r <= world; ++r) rows_of.start[r] = row_starts[r];
+    if (rows_of.start[0] != 0 || rows_of.start[world] != tokens_all) return CDB_ERR_BAD_ARGUMENT;
+  } else {
+    if (tokens_all % world != 0) return CDB_ERR_BAD_ARGUMENT;
+    for (int r = 0; r <= world; ++r) rows_of.start[r] = tokens_all / world * r;
+  }
+  for (int r = 0; r < world; ++r)
+    if (rows_of.start[r + 1] - rows_of.start[r] < 0 || rows_of.start[r + 1] - rows_of.start[r] > dst_token_capacity)
+      return CDB_ERR_BAD_ARGUMENT;
+  const int64_t rows = batch * tokens_all;
+  const int64_t cap = (int64_t)sm_count() * 16;
+  gather_tokens_fp8_kernel<<<(unsigned)(rows < cap ? rows : cap), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(o), dst, dst_scale, rows_of, world, my_rank, batch, tokens_all,
+      dst_token_capacity, heads_per_rank, heads_per_rank * world, head_dim);
+  CDB_CUDA_CHECK(cudaGetLastError());
+  return CDB_OK;
+}
+
+extern "C" int cdb_fp8_dequant_heads(const void* const* q, const void* const* scales, void* const* out,
+                                     const int64_t* rows, int njobs, int head_dim, int scales_are_bf16, void* stream) {
+  if (!q || !scales || !out || !rows || njobs < 1 || njobs > 3) return CDB_ERR_BAD_ARGUMENT;
+  if (head_dim % 16 != 0) return CDB_ERR_UNSUPPORTED;
+  DequantJobs jobs{};
+  int64_t max_rows = 0;
+  for (int i = 0; i < njobs; ++i) {
+    if (!q[i] || !scales[i] || !out[i] || rows[i] < 0) return CDB_ERR_BAD_ARGUMENT;
+    if (!aligned16(q[i]) || !aligned16(out[i])) return CDB_ERR_UNSUPPORTED;
+    jobs.q[i] = static_cast<const uint8_t*>(q[i]);
+    jobs.scale[i] = scales[i];
+    jobs.out[i] = static_cast<__nv_bfloat16*>(out[i]);
+    jobs.rows[i] = rows[i];
+    max_rows = rows[i] > max_rows ? rows[i] : max_rows;
+  }
+  if (max_rows == 0) return CDB_OK;
+  const int64_t total = max_rows * (head_dim / 16);
+  const int64_t want = (total + 255) / 256;
+  const int64_t cap = (int64_t)sm_count() * 8;
+  const dim3 grid((unsigned)(want < cap ? want : cap), (unsigned)njobs);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (scales_are_bf16) dequant_heads_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(jobs, head_dim);
+  else dequant_heads_kernel<float><<<grid, 256, 0, st>>>(jobs, head_dim);
   CDB_CUDA_CHECK(cudaGetLastError());
   return CDB_OK;
 }

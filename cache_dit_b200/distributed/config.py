@@ -38,8 +38,6 @@ class ParallelismConfig:
       raise NotImplementedError("ring attention is not built in cache_dit_b200 (Ulysses only)")
     if (self.tp_size or 1) > 1:
       raise NotImplementedError("tensor parallelism is not built in cache_dit_b200 (context parallel only)")
-    if self.ulysses_float8:
-      raise NotImplementedError("FP8 all-to-all is not built in cache_dit_b200 yet")
     if self.ulysses_async:
       raise NotImplementedError("async Ulysses is not built in cache_dit_b200 yet")
     if self.cp_enabled() and dist.is_available() and dist.is_initialized():

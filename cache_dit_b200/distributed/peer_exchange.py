@@ -43,7 +43,10 @@ def _as_tensor(ptr: int, shape, dtype: torch.dtype, device) -> torch.Tensor:
 class PeerExchange:
   """Buffers, flags and launch helpers of one rank.  Construction and `ensure` are collective."""
 
-  def __init__(self, group=None, device: Optional[torch.device] = None, timeout_s: float = 10.0):
+  def __init__(self, group=None, device: Optional[torch.device] = None, timeout_s: float = 10.0, fp8: bool = False):
+    # fp8: e4m3 bytes + one scale per (token, head) cross NVLink instead of bf16 (the reference's
+    # `ulysses_float8`, src/cache_dit/distributed/core/_distributed_primitives.py:741-813); the receiver unpacks
+    self.fp8 = bool(fp8)
     self.group = group
     self.world = dist.get_world_size(group)
     self.rank = dist.get_rank(group)
@@ -98,13 +101,31 @@ class PeerExchange:
     self.uneven = len(set(counts)) > 1
     esz = torch.empty((), dtype=dtype).element_size()
     hpr, all_tokens = heads // self.world, self.row_starts[-1]
-    for name in ("q", "k", "v"):
-      shape = (batch, all_tokens, hpr, head_dim)
-      own, self.ptrs[name] = self._alloc_shared(batch * all_tokens * hpr * head_dim * esz)
-      self.buffers[name] = _as_tensor(own, shape, dtype, self.device)
-    shape = (batch, self.capacity, heads, head_dim)
-    own, self.ptrs["o"] = self._alloc_shared(batch * self.capacity * heads * head_dim * esz)
-    self.buffers["o"] = _as_tensor(own, shape, dtype, self.device)
+    self.head_dim = head_dim
+    if not self.fp8:
+      for name in ("q", "k", "v"):
+        shape = (batch, all_tokens, hpr, head_dim)
+        own, self.ptrs[name] = self._alloc_shared(batch * all_tokens * hpr * head_dim * esz)
+        self.buffers[name] = _as_tensor(own, shape, dtype, self.device)
+      shape = (batch, self.capacity, heads, head_dim)
+      own, self.ptrs["o"] = self._alloc_shared(batch * self.capacity * heads * head_dim * esz)
+      self.buffers["o"] = _as_tensor(own, shape, dtype, self.device)
+    else:
+      if dtype != torch.bfloat16:
+        raise NotImplementedError("FP8 exchange packs bf16 activations")
+      for name in ("q", "k", "v"):
+        n = batch * all_tokens * hpr
+        own, self.ptrs[name] = self._alloc_shared(n * head_dim)
+        self.buffers[name + "8"] = _as_tensor(own, (n * head_dim // 4, ), torch.int32, self.device)
+        own, self.ptrs[name + "_scale"] = self._alloc_shared(n * 4)
+        self.buffers[name + "_scale"] = _as_tensor(own, (n, ), torch.float32, self.device)
+        self.buffers[name] = torch.empty(batch, all_tokens, hpr, head_dim, dtype=dtype, device=self.device)
+      n = batch * self.capacity * heads
+      own, self.ptrs["o"] = self._alloc_shared(n * head_dim)
+      self.buffers["o8"] = _as_tensor(own, (n * head_dim // 4, ), torch.int32, self.device)
+      own, self.ptrs["o_scale"] = self._alloc_shared(n * 2)
+      self.buffers["o_scale"] = _as_tensor(own, (n, ), torch.bfloat16, self.device)
+      self.buffers["o"] = torch.empty(batch, self.capacity, heads, head_dim, dtype=dtype, device=self.device)
     self._shape_key = key
     dist.barrier(group=self.group)
 
@@ -112,6 +133,9 @@ class PeerExchange:
   def scatter(self, name: str, x: torch.Tensor, heads: int, row_offset_local: int, norm_weight=None, cos=None,
               sin=None, eps: float = 0.0, across_heads: bool = False):
     """x [batch, t, heads*head_dim]: this rank's rows [row_offset_local, +t) of its token shard."""
+    if self.fp8:
+      return self.scatter_jobs([self.scatter_job(name, x, row_offset_local, norm_weight, cos, sin, eps, across_heads)],
+                               heads)
     buf = self.buffers[name]
     _native.scatter_heads(x, norm_weight, cos, sin, row_offset_local, self.ptrs[name], buf.stride(0),
                           self.row_starts[self.rank] + row_offset_local, heads, eps, across_heads)
@@ -121,7 +145,8 @@ class PeerExchange:
     """The same scatter as a job description for `scatter_jobs` (several in one launch)."""
     return dict(x=x, norm_weight=norm_weight, cos=cos, sin=sin, table_row_offset=row_offset_local,
                 dst_ptrs=self.ptrs[name], dst_batch_stride=self.buffers[name].stride(0),
-                dst_row_offset=self.row_starts[self.rank] + row_offset_local, eps=eps, across_heads=across_heads)
+                dst_row_offset=self.row_starts[self.rank] + row_offset_local, eps=eps, across_heads=across_heads,
+                dst_scale_ptrs=self.ptrs[name + "_scale"] if self.fp8 else None)
 
   def scatter_jobs(self, jobs, heads: int):
     for i in range(0, len(jobs), 6):
@@ -130,10 +155,24 @@ class PeerExchange:
   def barrier(self):
     _native.peer_barrier(self.flag_ptrs, self.flags, self.rank, self.sync, self.timeout_ns)
 
+  def qkv_ready(self):
+    """After the scatters of all ranks: wait for them, and unpack the FP8 wire format if it is in use."""
+    self.barrier()
+    if self.fp8:
+      b = self.buffers
+      _native.fp8_dequant_heads([b["q8"], b["k8"], b["v8"]], [b["q_scale"], b["k_scale"], b["v_scale"]],
+                                [b["q"], b["k"], b["v"]], self.head_dim)
+
   def gather_output(self, o_local: torch.Tensor) -> torch.Tensor:
     """o_local [batch, tokens_all, heads / W, head_dim] -> this rank's `o` buffer after the exchange."""
-    _native.gather_tokens(o_local, self.ptrs["o"], self.rank, self.row_starts, self.capacity)
-    self.barrier()
+    if self.fp8:
+      _native.gather_tokens_fp8(o_local, self.ptrs["o"], self.ptrs["o_scale"], self.rank, self.row_starts, self.capacity)
+      self.barrier()
+      b = self.buffers
+      _native.fp8_dequant_heads([b["o8"]], [b["o_scale"]], [b["o"]], self.head_dim)
+    else:
+      _native.gather_tokens(o_local, self.ptrs["o"], self.rank, self.row_starts, self.capacity)
+      self.barrier()
     out = self.buffers["o"]
     return out if self.tokens_local == self.capacity else out[:, :self.tokens_local]
 

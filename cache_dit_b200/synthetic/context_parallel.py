@@ -25,7 +25,10 @@ class ContextParallelMixin:
     exchange = None
     if config.exchange_mode() == "peer":
       from ..distributed.peer_exchange import PeerExchange
-      exchange = PeerExchange(group)
+      exchange = PeerExchange(group, fp8=bool(config.ulysses_float8))
+    elif config.ulysses_float8:
+      raise NotImplementedError("FP8 head/token exchange is built for the peer-memory exchange only "
+                                "(parallel_kwargs={'exchange': 'peer'})")
     self._cp = UlyssesGroup(group, exchange)
     for block in self._cp_blocks():
       block.cp = self._cp

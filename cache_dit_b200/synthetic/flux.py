@@ -164,7 +164,10 @@ class FluxTransformer2DModel(nn.Module):
     exchange = None
     if config.exchange_mode() == "peer":
       from ..distributed.peer_exchange import PeerExchange
-      exchange = PeerExchange(group)
+      exchange = PeerExchange(group, fp8=bool(config.ulysses_float8))
+    elif config.ulysses_float8:
+      raise NotImplementedError("FP8 head/token exchange is built for the peer-memory exchange only "
+                                "(parallel_kwargs={'exchange': 'peer'})")
     self._cp = UlyssesGroup(group, exchange)
     for block in list(self.transformer_blocks) + list(self.single_transformer_blocks):
       block.cp = self._cp

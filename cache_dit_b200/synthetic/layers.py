@@ -242,7 +242,7 @@ def joint_attention(q_parts, k_parts, v_parts, rope, heads: int, cp: Optional["U
     jobs.append(ex.scatter_job("v", xv, off))
     off += xq.shape[1]
   ex.scatter_jobs(jobs, heads)
-  ex.barrier()
+  ex.qkv_ready()
   b = ex.buffers
   o = F.scaled_dot_product_attention(b["q"].transpose(1, 2), b["k"].transpose(1, 2), b["v"].transpose(1, 2))
   o = o.transpose(1, 2).contiguous()  # [B, S_all, H/W, D]

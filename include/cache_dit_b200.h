@@ -247,12 +247,26 @@ typedef struct cdb_scatter_job {
   int table_row_offset;
   void* const* dst_ptrs; /* `world` addresses */
   int64_t dst_batch_stride, dst_row_offset;
+  /* FP8 on the wire (the reference's `ulysses_float8`): NULL = bf16.  Otherwise dst_ptrs receive e4m3 bytes
+   * in the same [batch, rows, heads/world, head_dim] layout and these `world` buffers one float32 scale per
+   * (token, head): s = max(amax/448, 1e-6), q = e4m3(clamp(x / s))
+   * (src/cache_dit/kernels/triton/_float8_comm.py:78-124). */
+  void* const* dst_scale_ptrs;
 } cdb_scatter_job;
 CDB_API int cdb_scatter_heads_multi(const void* jobs /* cdb_scatter_job[njobs] */, int njobs, int world, int heads,
                             int head_dim, void* stream);
 CDB_API int cdb_gather_tokens(const void* o, void* const* dst_ptrs, int world, int my_rank, int64_t batch,
                       int64_t tokens_all, const int64_t* row_starts, int64_t dst_token_capacity,
                       int heads_per_rank, int head_dim, void* stream);
+/* FP8 variant of cdb_gather_tokens (per (token, head): s = max(amax, 1e-4)/448, q = e4m3(clamp(x * (1/s))),
+ * scale stored as bf16; src/cache_dit/kernels/triton/_float8_comm.py:6-44 as called at
+ * src/cache_dit/kernels/triton/_ops_registery.py:50-76), and the unpacking of either format on the receiver:
+ * out = bf16(float(q) * scale) for up to 3 tensors of `rows[i]` rows of head_dim bytes. */
+CDB_API int cdb_gather_tokens_fp8(const void* o, void* const* dst_ptrs, void* const* dst_scale_ptrs, int world,
+                          int my_rank, int64_t batch, int64_t tokens_all, const int64_t* row_starts,
+                          int64_t dst_token_capacity, int heads_per_rank, int head_dim, void* stream);
+CDB_API int cdb_fp8_dequant_heads(const void* const* q, const void* const* scales, void* const* out,
+                          const int64_t* rows, int njobs, int head_dim, int scales_are_bf16, void* stream);
 CDB_API size_t cdb_peer_sync_bytes(void);
 CDB_API int cdb_peer_signal(void* const* flag_ptrs, int world, int my_rank, void* sync, void* stream);
 CDB_API int cdb_peer_wait(const void* my_flags, int world, void* sync, uint64_t timeout_ns, void* stream);

@@ -18,7 +18,7 @@ sys.path.insert(0, ROOT)
 import cache_dit_b200 as cd  # noqa: E402
 
 
-def generation(world, exchange, graphs, steps=10):
+def generation(world, exchange, graphs, steps=10, fp8_wire=False):
   from cache_dit_b200.synthetic import FluxTransformer2DModel
   torch.manual_seed(0)
   with torch.device("cuda"):
@@ -30,7 +30,8 @@ def generation(world, exchange, graphs, steps=10):
                   cache_config=cd.DBCacheConfig(Fn_compute_blocks=2, Bn_compute_blocks=0, residual_diff_threshold=0.13,
                                                 max_warmup_steps=3, num_inference_steps=steps),
                   calibrator_config=cd.TaylorSeerCalibratorConfig(taylorseer_order=1),
-                  parallelism_config=cd.ParallelismConfig(ulysses_size=world, parallel_kwargs={"exchange": exchange}),
+                  parallelism_config=cd.ParallelismConfig(ulysses_size=world, ulysses_float8=fp8_wire,
+                                                          parallel_kwargs={"exchange": exchange}),
                   quantize_config=cd.QuantizeConfig(quant_type="float8_per_row"))
   if graphs:
     cd.enable_cuda_graphs(model, warmup_calls=1)
@@ -102,6 +103,8 @@ def main():
   nccl, _, _ = generation(world, "nccl", False)
   peer, st_peer, _ = generation(world, "peer", False)
   graphed, st_graph, replays = generation(world, "peer", True)
+  wire8, st_wire8, _ = generation(world, "peer", True, fp8_wire=True)
+  rel8 = float((wire8[-1][0].float() - peer[-1][0].float()).norm() / peer[-1][0].float().norm())
   others = {}
   for which in ("qwen", "wan"):
     o_nccl, m_nccl, _ = other_model(world, which, "nccl", False)
@@ -111,7 +114,8 @@ def main():
                          peer_equals_nccl=bool(torch.equal(o_nccl, o_peer)),
                          graphs_equal_peer=bool(torch.equal(o_peer, o_graph)),
                          finite=bool(torch.isfinite(o_peer).all().item()))
-  report = dict(others=others,
+  report = dict(others=others, fp8_wire=dict(rel=rel8, status=st_wire8, masks=[m for _, m in wire8],
+                                             finite=bool(torch.isfinite(wire8[-1][0]).all().item())),
     masks_nccl=[m for _, m in nccl], masks_peer=[m for _, m in peer], masks_graphs=[m for _, m in graphed],
     peer_equals_nccl=all(torch.equal(a, b) for (a, _), (b, _) in zip(nccl, peer)),
     graphs_equal_peer=all(torch.equal(a, b) for (a, _), (b, _) in zip(peer, graphed)),

@@ -49,3 +49,12 @@ def test_other_models_peer_exchange(reports, model):
     assert o["masks"][0] == o["masks"][1] == o["masks"][2] and o["masks"][0]
     assert o["peer_equals_nccl"] and o["graphs_equal_peer"]
   assert reports[0]["others"][model]["masks"] == reports[1]["others"][model]["masks"]
+
+
+def test_fp8_on_the_wire(reports):
+  """`ulysses_float8`: e4m3 + per-(token, head) scales cross NVLink; lossy, so close to, not equal to, bf16."""
+  for r in reports:
+    f = r["fp8_wire"]
+    assert f["finite"] and f["status"] == 0
+    assert f["rel"] < 0.1, f["rel"]
+  assert reports[0]["fp8_wire"]["masks"] == reports[1]["fp8_wire"]["masks"]

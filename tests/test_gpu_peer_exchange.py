@@ -109,3 +109,59 @@ def test_flag_protocol_and_bounded_wait(nat):
   t1.record()
   torch.cuda.synchronize()
   assert t0.elapsed_time(t1) < 100.0
+
+
+def _bf16(a):
+  import numpy as np
+  return torch.from_numpy(np.asarray(a, dtype=np.float32)).to(torch.bfloat16).float().numpy()
+
+
+@pytest.mark.parametrize("world,tokens,heads,d", [(2, 40, 4, 64), (4, 24, 8, 128)])
+def test_fp8_wire_format_matches_restatement(nat, world, tokens, heads, d):
+  """e4m3 bytes + one scale per (token, head) on the wire, unpacked on the receiver: both directions
+  against a numpy restatement of the reference's quantization rules (kernels/triton/_float8_comm.py)."""
+  import numpy as np
+  from oracle import fp8_oracle as FO
+  g = torch.Generator().manual_seed(world + d)
+  c, hpr, bf = heads * d, heads // world, torch.bfloat16
+  xs = [torch.randn(1, tokens, c, generator=g).mul(torch.rand(1, tokens, 1, generator=g) * 4).to("cuda", bf)
+        for _ in range(world)]
+  xs[0][0, 3, :d] = 0  # an all-zero head: the scale floor applies
+  n = tokens * world * hpr
+  q8 = [torch.zeros(n * d // 4, dtype=torch.int32, device="cuda") for _ in range(world)]
+  sc = [torch.zeros(n, dtype=torch.float32, device="cuda") for _ in range(world)]
+  out = [torch.empty(1, tokens * world, hpr, d, dtype=bf, device="cuda") for _ in range(world)]
+  for r in range(world):
+    nat.scatter_heads_multi([dict(x=xs[r], dst_ptrs=[t.data_ptr() for t in q8], dst_batch_stride=tokens * world * hpr * d,
+                                  dst_row_offset=r * tokens, dst_scale_ptrs=[t.data_ptr() for t in sc])], heads)
+  for r in range(world):
+    nat.fp8_dequant_heads([q8[r]], [sc[r]], [out[r]], d)
+  torch.cuda.synchronize()
+  allx = torch.cat(xs, dim=1).float().cpu().numpy().reshape(tokens * world, heads, d)
+  amax = np.abs(allx).max(axis=-1, keepdims=True).astype(np.float32)
+  s = np.maximum((amax / np.float32(448.0)).astype(np.float32), np.float32(1e-6))
+  q = FO.e4m3_round((allx / s).astype(np.float32))
+  want = _bf16((q * s).astype(np.float32))
+  for owner in range(world):
+    got = out[owner][0].float().cpu().numpy()
+    np.testing.assert_array_equal(got, want[:, owner * hpr:(owner + 1) * hpr])
+    np.testing.assert_array_equal(sc[owner].cpu().numpy().reshape(tokens * world, hpr), s[:, owner * hpr:(owner + 1) * hpr, 0])
+
+  # output direction: eps = 1e-4 on amax, multiply by the fp32 reciprocal, scale stored (and applied) as bf16
+  o_loc = [torch.randn(1, tokens * world, hpr, d, generator=g).to("cuda", bf) for _ in range(world)]
+  o8 = [torch.zeros(tokens * heads * d // 4, dtype=torch.int32, device="cuda") for _ in range(world)]
+  osc = [torch.zeros(tokens * heads, dtype=bf, device="cuda") for _ in range(world)]
+  oout = [torch.empty(1, tokens, heads, d, dtype=bf, device="cuda") for _ in range(world)]
+  for r in range(world):
+    nat.gather_tokens_fp8(o_loc[r], [t.data_ptr() for t in o8], [t.data_ptr() for t in osc], r)
+  for r in range(world):
+    nat.fp8_dequant_heads([o8[r]], [osc[r]], [oout[r]], d)
+  torch.cuda.synchronize()
+  for r in range(world):
+    src = torch.cat([o_loc[gk][:, r * tokens:(r + 1) * tokens] for gk in range(world)], dim=2)[0].float().cpu().numpy()
+    amax = np.maximum(np.abs(src).max(axis=-1, keepdims=True).astype(np.float32), np.float32(1e-4))
+    s = (amax / np.float32(448.0)).astype(np.float32)
+    inv = (np.float32(1.0) / s).astype(np.float32)
+    q = FO.e4m3_round((src * inv).astype(np.float32))
+    want = _bf16((q * _bf16(s)).astype(np.float32))
+    np.testing.assert_array_equal(oout[r][0].float().cpu().numpy(), want)
