@@ -80,7 +80,7 @@ __device__ __forceinline__ float row_reduce(float v, float (*s_red)[Q_CTA / 32],
 // VPT 16-byte packets per thread kept as packed bf16 in registers between the amax pass and the
 // conversion pass.
 template <int TPR, int VPT, int PREOP>
-__global__ void __launch_bounds__(Q_CTA, PREOP == CDB_PRE_LAYERNORM_MOD ? 3 : 1)
+__global__ void __launch_bounds__(Q_CTA)
     fp8_quant_rows_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int cols, int64_t ld_x,
                           const QuantFuse f, uint8_t* __restrict__ q, float* __restrict__ scale) {
   constexpr int RPC = Q_CTA / TPR;  // rows per CTA and iteration

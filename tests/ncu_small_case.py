@@ -44,6 +44,13 @@ aq3 = torch.empty(M, 12288, device=dev, dtype=torch.float8_e4m3fn)
 H, D = 24, 128
 cos, sin, wn = mk(M, D), mk(M, D), mk(D)
 joint = torch.empty(1, M, H, D, device=dev, dtype=bf)
+joint_k = torch.empty_like(joint)
+# one-row product (modulation linear): the weight-streaming kernel
+x1 = mk(1, K)
+aq1 = torch.empty(1, K, device=dev, dtype=torch.float8_e4m3fn)
+sa1 = torch.empty(1, device=dev)
+out1 = torch.empty(1, N, device=dev, dtype=bf)
+nat.fp8_quant_rows(x1, aq1, sa1)
 xg, yg = mk(1, M, K), mk(1, M, K)
 
 
@@ -57,10 +64,15 @@ def launch_all():
     lambda: nat.fp8_quant_rows(x, aq, sa, nat.PRE_LAYERNORM_MOD, mod[:, :K], mod[:, K:2 * K], M, 1e-6),
     lambda: nat.fp8_quant_rows(wide[:, 9216:], aq3, sa, nat.PRE_GELU_TANH),
     lambda: nat.fp8_quant_rows_concat_gelu(attn, wide[:, 9216:], aq2, sa),
-    lambda: nat.qk_norm_rope(wide[None, :, :K], wn, cos, sin, joint, 0, H, 1e-6),
+    lambda: nat.scatter_heads_multi([
+      dict(x=wide[None, :, :K], norm_weight=wn, cos=cos, sin=sin, table_row_offset=0, dst_ptrs=[joint.data_ptr()],
+           dst_batch_stride=joint.stride(0), dst_row_offset=0, eps=1e-6),
+      dict(x=wide[None, :, K:2 * K], norm_weight=wn, cos=cos, sin=sin, table_row_offset=0, dst_ptrs=[joint_k.data_ptr()],
+           dst_batch_stride=joint.stride(0), dst_row_offset=0, eps=1e-6)], H),
     lambda: nat.gated_residual(xg, mod[:, 2 * K:3 * K], yg),
     lambda: nat.fp8_gemm_rowscaled(aq, sa, wq, sw, None, out),
     lambda: nat.fp8_gemm_rowscaled(aqs, sas, wq, sw, None, outs),
+    lambda: nat.fp8_gemm_rowscaled(aq1, sa1, wq, sw, None, out1),
   ]
   for step in steps:
     flush.zero_()
