@@ -726,18 +726,25 @@ __global__ void __launch_bounds__(GEMV_THREADS)
                               const uint8_t* __restrict__ w_q, const float* __restrict__ sw,
                               const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ out, int N, int K,
                               int64_t ld_out) {
-  extern __shared__ __half s_a[];  // [TM][K]
+  // Activations as f16 in shared memory, laid out so that a warp's reads are conflict-free: a lane
+  // needs the 16 values of "its" 16-byte weight piece = two 16-byte reads; all first halves of a row are
+  // stored contiguously, then all second halves: s_a[((m * 2 + half) * chunks + chunk) * 8 + i].
+  extern __shared__ __align__(16) __half s_a[];
+  const int chunks = K >> 4;  // 16-byte pieces per weight row
   for (int i = threadIdx.x; i < TM * K / 4; i += GEMV_THREADS) {
     float f[4];
     e4m3x4_to_float4(reinterpret_cast<const uint32_t*>(a_q)[i], f);
-    reinterpret_cast<__half2*>(s_a)[2 * i] = __floats2half2_rn(f[0], f[1]);
-    reinterpret_cast<__half2*>(s_a)[2 * i + 1] = __floats2half2_rn(f[2], f[3]);
+    const int e = i * 4, m = e / K, k = e - m * K;  // 4 consecutive elements never straddle a half
+    const int c = k >> 4, pos = k & 15;
+    __half2* dst = reinterpret_cast<__half2*>(s_a + ((int64_t)(m * 2 + (pos >> 3)) * chunks + c) * 8 + (pos & 7));
+    dst[0] = __floats2half2_rn(f[0], f[1]);
+    dst[1] = __floats2half2_rn(f[2], f[3]);
   }
   __syncthreads();
   const int lane = threadIdx.x & 31;
   const int warp = (blockIdx.x * GEMV_THREADS + threadIdx.x) >> 5;
   const int nwarps = (gridDim.x * GEMV_THREADS) >> 5;
-  const int chunks = K >> 4;  // 16-byte pieces per weight row
+  const uint4* s_a4 = reinterpret_cast<const uint4*>(s_a);
   for (int n = warp; n < N; n += nwarps) {
     const uint4* wrow = reinterpret_cast<const uint4*>(w_q + (int64_t)n * K);
     float acc[TM];
@@ -755,18 +762,25 @@ __global__ void __launch_bounds__(GEMV_THREADS)
         const int c = c0 + j * 32;
         if (c < chunks) {
           const uint32_t words[4] = {wv[j].x, wv[j].y, wv[j].z, wv[j].w};
+          float wf[16];
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
-            float wf[4];
-            e4m3x4_to_float4(words[q], wf);
+            float t[4];
+            e4m3x4_to_float4(words[q], t);
+            wf[4 * q] = t[0]; wf[4 * q + 1] = t[1]; wf[4 * q + 2] = t[2]; wf[4 * q + 3] = t[3];
+          }
 #pragma unroll
-            for (int m = 0; m < TM; ++m) {
-              const __half2* ap = reinterpret_cast<const __half2*>(s_a + (int64_t)m * K + c * 16 + q * 4);
-              const float2 a01 = __half22float2(ap[0]), a23 = __half22float2(ap[1]);
-              acc[m] = fmaf(wf[0], a01.x, acc[m]);
-              acc[m] = fmaf(wf[1], a01.y, acc[m]);
-              acc[m] = fmaf(wf[2], a23.x, acc[m]);
-              acc[m] = fmaf(wf[3], a23.y, acc[m]);
+          for (int m = 0; m < TM; ++m) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const uint4 av = s_a4[(int64_t)(m * 2 + h) * chunks + c];
+              const uint32_t aw[4] = {av.x, av.y, av.z, av.w};
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const float2 a2 = __half22float2(*reinterpret_cast<const __half2*>(&aw[i]));
+                acc[m] = fmaf(wf[8 * h + 2 * i], a2.x, acc[m]);
+                acc[m] = fmaf(wf[8 * h + 2 * i + 1], a2.y, acc[m]);
+              }
             }
           }
         }
