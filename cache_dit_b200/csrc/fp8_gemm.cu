@@ -264,16 +264,17 @@ __device__ __forceinline__ void epilogue_rows(const CUtensorMap* map_out, uint8_
   }
 }
 
-// Tile order: M fastest inside groups of TILE_GROUP_M row tiles, all column tiles of a group before
+// Tile order: M fastest inside groups of `group_m` row tiles, all column tiles of a group before
 // the next group.  The CTAs of a wave then share a few weight tiles AND at most TILE_GROUP_M row
 // panels of A, so both operands are re-read from L2; with plain M-fastest order an A that does not fit
 // the L2 (M = 16384, K = 12288: 201 MB) was streamed from HBM once per column tile.
-constexpr int TILE_GROUP_M = 16;
-__device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int& mi, int& ni) {
-  const int per_group = TILE_GROUP_M * n_tiles;
+// The group size is chosen on the host (tile_group_rows): all row tiles when there are few (every weight
+// tile is then read from HBM once), else balanced groups of at most 16.
+__device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int group_m, int& mi, int& ni) {
+  const int per_group = group_m * n_tiles;
   const int group = tile / per_group;
-  const int first_m = group * TILE_GROUP_M;
-  const int rows = min(TILE_GROUP_M, m_tiles - first_m);  // the last group may be short
+  const int first_m = group * group_m;
+  const int rows = min(group_m, m_tiles - first_m);  // the last group may be short
   const int in_group = tile - group * per_group;
   mi = first_m + in_group % rows;
   ni = in_group / rows;
@@ -285,7 +286,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                               const __grid_constant__ CUtensorMap map_w,
                               const __grid_constant__ CUtensorMap map_out, const float* __restrict__ sa,
                               const float* __restrict__ sw, const __nv_bfloat16* __restrict__ bias, int M, int N,
-                              int K, int32_t* status_word) {
+                              int K, int group_m, int32_t* status_word) {
   extern __shared__ uint8_t smem_raw[];
   // 128-byte swizzle needs 1024-byte aligned tiles.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -334,7 +335,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         int mi, ni;
-        tile_coords(tile, m_tiles, n_tiles, mi, ni);
+        tile_coords(tile, m_tiles, n_tiles, group_m, mi, ni);
         const int m0 = mi * BM, n0 = ni * BN;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % STAGES;
@@ -403,7 +404,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
       int mi, ni;
-      tile_coords(tile, m_tiles, n_tiles, mi, ni);
+      tile_coords(tile, m_tiles, n_tiles, group_m, mi, ni);
       const int m0 = mi * BM, n0 = ni * BN;
       const uint32_t buf = local_tile & 1u;
       const uint32_t use = local_tile >> 1;
@@ -537,7 +538,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
                                    const __grid_constant__ CUtensorMap map_w,
                                    const __grid_constant__ CUtensorMap map_out, const float* __restrict__ sa,
                                    const float* __restrict__ sw, const __nv_bfloat16* __restrict__ bias, int M,
-                                   int N, int K, int32_t* status_word) {
+                                   int N, int K, int group_m, int32_t* status_word) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* s_staging = smem + P_SMEM_TILE_BYTES;
@@ -589,7 +590,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
       bool ok = true;
       for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
         int mi, ni;
-        tile_coords(tile, m_tiles, n_tiles, mi, ni);
+        tile_coords(tile, m_tiles, n_tiles, group_m, mi, ni);
         const int m0 = mi * P_BM + (int)rank * 128;
         const int n0 = ni * BN + (int)rank * 128;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
@@ -664,7 +665,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
     bool ok = true;
     for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs, ++local_tile) {
       int mi, ni;
-      tile_coords(tile, m_tiles, n_tiles, mi, ni);
+      tile_coords(tile, m_tiles, n_tiles, group_m, mi, ni);
       const int m0 = mi * P_BM + (int)rank * 128;
       const int n0 = ni * BN;
       const uint32_t buf = local_tile & 1u;
@@ -878,6 +879,12 @@ static bool output_map(CUtensorMap* out, const void* base, uint64_t rows, uint64
   return cached_map(out, MapKey{base, rows, cols, pitch, (uint32_t)OUT_BOX_ROWS, 2});
 }
 
+static int tile_group_rows(int64_t m_tiles) {
+  if (m_tiles <= 24) return (int)m_tiles;
+  const int64_t groups = (m_tiles + 15) / 16;
+  return (int)((m_tiles + groups - 1) / groups);
+}
+
 }  // namespace cdb
 
 using namespace cdb;
@@ -945,7 +952,7 @@ extern "C" int cdb_fp8_gemm_rowscaled(const void* a_q, const float* a_scale, con
     const int64_t pairs = tiles < sms / 2 ? tiles : sms / 2;
     fp8_gemm_rowscaled_pair_kernel<<<(unsigned)(2 * pairs), GEMM_THREADS, P_SMEM_TOTAL_BYTES, st>>>(
         map_a, map_w, map_out, a_scale, w_scale, static_cast<const __nv_bfloat16*>(bias), (int)M, (int)N, (int)K,
-        status_word);
+        tile_group_rows((M + P_BM - 1) / P_BM), status_word);
   } else {
     if (!operand_map(&map_a, a_q, (uint64_t)M, (uint64_t)K, BM) ||
         !operand_map(&map_w, w_q, (uint64_t)N, (uint64_t)K, BN)) {
@@ -956,7 +963,7 @@ extern "C" int cdb_fp8_gemm_rowscaled(const void* a_q, const float* a_scale, con
     const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
     fp8_gemm_rowscaled_kernel<<<grid, GEMM_THREADS, SMEM_TOTAL_BYTES, st>>>(
         map_a, map_w, map_out, a_scale, w_scale, static_cast<const __nv_bfloat16*>(bias), (int)M, (int)N, (int)K,
-        status_word);
+        tile_group_rows((M + BM - 1) / BM), status_word);
   }
   CDB_CUDA_CHECK(cudaGetLastError());
   return CDB_OK;
