@@ -474,7 +474,10 @@ def run_ours(args):
                  "frac_of_burst": round(achieved / fp8_lib[0], 3) if fp8_lib else None,
                  "frac_of_nominal_4500": round(achieved / FP8_NOMINAL_TFLOPS, 3), "launches": len(records),
                  "timing": "CUDA events around every GEMM launch in an instrumented repeat of the timed steps",
-                 "traffic": None},
+                 # dram__bytes_read + dram__bytes_write of one launch of the dominant shape class from the
+                 # committed ncu capture (profiles/kernels_small_case_ncu_set_full.md): 52.1 MB + 67.9 MB for
+                 # 165.1 MB of operands and output (part of the output is still in L2 when the kernel ends)
+                 "traffic": 120.0e6, "traffic_case": "ncu, pair kernel, M=4608 N=12288 K=3072 (a single-stream MLP-in product)"},
   }
   if not args.skip_extras:
     line["roofline_cache_kernels"] = cache_roof
