@@ -17,7 +17,7 @@ from __future__ import annotations
 
 import inspect
 import logging
-from typing import Optional, Tuple
+from typing import Optional
 
 import torch
 import torch.distributed as dist

@@ -5,7 +5,6 @@ Signatures and the order cache -> parallelism -> quantization follow the referen
 """
 from __future__ import annotations
 
-import copy
 import logging
 from typing import List, Optional, Union
 
