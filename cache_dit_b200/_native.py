@@ -38,6 +38,7 @@ SIGNATURES = {
                                              c_void_p, c_void_p, c_void_p]),
   "cdb_fp8_gemm_rowscaled": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                                      c_int64, c_int64, c_int64, c_void_p, c_void_p]),
+  "cdb_fp8_gemm_rowscaled_grouped": (c_int, [c_void_p, c_int, c_void_p, c_void_p]),
   "cdb_qk_norm_rope": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                                c_int64, c_int64, c_int, c_int, c_int, c_float, c_void_p]),
   "cdb_peer_enable_access": (c_int, [c_int]),
@@ -457,3 +458,45 @@ def fp8_dequant_heads(q_list, scale_list, out_list, head_dim: int):
                                    _ptr_array([o.data_ptr() for o in out_list]), rows, n, int(head_dim),
                                    int(bf16_scales), _stream(out_list[0]))
   check(st, "cdb_fp8_dequant_heads")
+
+
+class GemmProblem(ctypes.Structure):
+  """ctypes image of `cdb_gemm_problem`."""
+  _fields_ = [("a_q", c_void_p), ("a_scale", c_void_p), ("w_q", c_void_p), ("w_scale", c_void_p), ("bias", c_void_p),
+              ("out", c_void_p), ("M", c_int64), ("N", c_int64), ("K", c_int64), ("ld_out", c_int64)]
+
+
+def fp8_gemm_rowscaled_grouped(problems):
+  """Up to two products (a_q, a_scale, w_q, w_scale, bias, out) in one launch; see fp8_gemm_rowscaled."""
+  if not 1 <= len(problems) <= 2:
+    raise RuntimeError("fp8_gemm_rowscaled_grouped: one or two problems per launch")
+  arr = (GemmProblem * len(problems))()
+  flops = 0.0
+  for slot, (a_q, a_scale, w_q, w_scale, bias, out) in zip(arr, problems):
+    _need_cuda(a_q, a_scale, w_q, w_scale, bias, out)
+    _need_contig(a_q, a_scale, w_q, w_scale, bias)
+    M, K = a_q.shape
+    N = w_q.shape[0]
+    if w_q.shape[1] != K or tuple(out.shape) != (M, N) or out.stride(1) != 1 or out.dtype != torch.bfloat16:
+      raise RuntimeError("fp8_gemm_rowscaled_grouped: shapes do not match / output must be bf16 rows")
+    if a_scale.numel() != M or w_scale.numel() != N or a_scale.dtype != torch.float32 or w_scale.dtype != torch.float32 \
+        or (bias is not None and (bias.dtype != torch.bfloat16 or bias.numel() != N)):
+      raise RuntimeError("fp8_gemm_rowscaled_grouped: scales must be float32 [M] / [N], bias bf16 [N]")
+    slot.a_q, slot.a_scale, slot.w_q, slot.w_scale = a_q.data_ptr(), a_scale.data_ptr(), w_q.data_ptr(), w_scale.data_ptr()
+    slot.bias = None if bias is None else bias.data_ptr()
+    slot.out = out.data_ptr()
+    slot.M, slot.N, slot.K = M, N, K
+    slot.ld_out = out.stride(0) if M > 1 else max(N, out.stride(0))
+    flops += 2.0 * M * N * K
+  out0 = problems[0][5]
+  timer = gemm_timer
+  if timer is not None:
+    start = torch.cuda.Event(enable_timing=True)
+    end = torch.cuda.Event(enable_timing=True)
+    start.record()
+  st = lib().cdb_fp8_gemm_rowscaled_grouped(ctypes.cast(arr, c_void_p), len(problems),
+                                            _ptr(gemm_status_word(out0.device)), _stream(out0))
+  if timer is not None:
+    end.record()
+    timer.append((start, end, flops))
+  check(st, "cdb_fp8_gemm_rowscaled_grouped")

@@ -25,6 +25,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
+#include <utility>
 #include <unordered_map>
 
 #include "common.cuh"
@@ -264,6 +265,32 @@ __device__ __forceinline__ void epilogue_rows(const CUtensorMap* map_out, uint8_
   }
 }
 
+// One launch can run two independent products (a "problem set"): the second is meant to be small (the
+// text stream of a double-stream block beside the image stream's product of the same layer) and its
+// tiles come last, so they fill the SMs the first problem's final, partial wave leaves idle instead of
+// paying a launch, a pipeline start and a mostly empty grid of their own.
+constexpr int MAX_PROBLEMS = 2;
+struct GemmProblem {
+  CUtensorMap map_a, map_w, map_out;
+  const float* sa;
+  const float* sw;
+  const __nv_bfloat16* bias;
+  int M, N, K;
+  int m_tiles, n_tiles, k_blocks, group_m;
+  int tile_begin;  // index of this problem's first tile in the launch's tile sequence
+};
+struct GemmProblems {
+  GemmProblem p[MAX_PROBLEMS];
+  int count;
+  int num_tiles;
+};
+__device__ __forceinline__ const GemmProblem* problem_of(const GemmProblems& ps, int tile, int& local) {
+  const bool second = ps.count > 1 && tile >= ps.p[1].tile_begin;
+  const GemmProblem* pr = second ? &ps.p[1] : &ps.p[0];
+  local = tile - pr->tile_begin;
+  return pr;
+}
+
 // Tile order: M fastest inside groups of `group_m` row tiles, all column tiles of a group before
 // the next group.  The CTAs of a wave then share a few weight tiles AND at most TILE_GROUP_M row
 // panels of A, so both operands are re-read from L2; with plain M-fastest order an A that does not fit
@@ -282,11 +309,7 @@ __device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, 
 
 // ---- kernel --------------------------------------------------------------------------------
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
-    fp8_gemm_rowscaled_kernel(const __grid_constant__ CUtensorMap map_a,
-                              const __grid_constant__ CUtensorMap map_w,
-                              const __grid_constant__ CUtensorMap map_out, const float* __restrict__ sa,
-                              const float* __restrict__ sw, const __nv_bfloat16* __restrict__ bias, int M, int N,
-                              int K, int group_m, int32_t* status_word) {
+    fp8_gemm_rowscaled_kernel(const __grid_constant__ GemmProblems ps, int32_t* status_word) {
   extern __shared__ uint8_t smem_raw[];
   // 128-byte swizzle needs 1024-byte aligned tiles.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -297,10 +320,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int m_tiles = (M + BM - 1) / BM;
-  const int n_tiles = (N + BN - 1) / BN;
-  const int num_tiles = m_tiles * n_tiles;
-  const int k_blocks = (K + BK - 1) / BK;
+  const int num_tiles = ps.num_tiles;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -329,13 +349,18 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
-      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
-      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+      for (int i = 0; i < ps.count; ++i) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&ps.p[i].map_a) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&ps.p[i].map_w) : "memory");
+      }
       uint32_t it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int local;
+        const GemmProblem* pr = problem_of(ps, tile, local);
+        const int k_blocks = pr->k_blocks;
         int mi, ni;
-        tile_coords(tile, m_tiles, n_tiles, group_m, mi, ni);
+        tile_coords(local, pr->m_tiles, pr->n_tiles, pr->group_m, mi, ni);
         const int m0 = mi * BM, n0 = ni * BN;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % STAGES;
@@ -345,8 +370,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
           uint8_t* a_dst = smem + s * STAGE_BYTES;
           uint8_t* b_dst = a_dst + A_STAGE_BYTES;
           mbar_expect_tx(&gb->full[s], STAGE_BYTES);
-          tma_load_2d(&map_a, &gb->full[s], a_dst, kb * BK, m0);
-          tma_load_2d(&map_w, &gb->full[s], b_dst, kb * BK, n0);
+          tma_load_2d(&pr->map_a, &gb->full[s], a_dst, kb * BK, m0);
+          tma_load_2d(&pr->map_w, &gb->full[s], b_dst, kb * BK, n0);
         }
       }
       // Do not let the CTA retire while bulk copies into its shared memory are in flight:
@@ -374,6 +399,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         if (!ok) break;
         tcgen05_fence_after();
         const uint32_t tmem_d = tmem_base + buf * BN;
+        int local;
+        const int k_blocks = problem_of(ps, tile, local)->k_blocks;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
@@ -403,8 +430,14 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     uint32_t local_tile = 0, blocks_done = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
+      int local;
+      const GemmProblem* pr = problem_of(ps, tile, local);
+      const int M = pr->M, N = pr->N;
+      const float* sa = pr->sa;
+      const float* sw = pr->sw;
+      const __nv_bfloat16* bias = pr->bias;
       int mi, ni;
-      tile_coords(tile, m_tiles, n_tiles, group_m, mi, ni);
+      tile_coords(local, pr->m_tiles, pr->n_tiles, pr->group_m, mi, ni);
       const int m0 = mi * BM, n0 = ni * BN;
       const uint32_t buf = local_tile & 1u;
       const uint32_t use = local_tile >> 1;
@@ -425,7 +458,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       const int row = m0 + quarter * 32 + lane;
       const float rs = row < M ? __ldg(sa + row) : 0.f;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
-      epilogue_rows(&map_out, s_staging + quarter * 2 * OUT_BLOCK_BYTES, taddr, rs, s_colscale, s_bias,
+      epilogue_rows(&pr->map_out, s_staging + quarter * 2 * OUT_BLOCK_BYTES, taddr, rs, s_colscale, s_bias,
                     m0 + quarter * 32, n0, M, N, lane, blocks_done);
       tcgen05_fence_before();
       __syncwarp();
@@ -534,11 +567,7 @@ __device__ __forceinline__ bool pair_wait(uint64_t* bar, uint32_t parity, PairBa
 }
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
-    fp8_gemm_rowscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a,
-                                   const __grid_constant__ CUtensorMap map_w,
-                                   const __grid_constant__ CUtensorMap map_out, const float* __restrict__ sa,
-                                   const float* __restrict__ sw, const __nv_bfloat16* __restrict__ bias, int M,
-                                   int N, int K, int group_m, int32_t* status_word) {
+    fp8_gemm_rowscaled_pair_kernel(const __grid_constant__ GemmProblems ps, int32_t* status_word) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* s_staging = smem + P_SMEM_TILE_BYTES;
@@ -549,10 +578,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();  // 0 = even CTA: owns the shared barriers, issues the MMAs
-  const int m_tiles = (M + P_BM - 1) / P_BM;
-  const int n_tiles = (N + BN - 1) / BN;
-  const int num_tiles = m_tiles * n_tiles;
-  const int k_blocks = (K + BK - 1) / BK;
+  const int num_tiles = ps.num_tiles;
   const int pair_id = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
 
@@ -584,13 +610,18 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
   if (warp == 0) {
     // ---------------- TMA producer (both CTAs) ----------------
     if (lane == 0) {
-      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
-      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+      for (int i = 0; i < ps.count; ++i) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&ps.p[i].map_a) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&ps.p[i].map_w) : "memory");
+      }
       uint32_t it = 0;
       bool ok = true;
       for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
+        int local;
+        const GemmProblem* pr = problem_of(ps, tile, local);
+        const int k_blocks = pr->k_blocks;
         int mi, ni;
-        tile_coords(tile, m_tiles, n_tiles, group_m, mi, ni);
+        tile_coords(local, pr->m_tiles, pr->n_tiles, pr->group_m, mi, ni);
         const int m0 = mi * P_BM + (int)rank * 128;
         const int n0 = ni * BN + (int)rank * 128;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
@@ -602,8 +633,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
           uint8_t* b_dst = a_dst + P_A_BYTES;
           if (rank == 0) mbar_expect_tx(&gb->full[s], 2 * P_STAGE_BYTES);  // both CTAs' bytes
           const uint32_t full_addr = map_to_cta(smem_u32(&gb->full[s]), 0);
-          tma_load_2d_pair(&map_a, full_addr, a_dst, kb * BK, m0);
-          tma_load_2d_pair(&map_w, full_addr, b_dst, kb * BK, n0);
+          tma_load_2d_pair(&pr->map_a, full_addr, a_dst, kb * BK, m0);
+          tma_load_2d_pair(&pr->map_w, full_addr, b_dst, kb * BK, n0);
         }
       }
       // A CTA may not retire while copies into its shared memory are in flight or while the peer's
@@ -631,6 +662,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
         if (!ok) break;
         tcgen05_fence_after();
         const uint32_t tmem_d = tmem_base + buf * BN;
+        int local;
+        const int k_blocks = problem_of(ps, tile, local)->k_blocks;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % P_STAGES;
           const uint32_t ph = (it / P_STAGES) & 1u;
@@ -664,8 +697,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
     uint32_t local_tile = 0, blocks_done = 0;
     bool ok = true;
     for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs, ++local_tile) {
+      int local;
+      const GemmProblem* pr = problem_of(ps, tile, local);
+      const int M = pr->M, N = pr->N;
+      const float* sa = pr->sa;
+      const float* sw = pr->sw;
+      const __nv_bfloat16* bias = pr->bias;
       int mi, ni;
-      tile_coords(tile, m_tiles, n_tiles, group_m, mi, ni);
+      tile_coords(local, pr->m_tiles, pr->n_tiles, pr->group_m, mi, ni);
       const int m0 = mi * P_BM + (int)rank * 128;
       const int n0 = ni * BN;
       const uint32_t buf = local_tile & 1u;
@@ -684,7 +723,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
       const int row = m0 + quarter * 32 + lane;
       const float rs = row < M ? __ldg(sa + row) : 0.f;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
-      epilogue_rows(&map_out, s_staging + quarter * 2 * OUT_BLOCK_BYTES, taddr, rs, s_colscale, s_bias,
+      epilogue_rows(&pr->map_out, s_staging + quarter * 2 * OUT_BLOCK_BYTES, taddr, rs, s_colscale, s_bias,
                     m0 + quarter * 32, n0, M, N, lane, blocks_done);
       tcgen05_fence_before();
       __syncwarp();
@@ -889,16 +928,58 @@ static int tile_group_rows(int64_t m_tiles) {
 
 using namespace cdb;
 
-extern "C" int cdb_fp8_gemm_rowscaled(const void* a_q, const float* a_scale, const void* w_q,
-                                      const float* w_scale, const void* bias, void* out, int64_t M,
-                                      int64_t N, int64_t K, int64_t ld_out, int32_t* status_word,
-                                      void* stream) {
-  if (!a_q || !a_scale || !w_q || !w_scale || !out || M < 0 || N <= 0 || K <= 0 || ld_out < N)
+struct cdb_gemm_problem_abi {  // mirrors `cdb_gemm_problem` of the public header
+  const void* a_q;
+  const float* a_scale;
+  const void* w_q;
+  const float* w_scale;
+  const void* bias;
+  void* out;
+  int64_t M, N, K, ld_out;
+};
+
+static int check_problem(const cdb_gemm_problem_abi& g) {
+  if (!g.a_q || !g.a_scale || !g.w_q || !g.w_scale || !g.out || g.M < 0 || g.N <= 0 || g.K <= 0 || g.ld_out < g.N)
     return CDB_ERR_BAD_ARGUMENT;
-  if (M == 0) return CDB_OK;
-  if (K % 16 != 0 || N % 8 != 0 || ld_out % 8 != 0 || !aligned16(a_q) || !aligned16(w_q) || !aligned16(out) ||
-      M > INT32_MAX || N > INT32_MAX || K > INT32_MAX)
+  if (g.K % 16 != 0 || g.N % 8 != 0 || g.ld_out % 8 != 0 || !aligned16(g.a_q) || !aligned16(g.w_q) ||
+      !aligned16(g.out) || g.M > INT32_MAX || g.N > INT32_MAX || g.K > INT32_MAX)
     return CDB_ERR_UNSUPPORTED;
+  return CDB_OK;
+}
+
+static int launch_few_rows(const cdb_gemm_problem_abi& g, int sms, cudaStream_t st) {
+  const uint8_t* ap = static_cast<const uint8_t*>(g.a_q);
+  const uint8_t* wp = static_cast<const uint8_t*>(g.w_q);
+  const __nv_bfloat16* bp = static_cast<const __nv_bfloat16*>(g.bias);
+  __nv_bfloat16* op = static_cast<__nv_bfloat16*>(g.out);
+  const int64_t want = (g.N + GEMV_THREADS / 32 - 1) / (GEMV_THREADS / 32);
+  const unsigned grid = (unsigned)(want < (int64_t)sms * 4 ? want : (int64_t)sms * 4);
+  const size_t smem = (size_t)g.M * g.K * 2;
+#define CDB_GEMV(TM)                                                                                          \
+  fp8_gemv_rowscaled_kernel<TM><<<grid, GEMV_THREADS, smem, st>>>(ap, g.a_scale, wp, g.w_scale, bp, op, (int)g.N, \
+                                                                  (int)g.K, g.ld_out)
+  if (g.M == 1) CDB_GEMV(1);
+  else if (g.M == 2) CDB_GEMV(2);
+  else if (g.M == 3) CDB_GEMV(3);
+  else CDB_GEMV(4);
+#undef CDB_GEMV
+  CDB_CUDA_CHECK(cudaGetLastError());
+  return CDB_OK;
+}
+
+// Up to two products in one launch of the tile kernels; the one with more rows goes first.
+extern "C" int cdb_fp8_gemm_rowscaled_grouped(const void* problems_v, int count, int32_t* status_word, void* stream) {
+  const cdb_gemm_problem_abi* in = static_cast<const cdb_gemm_problem_abi*>(problems_v);
+  if (!in || count < 1 || count > MAX_PROBLEMS) return CDB_ERR_BAD_ARGUMENT;
+  cdb_gemm_problem_abi g[MAX_PROBLEMS];
+  int n = 0;
+  for (int i = 0; i < count; ++i) {
+    const int rc = check_problem(in[i]);
+    if (rc != CDB_OK) return rc;
+    if (in[i].M > 0) g[n++] = in[i];
+  }
+  if (n == 0) return CDB_OK;
+  if (n == 2 && g[1].M > g[0].M) std::swap(g[0], g[1]);
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   static int mode = 0;  // 0 = choose by shape, 1 = single-CTA kernel, 2 = CTA-pair kernel
@@ -914,57 +995,54 @@ extern "C" int cdb_fp8_gemm_rowscaled(const void* a_q, const float* a_scale, con
   });
   CDB_CUDA_CHECK(attr_err);
   const int sms = sm_count();
-  cudaStream_t st_gemv = static_cast<cudaStream_t>(stream);
-  if (mode == 0 && M <= GEMV_MAX_M && M * K * 2 <= 48 * 1024 && !(reinterpret_cast<uintptr_t>(a_q) & 3u)) {
-    const uint8_t* ap = static_cast<const uint8_t*>(a_q);
-    const uint8_t* wp = static_cast<const uint8_t*>(w_q);
-    const __nv_bfloat16* bp = static_cast<const __nv_bfloat16*>(bias);
-    __nv_bfloat16* op = static_cast<__nv_bfloat16*>(out);
-    const int64_t want = (N + GEMV_THREADS / 32 - 1) / (GEMV_THREADS / 32);
-    const unsigned grid = (unsigned)(want < (int64_t)sms * 4 ? want : (int64_t)sms * 4);
-    const size_t smem = (size_t)M * K * 2;
-#define CDB_GEMV(TM) \
-  fp8_gemv_rowscaled_kernel<TM><<<grid, GEMV_THREADS, smem, st_gemv>>>(ap, a_scale, wp, w_scale, bp, op, (int)N, (int)K, ld_out)
-    if (M == 1) CDB_GEMV(1);
-    else if (M == 2) CDB_GEMV(2);
-    else if (M == 3) CDB_GEMV(3);
-    else CDB_GEMV(4);
-#undef CDB_GEMV
-    CDB_CUDA_CHECK(cudaGetLastError());
-    return CDB_OK;
-  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (n == 1 && mode == 0 && g[0].M <= GEMV_MAX_M && g[0].M * g[0].K * 2 <= 48 * 1024) return launch_few_rows(g[0], sms, st);
   // CTA pairs pay off on tall problems; below ~4096 rows (rank shards of a context-parallel run: 2304,
   // 1152, 576) the single-CTA kernel's 128-row tiles waste less and measured 4-25 % faster
-  const bool pair = mode == 2 || (mode == 0 && M >= 4096 && CDB_GEMM_DEFAULT_PAIR);
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  CUtensorMap map_a, map_w, map_out;
-  if (!output_map(&map_out, out, (uint64_t)M, (uint64_t)N, (uint64_t)ld_out)) {
-    set_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled");
-    return CDB_ERR_CUDA;
+  const bool pair = mode == 2 || (mode == 0 && g[0].M >= 4096 && CDB_GEMM_DEFAULT_PAIR);
+  const int64_t tile_rows = pair ? P_BM : BM;
+  GemmProblems ps{};
+  ps.count = n;
+  int64_t tiles = 0;
+  for (int i = 0; i < n; ++i) {
+    GemmProblem& o = ps.p[i];
+    const uint32_t a_box = pair ? 128 : BM, w_box = pair ? 128 : BN;
+    if (!operand_map(&o.map_a, g[i].a_q, (uint64_t)g[i].M, (uint64_t)g[i].K, a_box) ||
+        !operand_map(&o.map_w, g[i].w_q, (uint64_t)g[i].N, (uint64_t)g[i].K, w_box) ||
+        !output_map(&o.map_out, g[i].out, (uint64_t)g[i].M, (uint64_t)g[i].N, (uint64_t)g[i].ld_out)) {
+      set_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled");
+      return CDB_ERR_CUDA;
+    }
+    o.sa = g[i].a_scale;
+    o.sw = g[i].w_scale;
+    o.bias = static_cast<const __nv_bfloat16*>(g[i].bias);
+    o.M = (int)g[i].M;
+    o.N = (int)g[i].N;
+    o.K = (int)g[i].K;
+    o.m_tiles = (int)((g[i].M + tile_rows - 1) / tile_rows);
+    o.n_tiles = (int)((g[i].N + BN - 1) / BN);
+    o.k_blocks = (int)((g[i].K + BK - 1) / BK);
+    o.group_m = tile_group_rows(o.m_tiles);
+    o.tile_begin = (int)tiles;
+    tiles += (int64_t)o.m_tiles * o.n_tiles;
   }
+  if (tiles > INT32_MAX) return CDB_ERR_TOO_LARGE;
+  ps.num_tiles = (int)tiles;
   if (pair) {
-    if (!operand_map(&map_a, a_q, (uint64_t)M, (uint64_t)K, 128) ||
-        !operand_map(&map_w, w_q, (uint64_t)N, (uint64_t)K, 128)) {
-      set_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled");
-      return CDB_ERR_CUDA;
-    }
-    const int64_t tiles = ((M + P_BM - 1) / P_BM) * ((N + BN - 1) / BN);
     const int64_t pairs = tiles < sms / 2 ? tiles : sms / 2;
-    fp8_gemm_rowscaled_pair_kernel<<<(unsigned)(2 * pairs), GEMM_THREADS, P_SMEM_TOTAL_BYTES, st>>>(
-        map_a, map_w, map_out, a_scale, w_scale, static_cast<const __nv_bfloat16*>(bias), (int)M, (int)N, (int)K,
-        tile_group_rows((M + P_BM - 1) / P_BM), status_word);
+    fp8_gemm_rowscaled_pair_kernel<<<(unsigned)(2 * pairs), GEMM_THREADS, P_SMEM_TOTAL_BYTES, st>>>(ps, status_word);
   } else {
-    if (!operand_map(&map_a, a_q, (uint64_t)M, (uint64_t)K, BM) ||
-        !operand_map(&map_w, w_q, (uint64_t)N, (uint64_t)K, BN)) {
-      set_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled");
-      return CDB_ERR_CUDA;
-    }
-    const int64_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
     const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
-    fp8_gemm_rowscaled_kernel<<<grid, GEMM_THREADS, SMEM_TOTAL_BYTES, st>>>(
-        map_a, map_w, map_out, a_scale, w_scale, static_cast<const __nv_bfloat16*>(bias), (int)M, (int)N, (int)K,
-        tile_group_rows((M + BM - 1) / BM), status_word);
+    fp8_gemm_rowscaled_kernel<<<grid, GEMM_THREADS, SMEM_TOTAL_BYTES, st>>>(ps, status_word);
   }
   CDB_CUDA_CHECK(cudaGetLastError());
   return CDB_OK;
+}
+
+extern "C" int cdb_fp8_gemm_rowscaled(const void* a_q, const float* a_scale, const void* w_q,
+                                      const float* w_scale, const void* bias, void* out, int64_t M,
+                                      int64_t N, int64_t K, int64_t ld_out, int32_t* status_word,
+                                      void* stream) {
+  const cdb_gemm_problem_abi g{a_q, a_scale, w_q, w_scale, bias, out, M, N, K, ld_out};
+  return cdb_fp8_gemm_rowscaled_grouped(&g, 1, status_word, stream);
 }

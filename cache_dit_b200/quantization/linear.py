@@ -137,3 +137,19 @@ def fused_group(linears) -> FusedFloat8Linears:
     fused = FusedFloat8Linears(list(linears))
     cache[key] = fused
   return fused
+
+
+def grouped_forward_quantized(items):
+  """Products of up to two FP8 linears (or fused groups) with already quantized activations as ONE
+  launch: items = [(module, a_q, a_scale, lead_shape), ...].  Returns each module's usual result (a
+  tensor, or the tuple of splits of a fused group).  The second product is typically the small text
+  stream of a double-stream block, whose tiles fill the tail wave of the first."""
+  outs = [torch.empty((a_q.shape[0], m.out_features), dtype=torch.bfloat16, device=a_q.device) for m, a_q, _, _ in items]
+  problems = [(a_q, a_scale, m.weight_q, m.weight_scale, m.bias, out) for (m, a_q, a_scale, _), out in zip(items, outs)]
+  for i in range(0, len(problems), 2):
+    _native.fp8_gemm_rowscaled_grouped(problems[i:i + 2])
+  results = []
+  for (m, _, _, lead), out in zip(items, outs):
+    out = out.view(*lead, m.out_features)
+    results.append(out.split(m.splits, dim=-1) if isinstance(m, FusedFloat8Linears) else out)
+  return results

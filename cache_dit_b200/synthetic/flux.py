@@ -19,9 +19,9 @@ from torch import nn
 
 from ..caching.block_adapters import BlockAdapter, BlockAdapterRegister
 from ..caching.forward_pattern import ForwardPattern
-from .layers import (RMSNorm, TimestepMLP, UlyssesGroup, concat_gelu_linear, gated_add, gelu_linear,
-                     joint_attention, join_tokens, norm_modulate, norm_modulate_linears, RopeCache,
-                     split_tokens, timestep_embedding)
+from .layers import (RMSNorm, RopeCache, TimestepMLP, UlyssesGroup, concat_gelu_linear, gated_add, gelu_linear_pair,
+                     joint_attention, join_tokens, linear_pair, norm_modulate, norm_modulate_linears,
+                     norm_modulate_linears_pair, split_tokens, timestep_embedding)
 
 
 class AdaLayerNormZero(nn.Module):
@@ -84,18 +84,20 @@ class FluxTransformerBlock(nn.Module):
     a = self.attn
     shift, scale, gate, shift_mlp, scale_mlp, gate_mlp = self.norm1(temb)
     c_shift, c_scale, c_gate, c_shift_mlp, c_scale_mlp, c_gate_mlp = self.norm1_context(temb)
-    q, k, v = norm_modulate_linears(hidden_states, shift, scale, (a.to_q, a.to_k, a.to_v))
-    cq, ck, cv = norm_modulate_linears(encoder_hidden_states, c_shift, c_scale,
-                                       (a.add_q_proj, a.add_k_proj, a.add_v_proj))
+    (q, k, v), (cq, ck, cv) = norm_modulate_linears_pair(
+      (hidden_states, shift, scale, (a.to_q, a.to_k, a.to_v)),
+      (encoder_hidden_states, c_shift, c_scale, (a.add_q_proj, a.add_k_proj, a.add_v_proj)))
     o = joint_attention(((cq, a.norm_added_q), (q, a.norm_q)), ((ck, a.norm_added_k), (k, a.norm_k)), (cv, v),
                         image_rotary_emb, a.heads, self.cp)
     n_txt = encoder_hidden_states.shape[1]
-    hidden_states = gated_add(hidden_states, gate, a.to_out(o[:, n_txt:]))
-    encoder_hidden_states = gated_add(encoder_hidden_states, c_gate, a.to_add_out(o[:, :n_txt]))
-    (h, ) = norm_modulate_linears(hidden_states, shift_mlp, scale_mlp, (self.ff.proj_in, ))
-    hidden_states = gated_add(hidden_states, gate_mlp, gelu_linear(h, self.ff.proj_out))
-    (c, ) = norm_modulate_linears(encoder_hidden_states, c_shift_mlp, c_scale_mlp, (self.ff_context.proj_in, ))
-    encoder_hidden_states = gated_add(encoder_hidden_states, c_gate_mlp, gelu_linear(c, self.ff_context.proj_out))
+    y, cy = linear_pair(o[:, n_txt:], a.to_out, o[:, :n_txt], a.to_add_out)
+    hidden_states = gated_add(hidden_states, gate, y)
+    encoder_hidden_states = gated_add(encoder_hidden_states, c_gate, cy)
+    (h, ), (c, ) = norm_modulate_linears_pair((hidden_states, shift_mlp, scale_mlp, (self.ff.proj_in, )),
+                                              (encoder_hidden_states, c_shift_mlp, c_scale_mlp, (self.ff_context.proj_in, )))
+    y, cy = gelu_linear_pair(h, self.ff.proj_out, c, self.ff_context.proj_out)
+    hidden_states = gated_add(hidden_states, gate_mlp, y)
+    encoder_hidden_states = gated_add(encoder_hidden_states, c_gate_mlp, cy)
     return encoder_hidden_states, hidden_states
 
 

@@ -16,7 +16,8 @@ import torch.nn.functional as F
 from torch import nn
 
 from .. import _native
-from ..quantization.linear import Float8RowwiseLinear, fused_group, quantize_rows_fused
+from ..quantization.linear import (Float8RowwiseLinear, fused_group, grouped_forward_quantized,
+                                   quantize_rows_fused)
 
 
 def _all_fp8(linears: Sequence[nn.Module]) -> bool:
@@ -34,6 +35,52 @@ def norm_modulate_linears(x: torch.Tensor, shift: torch.Tensor, scale: torch.Ten
     return [linears[0].forward_quantized(a_q, a_scale, lead)]
   y = F.layer_norm(x, (x.shape[-1], ), eps=eps) * (1 + scale[:, None]) + shift[:, None]
   return [l(y) for l in linears]
+
+
+# ---- two streams at once -----------------------------------------------------------------------------
+# A double-stream block runs every layer twice: on the image tokens and, with other weights, on the much
+# shorter text sequence.  The pair helpers quantize both activations and run both products in ONE GEMM
+# launch, where the text product's tiles ride in the tail wave of the image product.
+def _pair_ready(xa, xb, linears) -> bool:
+  return xa.is_cuda and xb.is_cuda and _all_fp8(linears)
+
+
+def norm_modulate_linears_pair(a, b, eps: float = 1e-6):
+  """(x, shift, scale, linears) for each stream -> (outputs of stream a, outputs of stream b)."""
+  (xa, sha, sca, la), (xb, shb, scb, lb) = a, b
+  if not _pair_ready(xa, xb, tuple(la) + tuple(lb)):
+    return norm_modulate_linears(xa, sha, sca, la, eps), norm_modulate_linears(xb, shb, scb, lb, eps)
+  items = []
+  for x, sh, sc, lin in ((xa, sha, sca, la), (xb, shb, scb, lb)):
+    a_q, a_scale, lead = quantize_rows_fused(x, _native.PRE_LAYERNORM_MOD, sh, sc, eps)
+    items.append((fused_group(lin) if len(lin) > 1 else lin[0], a_q, a_scale, lead))
+  ra, rb = grouped_forward_quantized(items)
+  as_list = lambda r: list(r) if isinstance(r, (tuple, list)) else [r]
+  return as_list(ra), as_list(rb)
+
+
+def linear_pair(xa, lina, xb, linb):
+  """(lina(xa), linb(xb)) with one GEMM launch."""
+  if not _pair_ready(xa, xb, (lina, linb)):
+    return lina(xa), linb(xb)
+  items = []
+  for x, lin in ((xa, lina), (xb, linb)):
+    a_q, a_scale = lin.quantize_input(x)
+    items.append((lin, a_q, a_scale, x.shape[:-1]))
+  ra, rb = grouped_forward_quantized(items)
+  return ra, rb
+
+
+def gelu_linear_pair(xa, lina, xb, linb):
+  """(lina(gelu_tanh(xa)), linb(gelu_tanh(xb))) with one GEMM launch."""
+  if not _pair_ready(xa, xb, (lina, linb)):
+    return gelu_linear(xa, lina), gelu_linear(xb, linb)
+  items = []
+  for x, lin in ((xa, lina), (xb, linb)):
+    a_q, a_scale, lead = quantize_rows_fused(x, _native.PRE_GELU_TANH)
+    items.append((lin, a_q, a_scale, lead))
+  ra, rb = grouped_forward_quantized(items)
+  return ra, rb
 
 
 def norm_modulate(x: torch.Tensor, shift: torch.Tensor, scale: torch.Tensor, eps: float = 1e-6):

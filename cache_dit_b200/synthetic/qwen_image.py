@@ -21,8 +21,8 @@ from torch import nn
 from ..caching.block_adapters import BlockAdapter, BlockAdapterRegister
 from ..caching.forward_pattern import ForwardPattern
 from .context_parallel import ContextParallelMixin
-from .layers import (RMSNorm, TimestepMLP, UlyssesGroup, gated_add, gelu_linear, joint_attention, norm_modulate,
-                     norm_modulate_linears, RopeCache, timestep_embedding)
+from .layers import (RMSNorm, RopeCache, TimestepMLP, UlyssesGroup, gated_add, gelu_linear_pair, joint_attention,
+                     linear_pair, norm_modulate, norm_modulate_linears_pair, timestep_embedding)
 
 
 class _GeluProj(nn.Module):
@@ -69,18 +69,20 @@ class QwenImageTransformerBlock(nn.Module):
     a = self.attn
     shift1, scale1, gate1, shift2, scale2, gate2 = self.img_mod(temb).chunk(6, dim=-1)
     c_shift1, c_scale1, c_gate1, c_shift2, c_scale2, c_gate2 = self.txt_mod(temb).chunk(6, dim=-1)
-    q, k, v = norm_modulate_linears(hidden_states, shift1, scale1, (a.to_q, a.to_k, a.to_v))
-    cq, ck, cv = norm_modulate_linears(encoder_hidden_states, c_shift1, c_scale1,
-                                       (a.add_q_proj, a.add_k_proj, a.add_v_proj))
+    (q, k, v), (cq, ck, cv) = norm_modulate_linears_pair(
+      (hidden_states, shift1, scale1, (a.to_q, a.to_k, a.to_v)),
+      (encoder_hidden_states, c_shift1, c_scale1, (a.add_q_proj, a.add_k_proj, a.add_v_proj)))
     o = joint_attention(((cq, a.norm_added_q), (q, a.norm_q)), ((ck, a.norm_added_k), (k, a.norm_k)), (cv, v),
                         image_rotary_emb, a.heads, self.cp)
     n_txt = encoder_hidden_states.shape[1]
-    hidden_states = gated_add(hidden_states, gate1, a.to_out[0](o[:, n_txt:]))
-    encoder_hidden_states = gated_add(encoder_hidden_states, c_gate1, a.to_add_out(o[:, :n_txt]))
-    (h, ) = norm_modulate_linears(hidden_states, shift2, scale2, (self.img_mlp.net[0].proj, ))
-    hidden_states = gated_add(hidden_states, gate2, gelu_linear(h, self.img_mlp.net[2]))
-    (c, ) = norm_modulate_linears(encoder_hidden_states, c_shift2, c_scale2, (self.txt_mlp.net[0].proj, ))
-    encoder_hidden_states = gated_add(encoder_hidden_states, c_gate2, gelu_linear(c, self.txt_mlp.net[2]))
+    y, cy = linear_pair(o[:, n_txt:], a.to_out[0], o[:, :n_txt], a.to_add_out)
+    hidden_states = gated_add(hidden_states, gate1, y)
+    encoder_hidden_states = gated_add(encoder_hidden_states, c_gate1, cy)
+    (h, ), (c, ) = norm_modulate_linears_pair((hidden_states, shift2, scale2, (self.img_mlp.net[0].proj, )),
+                                              (encoder_hidden_states, c_shift2, c_scale2, (self.txt_mlp.net[0].proj, )))
+    y, cy = gelu_linear_pair(h, self.img_mlp.net[2], c, self.txt_mlp.net[2])
+    hidden_states = gated_add(hidden_states, gate2, y)
+    encoder_hidden_states = gated_add(encoder_hidden_states, c_gate2, cy)
     return encoder_hidden_states, hidden_states
 
 

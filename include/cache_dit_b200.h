@@ -147,6 +147,22 @@ CDB_API int cdb_fp8_quant_rows_fused(const void* x, int64_t rows, int64_t cols, 
                              const void* mod_shift, const void* mod_scale, int64_t rows_per_batch,
                              int64_t ld_mod, float eps, void* q, float* scale, void* stream);
 
+/* Up to two independent products in one launch: the tiles of the one with fewer rows come last and fill
+ * the SMs that the other's final, partial wave leaves idle (the text stream of a double-stream block beside
+ * the image stream's product of the same layer).  Same arithmetic and requirements per problem as
+ * cdb_fp8_gemm_rowscaled. */
+typedef struct cdb_gemm_problem {
+  const void* a_q;
+  const float* a_scale;
+  const void* w_q;
+  const float* w_scale;
+  const void* bias;
+  void* out;
+  int64_t M, N, K, ld_out;
+} cdb_gemm_problem;
+CDB_API int cdb_fp8_gemm_rowscaled_grouped(const void* problems /* cdb_gemm_problem[count] */, int count,
+                                   int32_t* status_word, void* stream);
+
 /* Quantizes the rows of the concatenation [head | gelu_tanh(tail)] without building it: the input
  * of a parallel attention + MLP block's output projection (attention output beside the activated
  * MLP branch).  head [rows, head_cols] and tail [rows, tail_cols] are bf16 with their own row

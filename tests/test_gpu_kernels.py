@@ -357,3 +357,27 @@ def test_fp8_quant_matches_torch_cast_pipeline(nat, rows, cols):
   want = (xf / scale[:, None]).clamp(-448.0, 448.0).to(torch.float8_e4m3fn)
   assert torch.equal(s, scale)
   assert torch.equal(q.view(torch.uint8), want.view(torch.uint8))
+
+
+@pytest.mark.parametrize("shapes", [((4608, 3072, 3072), (512, 3072, 3072)), ((1000, 520, 256), (130, 264, 256)),
+                                    ((300, 272, 512), (700, 1024, 256)), ((4096, 9216, 3072), (512, 9216, 3072))])
+def test_fp8_gemm_grouped_equals_separate_launches(nat, shapes):
+  """Two products in one launch (the second one's tiles ride in the tail wave of the first) give exactly
+  what two launches give, whatever their shapes and order."""
+  g = torch.Generator(device="cuda").manual_seed(sum(shapes[0]))
+  problems, want = [], []
+  for M, N, K in shapes:
+    aq = torch.randn(M, K, device="cuda", generator=g).to(torch.float8_e4m3fn)
+    wq = torch.randn(N, K, device="cuda", generator=g).to(torch.float8_e4m3fn)
+    sa = torch.rand(M, device="cuda", generator=g) + 0.5
+    sw = torch.rand(N, device="cuda", generator=g) + 0.5
+    bias = torch.randn(N, device="cuda", generator=g).to(torch.bfloat16)
+    ref = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    nat.fp8_gemm_rowscaled(aq, sa, wq, sw, bias, ref)
+    want.append(ref)
+    problems.append((aq, sa, wq, sw, bias, torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")))
+  nat.fp8_gemm_rowscaled_grouped(problems)
+  torch.cuda.synchronize()
+  for (_, _, _, _, _, out), ref in zip(problems, want):
+    assert torch.equal(out, ref)
+  assert nat.gemm_device_status(torch.device("cuda:0")) == 0
