@@ -21,7 +21,7 @@ from ..caching.block_adapters import BlockAdapter, BlockAdapterRegister
 from ..caching.forward_pattern import ForwardPattern
 from .layers import (RMSNorm, RopeCache, TimestepMLP, UlyssesGroup, concat_gelu_linear, gated_add, gelu_linear_pair,
                      joint_attention, join_tokens, linear_pair, norm_modulate, norm_modulate_linears,
-                     norm_modulate_linears_pair, split_tokens, timestep_embedding)
+                     norm_modulate_linears_pair, shared_input_linears, split_tokens, timestep_embedding)
 
 
 class AdaLayerNormZero(nn.Module):
@@ -82,8 +82,10 @@ class FluxTransformerBlock(nn.Module):
 
   def forward(self, hidden_states, encoder_hidden_states, temb, image_rotary_emb):
     a = self.attn
-    shift, scale, gate, shift_mlp, scale_mlp, gate_mlp = self.norm1(temb)
-    c_shift, c_scale, c_gate, c_shift_mlp, c_scale_mlp, c_gate_mlp = self.norm1_context(temb)
+    # both streams' modulation projections read SiLU(temb): one quantization, one weight-streaming product
+    mod, c_mod = shared_input_linears(F.silu(temb), (self.norm1.linear, self.norm1_context.linear))
+    shift, scale, gate, shift_mlp, scale_mlp, gate_mlp = mod.chunk(6, dim=-1)
+    c_shift, c_scale, c_gate, c_shift_mlp, c_scale_mlp, c_gate_mlp = c_mod.chunk(6, dim=-1)
     (q, k, v), (cq, ck, cv) = norm_modulate_linears_pair(
       (hidden_states, shift, scale, (a.to_q, a.to_k, a.to_v)),
       (encoder_hidden_states, c_shift, c_scale, (a.add_q_proj, a.add_k_proj, a.add_v_proj)))

@@ -83,6 +83,14 @@ def gelu_linear_pair(xa, lina, xb, linb):
   return ra, rb
 
 
+def shared_input_linears(x: torch.Tensor, linears: Sequence[nn.Module]) -> List[torch.Tensor]:
+  """[lin(x) for lin in linears]; FP8 linears share one quantization of x and one product."""
+  if _all_fp8(linears) and x.is_cuda and len(linears) > 1:
+    a_q, a_scale = linears[0].quantize_input(x)
+    return list(fused_group(linears).forward_quantized(a_q, a_scale, x.shape[:-1]))
+  return [lin(x) for lin in linears]
+
+
 def norm_modulate(x: torch.Tensor, shift: torch.Tensor, scale: torch.Tensor, eps: float = 1e-6):
   return F.layer_norm(x, (x.shape[-1], ), eps=eps) * (1 + scale[:, None]) + shift[:, None]
 
