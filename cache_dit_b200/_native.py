@@ -34,6 +34,9 @@ SIGNATURES = {
   "cdb_fp8_quant_rows": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
   "cdb_fp8_quant_rows_fused": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p,
                                        c_int64, c_int64, c_float, c_void_p, c_void_p, c_void_p]),
+  "cdb_fp8_quant_rows_fused_pair": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_void_p,
+                                            c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_int64,
+                                            c_void_p, c_void_p, c_int64, c_int, c_float, c_void_p]),
   "cdb_fp8_quant_rows_concat_gelu": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64,
                                              c_void_p, c_void_p, c_void_p]),
   "cdb_fp8_gemm_rowscaled": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
@@ -500,3 +503,29 @@ def fp8_gemm_rowscaled_grouped(problems):
     end.record()
     timer.append((start, end, flops))
   check(st, "cdb_fp8_gemm_rowscaled_grouped")
+
+
+def fp8_quant_rows_pair(jobs, preop=PRE_NONE, eps=0.0):
+  """Two `fp8_quant_rows` jobs of the same width in one launch.  jobs: two dicts with x2d [rows, cols] bf16, q,
+  scale and, for the LayerNorm variant, mod_shift / mod_scale [batch, cols] and rows_per_batch."""
+  a, b = jobs
+  args = []
+  cols = a["x2d"].shape[1]
+  for j in (a, b):
+    x2d, q, scale = j["x2d"], j["q"], j["scale"]
+    sh, sc = j.get("mod_shift"), j.get("mod_scale")
+    _need_cuda(x2d, q, scale, sh, sc)
+    _need_contig(q, scale)
+    if x2d.dtype != torch.bfloat16 or x2d.dim() != 2 or x2d.stride(1) != 1 or x2d.shape[1] != cols:
+      raise RuntimeError("fp8_quant_rows_pair: bf16 matrices of one width with unit column stride")
+    rows = x2d.shape[0]
+    ld_mod = 0
+    if preop == PRE_LAYERNORM_MOD:
+      if sh.dim() != 2 or sc.dim() != 2 or sh.stride(1) != 1 or sc.stride(1) != 1 or sh.stride(0) != sc.stride(0) \
+          or sh.dtype != torch.bfloat16 or sc.dtype != torch.bfloat16:
+        raise RuntimeError("fp8_quant_rows_pair: modulation must be two bf16 [batch, cols] matrices")
+      ld_mod = sh.stride(0)
+    args += [_ptr(x2d), rows, x2d.stride(0) if rows > 1 else max(cols, x2d.stride(0)), _ptr(sh), _ptr(sc),
+             int(j.get("rows_per_batch", 0)), ld_mod, _ptr(q), _ptr(scale)]
+  st = lib().cdb_fp8_quant_rows_fused_pair(*args, cols, int(preop), float(eps), _stream(a["x2d"]))
+  check(st, "cdb_fp8_quant_rows_fused_pair")

@@ -7,6 +7,7 @@
 // plus one float per row are written.  HBM-bound: 2 B read + 1 B written per element.
 #include <cuda_fp8.h>
 
+#include <cstdint>
 #include <cstdlib>
 
 #include "common.cuh"
@@ -26,6 +27,16 @@ struct QuantFuse {
   const __nv_bfloat16* tail;
   int64_t ld_tail;
   int head_packs;
+  // Second tensor quantized by the same launch (x2 != nullptr): rows [rows1, rows) of the launch are its
+  // rows 0..; it has its own modulation vectors and outputs.  Used for the image and the text stream of a
+  // double-stream block, whose text part alone would be a launch of a few microseconds.
+  const __nv_bfloat16* x2;
+  int64_t rows1, ld_x2;
+  const __nv_bfloat16* shift2;
+  const __nv_bfloat16* scale2;
+  int64_t rows_per_batch2, ld_mod2;
+  uint8_t* q2;
+  float* scale_out2;
 };
 
 // tanh-GELU as x * sigmoid(2u), u = sqrt(2/pi) (x + 0.044715 x^3) = x / (1 + 2^(c x (1 + 0.044715 x^2))),
@@ -93,11 +104,16 @@ __global__ void __launch_bounds__(Q_CTA)
   // round(1 + scale) and of shift stays in registers until the batch index changes.
   constexpr int MV = PREOP == CDB_PRE_LAYERNORM_MOD ? VPT : 1;
   uint4 m_one_plus[MV], m_shift[MV];
-  int64_t m_batch = -1;
+  int64_t m_batch = INT64_MIN;
+  // Rows [rows1, rows) belong to the second tensor of a two-tensor launch.
+  auto second = [&](int64_t row) { return f.x2 != nullptr && row >= f.rows1; };
+  auto row_ptr = [&](int64_t row) -> const __nv_bfloat16* {
+    return second(row) ? f.x2 + (row - f.rows1) * f.ld_x2 : x + row * ld_x;
+  };
   // One row's packets for this thread; rows past the end and packets past the row load zeros.
   auto load_row = [&](int64_t row, uint4 (&dst)[VPT]) {
     const bool valid = row < rows;
-    const __nv_bfloat16* xr = x + (valid ? row : 0) * ld_x;
+    const __nv_bfloat16* xr = row_ptr(valid ? row : 0);
 #pragma unroll
     for (int k = 0; k < VPT; ++k) {
       const int p = tig + k * TPR;
@@ -120,7 +136,7 @@ __global__ void __launch_bounds__(Q_CTA)
 #pragma unroll
     for (int k = 0; k < VPT; ++k) {
       const int p = tig + k * TPR;
-      const uint4* src = reinterpret_cast<const uint4*>(x + row * ld_x) + p;
+      const uint4* src = reinterpret_cast<const uint4*>(row_ptr(row)) + p;
       if constexpr (PREOP == CDB_PRE_CONCAT_GELU) {
         if (p >= f.head_packs) src = reinterpret_cast<const uint4*>(f.tail + row * f.ld_tail) + (p - f.head_packs);
       }
@@ -171,11 +187,14 @@ __global__ void __launch_bounds__(Q_CTA)
       }
       const float var = row_reduce<TPR, false>(ss, s_red, slot) / (float)cols;
       const float rstd = rsqrtf(var + f.eps);
-      const int64_t bidx = (valid ? row : 0) / f.rows_per_batch;
-      if (bidx != m_batch) {
-        m_batch = bidx;
-        const uint4* sh = reinterpret_cast<const uint4*>(f.shift + bidx * f.ld_mod);
-        const uint4* sc = reinterpret_cast<const uint4*>(f.scale + bidx * f.ld_mod);
+      const int64_t vrow = valid ? row : 0;
+      const bool sec = second(vrow);
+      const int64_t bidx = sec ? (vrow - f.rows1) / f.rows_per_batch2 : vrow / f.rows_per_batch;
+      const int64_t mod_key = sec ? ~bidx : bidx;  // distinct keys for the two tensors' batches
+      if (mod_key != m_batch) {
+        m_batch = mod_key;
+        const uint4* sh = reinterpret_cast<const uint4*>(sec ? f.shift2 + bidx * f.ld_mod2 : f.shift + bidx * f.ld_mod);
+        const uint4* sc = reinterpret_cast<const uint4*>(sec ? f.scale2 + bidx * f.ld_mod2 : f.scale + bidx * f.ld_mod);
         const __nv_bfloat162 one = __float2bfloat162_rn(1.0f);
 #pragma unroll
         for (int k = 0; k < VPT; ++k) {
@@ -237,7 +256,11 @@ __global__ void __launch_bounds__(Q_CTA)
     // amax / 448 the way PyTorch's CUDA division by a Python scalar computes it: times fl32(1/448)
     float sc = __fmul_rn(amax, 1.0f / E4M3_MAX);
     if (sc == 0.f) sc = 1.f;  // all-zero row: keep zeros exact instead of 0/0
-    if (valid && tig == 0) scale[row] = sc;
+    const bool out2 = valid && second(row);
+    if (valid && tig == 0) {
+      if (out2) f.scale_out2[row - f.rows1] = sc;
+      else scale[row] = sc;
+    }
 
     // x / sc with one reciprocal per row.  Plain variant (weights, bit-exact against the reference's
     // division): t = x * (1/sc) followed by one Newton correction (r = x - t*sc exactly by FMA;
@@ -255,7 +278,7 @@ __global__ void __launch_bounds__(Q_CTA)
       float r = fmaf(-t, sc, v);
       return fmaf(r, inv, t);
     };
-    uint8_t* qr = q + (valid ? row : 0) * (int64_t)cols;
+    uint8_t* qr = out2 ? f.q2 + (row - f.rows1) * (int64_t)cols : q + (valid ? row : 0) * (int64_t)cols;
 #pragma unroll
     for (int k = 0; k < VPT; ++k) {
       const int p = tig + k * TPR;
@@ -355,6 +378,54 @@ extern "C" int cdb_fp8_quant_rows_fused(const void* x, int64_t rows, int64_t col
       f.ld_mod = ld_mod;
       f.eps = eps;
       return launch_quant<CDB_PRE_LAYERNORM_MOD>(x, rows, cols, ld_x, f, q, scale, st);
+    default:
+      return CDB_ERR_BAD_ARGUMENT;
+  }
+}
+
+// Two tensors of the same width in one launch (rows of x first, then rows of x2), each with its own
+// modulation vectors and outputs.
+extern "C" int cdb_fp8_quant_rows_fused_pair(const void* x, int64_t rows, int64_t ld_x, const void* mod_shift,
+                                             const void* mod_scale, int64_t rows_per_batch, int64_t ld_mod, void* q,
+                                             float* scale, const void* x2, int64_t rows2, int64_t ld_x2,
+                                             const void* mod_shift2, const void* mod_scale2, int64_t rows_per_batch2,
+                                             int64_t ld_mod2, void* q2, float* scale2, int64_t cols, int preop,
+                                             float eps, void* stream) {
+  if (!x || !q || !scale || !x2 || !q2 || !scale2 || rows < 0 || rows2 < 0 || cols <= 0 || ld_x < cols || ld_x2 < cols)
+    return CDB_ERR_BAD_ARGUMENT;
+  if (rows + rows2 == 0) return CDB_OK;
+  if (cols % 8 != 0 || ld_x % 8 != 0 || ld_x2 % 8 != 0 || !aligned16(x) || !aligned16(x2) ||
+      (reinterpret_cast<uintptr_t>(q) & 7u) || (reinterpret_cast<uintptr_t>(q2) & 7u))
+    return CDB_ERR_UNSUPPORTED;
+  QuantFuse f{};
+  f.x2 = static_cast<const __nv_bfloat16*>(x2);
+  f.rows1 = rows;
+  f.ld_x2 = ld_x2;
+  f.q2 = static_cast<uint8_t*>(q2);
+  f.scale_out2 = scale2;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (preop) {
+    case CDB_PRE_NONE:
+      return launch_quant<CDB_PRE_NONE>(x, rows + rows2, cols, ld_x, f, q, scale, st);
+    case CDB_PRE_GELU_TANH:
+      return launch_quant<CDB_PRE_GELU_TANH>(x, rows + rows2, cols, ld_x, f, q, scale, st);
+    case CDB_PRE_LAYERNORM_MOD:
+      if (!mod_shift || !mod_scale || !mod_shift2 || !mod_scale2 || rows_per_batch <= 0 || rows_per_batch2 <= 0 ||
+          ld_mod < cols || ld_mod2 < cols)
+        return CDB_ERR_BAD_ARGUMENT;
+      if (ld_mod % 8 != 0 || ld_mod2 % 8 != 0 || !aligned16(mod_shift) || !aligned16(mod_scale) ||
+          !aligned16(mod_shift2) || !aligned16(mod_scale2))
+        return CDB_ERR_UNSUPPORTED;
+      f.shift = static_cast<const __nv_bfloat16*>(mod_shift);
+      f.scale = static_cast<const __nv_bfloat16*>(mod_scale);
+      f.rows_per_batch = rows_per_batch;
+      f.ld_mod = ld_mod;
+      f.shift2 = static_cast<const __nv_bfloat16*>(mod_shift2);
+      f.scale2 = static_cast<const __nv_bfloat16*>(mod_scale2);
+      f.rows_per_batch2 = rows_per_batch2;
+      f.ld_mod2 = ld_mod2;
+      f.eps = eps;
+      return launch_quant<CDB_PRE_LAYERNORM_MOD>(x, rows + rows2, cols, ld_x, f, q, scale, st);
     default:
       return CDB_ERR_BAD_ARGUMENT;
   }

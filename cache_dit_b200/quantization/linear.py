@@ -90,6 +90,28 @@ def quantize_rows_fused(x: torch.Tensor, preop: int, mod_shift=None, mod_scale=N
   return a_q, a_scale, lead
 
 
+def quantize_rows_fused_pair(xa: torch.Tensor, xb: torch.Tensor, preop: int, mods_a=None, mods_b=None,
+                             eps: float = 1e-6):
+  """`quantize_rows_fused` on two tensors of the same width with ONE launch (image and text stream of a
+  double-stream block).  mods_* = (shift, scale) for the LayerNorm variant.  Returns two
+  (a_q, a_scale, lead_shape) triples."""
+  jobs, results = [], []
+  for x, mods in ((xa, mods_a), (xb, mods_b)):
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.stride(-1) != 1:
+      x2 = x2.contiguous()
+    a_q = torch.empty(x2.shape, dtype=torch.float8_e4m3fn, device=x.device)
+    a_scale = torch.empty(x2.shape[0], dtype=torch.float32, device=x.device)
+    job = dict(x2d=x2, q=a_q, scale=a_scale)
+    if preop == _native.PRE_LAYERNORM_MOD:
+      job.update(mod_shift=mods[0], mod_scale=mods[1], rows_per_batch=x2.shape[0] // mods[0].shape[0])
+    jobs.append(job)
+    results.append((a_q, a_scale, lead))
+  _native.fp8_quant_rows_pair(jobs, preop, eps)
+  return results
+
+
 class FusedFloat8Linears(torch.nn.Module):
   """Several FP8 linears that read the same activations, run as ONE GEMM over the concatenated
   output rows (q/k/v, or q/k/v + MLP-in).  Per-row weight scales make this exactly the same

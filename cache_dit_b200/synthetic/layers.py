@@ -17,7 +17,7 @@ from torch import nn
 
 from .. import _native
 from ..quantization.linear import (Float8RowwiseLinear, fused_group, grouped_forward_quantized,
-                                   quantize_rows_fused)
+                                   quantize_rows_fused, quantize_rows_fused_pair)
 
 
 def _all_fp8(linears: Sequence[nn.Module]) -> bool:
@@ -50,10 +50,8 @@ def norm_modulate_linears_pair(a, b, eps: float = 1e-6):
   (xa, sha, sca, la), (xb, shb, scb, lb) = a, b
   if not _pair_ready(xa, xb, tuple(la) + tuple(lb)):
     return norm_modulate_linears(xa, sha, sca, la, eps), norm_modulate_linears(xb, shb, scb, lb, eps)
-  items = []
-  for x, sh, sc, lin in ((xa, sha, sca, la), (xb, shb, scb, lb)):
-    a_q, a_scale, lead = quantize_rows_fused(x, _native.PRE_LAYERNORM_MOD, sh, sc, eps)
-    items.append((fused_group(lin) if len(lin) > 1 else lin[0], a_q, a_scale, lead))
+  qa, qb = quantize_rows_fused_pair(xa, xb, _native.PRE_LAYERNORM_MOD, (sha, sca), (shb, scb), eps)
+  items = [(fused_group(lin) if len(lin) > 1 else lin[0], *triple) for lin, triple in ((la, qa), (lb, qb))]
   ra, rb = grouped_forward_quantized(items)
   as_list = lambda r: list(r) if isinstance(r, (tuple, list)) else [r]
   return as_list(ra), as_list(rb)
@@ -63,11 +61,8 @@ def linear_pair(xa, lina, xb, linb):
   """(lina(xa), linb(xb)) with one GEMM launch."""
   if not _pair_ready(xa, xb, (lina, linb)):
     return lina(xa), linb(xb)
-  items = []
-  for x, lin in ((xa, lina), (xb, linb)):
-    a_q, a_scale = lin.quantize_input(x)
-    items.append((lin, a_q, a_scale, x.shape[:-1]))
-  ra, rb = grouped_forward_quantized(items)
+  qa, qb = quantize_rows_fused_pair(xa, xb, _native.PRE_NONE)
+  ra, rb = grouped_forward_quantized([(lina, *qa), (linb, *qb)])
   return ra, rb
 
 
@@ -75,11 +70,8 @@ def gelu_linear_pair(xa, lina, xb, linb):
   """(lina(gelu_tanh(xa)), linb(gelu_tanh(xb))) with one GEMM launch."""
   if not _pair_ready(xa, xb, (lina, linb)):
     return gelu_linear(xa, lina), gelu_linear(xb, linb)
-  items = []
-  for x, lin in ((xa, lina), (xb, linb)):
-    a_q, a_scale, lead = quantize_rows_fused(x, _native.PRE_GELU_TANH)
-    items.append((lin, a_q, a_scale, lead))
-  ra, rb = grouped_forward_quantized(items)
+  qa, qb = quantize_rows_fused_pair(xa, xb, _native.PRE_GELU_TANH)
+  ra, rb = grouped_forward_quantized([(lina, *qa), (linb, *qb)])
   return ra, rb
 
 

@@ -163,6 +163,16 @@ typedef struct cdb_gemm_problem {
 CDB_API int cdb_fp8_gemm_rowscaled_grouped(const void* problems /* cdb_gemm_problem[count] */, int count,
                                    int32_t* status_word, void* stream);
 
+/* cdb_fp8_quant_rows_fused on two tensors of the same width in one launch (image and text stream of a
+ * double-stream block): each has its own rows, row stride, modulation vectors (LayerNorm variant) and
+ * outputs.  preop is CDB_PRE_NONE, CDB_PRE_LAYERNORM_MOD or CDB_PRE_GELU_TANH. */
+CDB_API int cdb_fp8_quant_rows_fused_pair(const void* x, int64_t rows, int64_t ld_x, const void* mod_shift,
+                                  const void* mod_scale, int64_t rows_per_batch, int64_t ld_mod, void* q,
+                                  float* scale, const void* x2, int64_t rows2, int64_t ld_x2,
+                                  const void* mod_shift2, const void* mod_scale2, int64_t rows_per_batch2,
+                                  int64_t ld_mod2, void* q2, float* scale2, int64_t cols, int preop, float eps,
+                                  void* stream);
+
 /* Quantizes the rows of the concatenation [head | gelu_tanh(tail)] without building it: the input
  * of a parallel attention + MLP block's output projection (attention output beside the activated
  * MLP branch).  head [rows, head_cols] and tail [rows, tail_cols] are bf16 with their own row

@@ -381,3 +381,37 @@ def test_fp8_gemm_grouped_equals_separate_launches(nat, shapes):
   for (_, _, _, _, _, out), ref in zip(problems, want):
     assert torch.equal(out, ref)
   assert nat.gemm_device_status(torch.device("cuda:0")) == 0
+
+
+@pytest.mark.parametrize("preop", ["none", "layernorm", "gelu"])
+def test_fp8_quant_pair_equals_separate_launches(nat, preop):
+  """Two tensors quantized by one launch (different row counts, strides and modulation vectors) give
+  exactly what two launches give."""
+  code = {"none": nat.PRE_NONE, "layernorm": nat.PRE_LAYERNORM_MOD, "gelu": nat.PRE_GELU_TANH}[preop]
+  cols = 3072
+  xa_d, _ = activations(2 * 300, cols, 31)
+  wide, _ = activations(3 * 37, cols + 64, 32)
+  xb_d = wide[:, 64:]  # strided rows
+  mods = {}
+  for name, batch, seed in (("a", 2, 33), ("b", 3, 34)):
+    m, _ = make((batch, 2 * cols), "bf16", seed, 0.2)
+    mods[name] = (m[:, :cols], m[:, cols:])
+  jobs, want = [], []
+  for x, name, batch in ((xa_d, "a", 2), (xb_d, "b", 3)):
+    rows = x.shape[0]
+    q = torch.empty(rows, cols, dtype=torch.float8_e4m3fn, device="cuda")
+    s = torch.empty(rows, dtype=torch.float32, device="cuda")
+    if preop == "layernorm":
+      nat.fp8_quant_rows(x, q, s, code, mods[name][0], mods[name][1], rows // batch, 1e-6)
+    else:
+      nat.fp8_quant_rows(x, q, s, code)
+    want.append((q, s))
+    job = dict(x2d=x, q=torch.zeros_like(q), scale=torch.zeros_like(s))
+    if preop == "layernorm":
+      job.update(mod_shift=mods[name][0], mod_scale=mods[name][1], rows_per_batch=rows // batch)
+    jobs.append(job)
+  nat.fp8_quant_rows_pair(jobs, code, 1e-6)
+  torch.cuda.synchronize()
+  for job, (q, s) in zip(jobs, want):
+    assert torch.equal(job["scale"], s)
+    assert torch.equal(job["q"].view(torch.uint8), q.view(torch.uint8))
