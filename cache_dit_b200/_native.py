@@ -44,6 +44,9 @@ SIGNATURES = {
   "cdb_fp8_gemm_rowscaled_grouped": (c_int, [c_void_p, c_int, c_void_p, c_void_p]),
   "cdb_qk_norm_rope": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                                c_int64, c_int64, c_int, c_int, c_int, c_float, c_void_p]),
+  "cdb_gated_residual_pair": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64,
+                                      c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64,
+                                      c_int64, c_void_p]),
   "cdb_peer_enable_access": (c_int, [c_int]),
   "cdb_peer_alloc": (c_int, [c_size_t, POINTER(c_void_p)]),
   "cdb_peer_free": (c_int, [c_void_p]),
@@ -529,3 +532,22 @@ def fp8_quant_rows_pair(jobs, preop=PRE_NONE, eps=0.0):
              int(j.get("rows_per_batch", 0)), ld_mod, _ptr(q), _ptr(scale)]
   st = lib().cdb_fp8_quant_rows_fused_pair(*args, cols, int(preop), float(eps), _stream(a["x2d"]))
   check(st, "cdb_fp8_quant_rows_fused_pair")
+
+
+def gated_residual_pair(xa, gate_a, ya, xb, gate_b, yb):
+  """(xa + gate_a * ya, xb + gate_b * yb) with one launch; same rules per set as `gated_residual`."""
+  args, outs = [], []
+  cols = xa.shape[-1]
+  for x, gate, y in ((xa, gate_a, ya), (xb, gate_b, yb)):
+    _need_cuda(x, gate, y)
+    _need_contig(x)
+    b, t, c = x.shape
+    if x.dtype != torch.bfloat16 or y.dtype != x.dtype or gate.dtype != x.dtype or y.stride(2) != 1 or c != cols \
+        or gate.stride(1) != 1 or (b > 1 and y.stride(0) != t * y.stride(1)) or y.shape != x.shape:
+      raise RuntimeError("gated_residual_pair: bf16 operands of one width, unit column stride, uniform row strides")
+    out = torch.empty_like(x)
+    outs.append(out)
+    args += [_ptr(x), _ptr(y), y.stride(1), _ptr(gate), gate.stride(0) if b > 1 else c, _ptr(out), b * t, t]
+  st = lib().cdb_gated_residual_pair(*args, cols, _stream(xa))
+  check(st, "cdb_gated_residual_pair")
+  return outs[0], outs[1]

@@ -40,6 +40,38 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+// Two gated residual adds in one launch (blockIdx.y = job): image and text stream of a double-stream block.
+struct GatedJob {
+  const __nv_bfloat16* x;
+  const __nv_bfloat16* y;
+  const __nv_bfloat16* gate;
+  __nv_bfloat16* out;
+  int64_t ld_y, ld_gate, rows, rows_per_batch;
+};
+struct GatedJobs {
+  GatedJob job[2];
+};
+__global__ void __launch_bounds__(256) gated_residual_pair_kernel(const __grid_constant__ GatedJobs jobs, int cols) {
+  const GatedJob& j = jobs.job[blockIdx.y];
+  const int packs = cols >> 3;
+  const int64_t total = j.rows * packs;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int64_t row = i / packs;
+    const int p = (int)(i - row * packs);
+    const int64_t b = row / j.rows_per_batch;
+    const uint4 xv = __ldcs(reinterpret_cast<const uint4*>(j.x + row * cols) + p);
+    const uint4 yv = __ldcs(reinterpret_cast<const uint4*>(j.y + row * j.ld_y) + p);
+    const uint4 gv = __ldg(reinterpret_cast<const uint4*>(j.gate + b * j.ld_gate) + p);
+    uint4 o;
+    o.x = b2u(__hadd2_rn(u2b(xv.x), __hmul2_rn(u2b(gv.x), u2b(yv.x))));
+    o.y = b2u(__hadd2_rn(u2b(xv.y), __hmul2_rn(u2b(gv.y), u2b(yv.y))));
+    o.z = b2u(__hadd2_rn(u2b(xv.z), __hmul2_rn(u2b(gv.z), u2b(yv.z))));
+    o.w = b2u(__hadd2_rn(u2b(xv.w), __hmul2_rn(u2b(gv.w), u2b(yv.w))));
+    __stcs(reinterpret_cast<uint4*>(j.out + row * cols) + p, o);
+  }
+}
+
 }  // namespace cdb
 
 using namespace cdb;
@@ -77,6 +109,34 @@ extern "C" int cdb_gated_residual(const void* x, const void* y, int64_t ld_y, co
       static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(y), ld_y,
       static_cast<const __nv_bfloat16*>(gate), ld_gate, static_cast<__nv_bfloat16*>(out), rows, rows_per_batch,
       (int)cols);
+  CDB_CUDA_CHECK(cudaGetLastError());
+  return CDB_OK;
+}
+
+extern "C" int cdb_gated_residual_pair(const void* x, const void* y, int64_t ld_y, const void* gate, int64_t ld_gate,
+                                       void* out, int64_t rows, int64_t rows_per_batch, const void* x2, const void* y2,
+                                       int64_t ld_y2, const void* gate2, int64_t ld_gate2, void* out2, int64_t rows2,
+                                       int64_t rows_per_batch2, int64_t cols, void* stream) {
+  if (!x || !y || !gate || !out || !x2 || !y2 || !gate2 || !out2 || rows < 0 || rows2 < 0 || rows_per_batch <= 0 ||
+      rows_per_batch2 <= 0 || cols <= 0)
+    return CDB_ERR_BAD_ARGUMENT;
+  if (rows + rows2 == 0) return CDB_OK;
+  if (cols % 8 != 0 || ld_y % 8 != 0 || ld_gate % 8 != 0 || ld_y2 % 8 != 0 || ld_gate2 % 8 != 0 || !aligned16(x) ||
+      !aligned16(y) || !aligned16(gate) || !aligned16(out) || !aligned16(x2) || !aligned16(y2) || !aligned16(gate2) ||
+      !aligned16(out2))
+    return CDB_ERR_UNSUPPORTED;
+  GatedJobs jobs{};
+  jobs.job[0] = GatedJob{static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(y),
+                         static_cast<const __nv_bfloat16*>(gate), static_cast<__nv_bfloat16*>(out), ld_y, ld_gate, rows,
+                         rows_per_batch};
+  jobs.job[1] = GatedJob{static_cast<const __nv_bfloat16*>(x2), static_cast<const __nv_bfloat16*>(y2),
+                         static_cast<const __nv_bfloat16*>(gate2), static_cast<__nv_bfloat16*>(out2), ld_y2, ld_gate2,
+                         rows2, rows_per_batch2};
+  const int64_t big = (rows > rows2 ? rows : rows2) * (cols / 8);
+  const int64_t blocks = (big + 255) / 256;
+  const int64_t cap = (int64_t)sm_count() * 8;
+  const dim3 grid((unsigned)(blocks < cap ? blocks : cap), 2);
+  gated_residual_pair_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(jobs, (int)cols);
   CDB_CUDA_CHECK(cudaGetLastError());
   return CDB_OK;
 }

@@ -19,7 +19,8 @@ from torch import nn
 
 from ..caching.block_adapters import BlockAdapter, BlockAdapterRegister
 from ..caching.forward_pattern import ForwardPattern
-from .layers import (RMSNorm, RopeCache, TimestepMLP, UlyssesGroup, concat_gelu_linear, gated_add, gelu_linear_pair,
+from .layers import (RMSNorm, RopeCache, TimestepMLP, UlyssesGroup, concat_gelu_linear, gated_add, gated_add_pair,
+                     gelu_linear_pair,
                      joint_attention, join_tokens, linear_pair, norm_modulate, norm_modulate_linears,
                      norm_modulate_linears_pair, shared_input_linears, split_tokens, timestep_embedding)
 
@@ -93,13 +94,11 @@ class FluxTransformerBlock(nn.Module):
                         image_rotary_emb, a.heads, self.cp)
     n_txt = encoder_hidden_states.shape[1]
     y, cy = linear_pair(o[:, n_txt:], a.to_out, o[:, :n_txt], a.to_add_out)
-    hidden_states = gated_add(hidden_states, gate, y)
-    encoder_hidden_states = gated_add(encoder_hidden_states, c_gate, cy)
+    hidden_states, encoder_hidden_states = gated_add_pair(hidden_states, gate, y, encoder_hidden_states, c_gate, cy)
     (h, ), (c, ) = norm_modulate_linears_pair((hidden_states, shift_mlp, scale_mlp, (self.ff.proj_in, )),
                                               (encoder_hidden_states, c_shift_mlp, c_scale_mlp, (self.ff_context.proj_in, )))
     y, cy = gelu_linear_pair(h, self.ff.proj_out, c, self.ff_context.proj_out)
-    hidden_states = gated_add(hidden_states, gate_mlp, y)
-    encoder_hidden_states = gated_add(encoder_hidden_states, c_gate_mlp, cy)
+    hidden_states, encoder_hidden_states = gated_add_pair(hidden_states, gate_mlp, y, encoder_hidden_states, c_gate_mlp, cy)
     return encoder_hidden_states, hidden_states
 
 

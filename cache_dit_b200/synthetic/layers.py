@@ -235,6 +235,15 @@ def gated_add(x: torch.Tensor, gate: torch.Tensor, y: torch.Tensor) -> torch.Ten
   return x + gate[:, None] * y
 
 
+def gated_add_pair(xa, gate_a, ya, xb, gate_b, yb):
+  """(xa + gate_a[:, None] * ya, xb + gate_b[:, None] * yb), one launch for both streams on the GPU."""
+  ok = lambda x, g, y: (_glue_kernels_apply(x) and x.is_contiguous() and x.shape[-1] % 8 == 0 and y.stride(-1) == 1
+                        and y.stride(1) % 8 == 0 and g.stride(-1) == 1 and g.stride(0) % 8 == 0)
+  if ok(xa, gate_a, ya) and ok(xb, gate_b, yb) and xa.shape[-1] == xb.shape[-1]:
+    return _native.gated_residual_pair(xa, gate_a, ya, xb, gate_b, yb)
+  return gated_add(xa, gate_a, ya), gated_add(xb, gate_b, yb)
+
+
 class UlyssesGroup:
   """What attention needs to know about context parallelism: the group, its size, and - when the
   ranks share one NVLink domain - the peer-memory exchange that replaces the all-to-all calls."""

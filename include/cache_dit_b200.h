@@ -300,6 +300,12 @@ CDB_API int cdb_peer_wait(const void* my_flags, int world, void* sync, uint64_t 
 CDB_API int cdb_peer_barrier(void* const* flag_ptrs, const void* my_flags, int world, int my_rank, void* sync,
                      uint64_t timeout_ns, void* stream);
 
+/* cdb_gated_residual on two (x, y, gate, out) sets of the same width in one launch. */
+CDB_API int cdb_gated_residual_pair(const void* x, const void* y, int64_t ld_y, const void* gate, int64_t ld_gate,
+                            void* out, int64_t rows, int64_t rows_per_batch, const void* x2, const void* y2,
+                            int64_t ld_y2, const void* gate2, int64_t ld_gate2, void* out2, int64_t rows2,
+                            int64_t rows_per_batch2, int64_t cols, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

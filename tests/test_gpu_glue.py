@@ -123,3 +123,17 @@ def test_fp8_quant_concat_gelu_matches_two_step(nat, rows, c1, c2):
   codes, codes2 = q.view(torch.uint8)[same_scale], q2.view(torch.uint8)[same_scale]
   assert (codes != codes2).float().mean().item() < 1e-3
   torch.testing.assert_close(s, s2, rtol=2.0**-7, atol=0)
+
+
+def test_gated_residual_pair_equals_separate(nat):
+  g = torch.Generator().manual_seed(9)
+  cols = 3072
+  sets = []
+  for batch, tokens in ((1, 4096), (1, 512)):
+    x = torch.randn(batch, tokens, cols, generator=g).to("cuda", torch.bfloat16)
+    y = torch.randn(batch, tokens, 2 * cols, generator=g).to("cuda", torch.bfloat16)[..., cols:]
+    gate = torch.randn(batch, 6 * cols, generator=g).to("cuda", torch.bfloat16).chunk(6, dim=-1)[4]
+    sets.append((x, gate, y))
+  a, b = nat.gated_residual_pair(*sets[0], *sets[1])
+  assert torch.equal(a, sets[0][0] + sets[0][1][:, None] * sets[0][2])
+  assert torch.equal(b, sets[1][0] + sets[1][1][:, None] * sets[1][2])
