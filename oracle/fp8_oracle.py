@@ -3,12 +3,16 @@
 TEST INFRASTRUCTURE, NOT PRODUCT CODE: imported only by the tests, the smoke check and the
 CPU-baseline leg of the benchmark.
 
-PARITY UNPINNED.  In the reference this arithmetic lives in two third-party dependencies that are
-neither vendored nor installed here: torchao (pyproject lower bound `torchao>=0.17.0`, no lock
-file) for the dynamic activation / weight quantization, and `torch._scaled_mm` for the product
-(which refuses row-wise scales on CPU).  The reference holds no golden values for this path; its
-tests compare torchao with itself.  This file therefore restates the published algorithm and is
-anchored on the reference's own call sites:
+PARITY: PINNED FOR THE E4M3 CAST AND THE PRODUCT, UNPINNED FOR TORCHAO'S SCALE RULE.  In the reference this
+arithmetic lives in two third-party dependencies: torchao (pyproject lower bound `torchao>=0.17.0`, no lock
+file; neither vendored nor installed here) for the dynamic activation / weight quantization, and
+`torch._scaled_mm` for the product (which refuses row-wise scales on CPU).  The reference holds no golden
+values for this path; its tests compare torchao with itself.  What is pinned: tests/golden/fp8_torch_cuda.npz
+holds scales, e4m3 codes and row-wise `torch._scaled_mm` outputs that PyTorch's CUDA ops produced on a B200
+for small seeded inputs (generator: tests/golden/make_fp8_torch_fixture.py); this file reproduces the scales
+and codes bit for bit and the product to within one bf16 step.  What is not: that torchao computes the scale
+as amax / 448 with 1 for an all-zero row is restated from its published algorithm and from the reference's
+own call sites:
   * config: PerRow/PerRow, e4m3fn, dynamic activations .... src/cache_dit/quantization/torchao/quantize_ao.py:540-558
   * all-zero row -> scale 1 .............................. src/cache_dit/quantization/torchao/quantize_ao.py:43-71
   * operand / scale layout, bias, output dtype ........... src/cache_dit/quantization/torchao/_scaled_mm.py:62-91

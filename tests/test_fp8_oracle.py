@@ -48,3 +48,49 @@ def test_fp8_linear_close_to_fp32_linear():
   got = F.fp8_linear(x, w, b)
   want = x @ w.T + b
   assert np.linalg.norm(got - want) / np.linalg.norm(want) < 0.06
+
+
+# ------------------------------------------------------------------------------ against values PyTorch's CUDA ops produced
+import os
+
+import pytest
+
+FIXTURE = os.path.join(os.path.dirname(__file__), "golden", "fp8_torch_cuda.npz")
+CASES = ["small_bias", "odd_rows", "wide"]
+
+
+def bf16_bits_to_f32(bits: np.ndarray) -> np.ndarray:
+  return (bits.astype(np.uint32) << 16).view(np.float32)
+
+
+@pytest.fixture(scope="module")
+def torch_cuda_fixture():
+  # made by tests/golden/make_fp8_torch_fixture.py on a B200: scales, e4m3 codes and the row-wise
+  # `torch._scaled_mm` product (the call of src/cache_dit/quantization/torchao/_scaled_mm.py:72-91)
+  return np.load(FIXTURE)
+
+
+@pytest.mark.parametrize("case", CASES)
+def test_quantize_rows_equals_torch_cuda(torch_cuda_fixture, case):
+  fx = torch_cuda_fixture
+  for operand, prefix in (("x", "a"), ("w", "w")):
+    codes, scale = F.quantize_rows(bf16_bits_to_f32(fx[f"{case}.{operand}"]))
+    np.testing.assert_array_equal(scale, fx[f"{case}.{prefix}_scale"])
+    np.testing.assert_array_equal(codes, fx[f"{case}.{prefix}_codes"])
+
+
+@pytest.mark.parametrize("case", CASES)
+def test_scaled_mm_matches_torch_cuda(torch_cuda_fixture, case):
+  fx = torch_cuda_fixture
+  bias = bf16_bits_to_f32(fx[f"{case}.bias"]) if f"{case}.bias" in fx.files else None
+  got = F.scaled_mm(fx[f"{case}.a_codes"], fx[f"{case}.a_scale"], fx[f"{case}.w_codes"], fx[f"{case}.w_scale"], bias)
+  want = bf16_bits_to_f32(fx[f"{case}.out"])
+  # both sides round one fp32 accumulation to bf16; summation order and where the scales are applied may
+  # move a value across a rounding boundary: at most one bf16 step, on a small share of the outputs
+  assert np.linalg.norm(got - want) / np.linalg.norm(want) < 1e-3
+  step = np.maximum(np.abs(want), np.abs(got)) * 2.0**-7 + 1e-5  # the absolute term covers results that cancel to ~0
+  assert np.all(np.abs(got - want) <= step)
+  assert np.mean(got != want) < 0.05
+  # and the whole linear from the bf16 operands
+  full = F.fp8_linear(bf16_bits_to_f32(fx[f"{case}.x"]), bf16_bits_to_f32(fx[f"{case}.w"]), bias)
+  np.testing.assert_array_equal(full, got)

@@ -359,6 +359,33 @@ def test_fp8_quant_matches_torch_cast_pipeline(nat, rows, cols):
   assert torch.equal(q.view(torch.uint8), want.view(torch.uint8))
 
 
+@pytest.mark.parametrize("case", ["small_bias", "odd_rows", "wide"])
+def test_fp8_linear_matches_committed_torch_fixture(nat, case):
+  """The committed outputs of PyTorch's CUDA ops (tests/golden/make_fp8_torch_fixture.py): codes and scales
+  bit for bit, the product within the path's tolerance of the library's."""
+  import os
+  fx = np.load(os.path.join(os.path.dirname(__file__), "golden", "fp8_torch_cuda.npz"))
+  dev = lambda bits: torch.from_numpy(bits.view(np.int16).copy()).view(torch.bfloat16).cuda()
+  x, w = dev(fx[f"{case}.x"]), dev(fx[f"{case}.w"])
+  b = dev(fx[f"{case}.bias"]) if f"{case}.bias" in fx.files else None
+  M, K, N = x.shape[0], x.shape[1], w.shape[0]
+  aq = torch.empty(M, K, dtype=torch.float8_e4m3fn, device="cuda")
+  sa = torch.empty(M, dtype=torch.float32, device="cuda")
+  wq = torch.empty(N, K, dtype=torch.float8_e4m3fn, device="cuda")
+  sw = torch.empty(N, dtype=torch.float32, device="cuda")
+  nat.fp8_quant_rows(x, aq, sa)
+  nat.fp8_quant_rows(w, wq, sw)
+  np.testing.assert_array_equal(sa.cpu().numpy(), fx[f"{case}.a_scale"])
+  np.testing.assert_array_equal(aq.view(torch.uint8).cpu().numpy(), fx[f"{case}.a_codes"])
+  np.testing.assert_array_equal(sw.cpu().numpy(), fx[f"{case}.w_scale"])
+  np.testing.assert_array_equal(wq.view(torch.uint8).cpu().numpy(), fx[f"{case}.w_codes"])
+  out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+  nat.fp8_gemm_rowscaled(aq, sa, wq, sw, b, out)
+  want = dev(fx[f"{case}.out"]).float()
+  err = (out.float() - want).norm() / want.norm()
+  assert err.item() < 2e-3, err.item()  # bound of the path: 2e-2
+
+
 @pytest.mark.parametrize("shapes", [((4608, 3072, 3072), (512, 3072, 3072)), ((1000, 520, 256), (130, 264, 256)),
                                     ((300, 272, 512), (700, 1024, 256)), ((4096, 9216, 3072), (512, 9216, 3072))])
 def test_fp8_gemm_grouped_equals_separate_launches(nat, shapes):
