@@ -16,10 +16,22 @@ from .caching import (BasicCacheConfig, BlockAdapter, BlockGraphRunner, disable_
                       CalibratorConfig, ContextNotExistError, DBCacheConfig, ExtraCacheConfig,
                       FakeDiffusionPipeline, ForwardPattern, LazyResidual, ParamsModifier, TaylorSeerCalibrator,
                       TaylorSeerCalibratorConfig, UnifiedBlocks, block_range, cache_type, disable_cache,
-                      enable_cache, get_adapter, refresh_context, steps_mask, supported_pipelines)
-from .distributed import ParallelismConfig, enable_parallelism
-from .quantization import Float8RowwiseLinear, QuantizeConfig, quantize
+                      enable_cache, get_adapter, load_attn_backend_config, load_cache_config, load_configs,
+                      load_options, load_parallelism_config, load_quantize_config, refresh_context, steps_mask,
+                      supported_pipelines)
+from .distributed import ParallelismBackend, ParallelismConfig, enable_parallelism
+from .quantization import Float8RowwiseLinear, QuantizeBackend, QuantizeConfig, quantize
 from .summary import CacheStats, strify, summary
 from . import synthetic  # registers the block adapters of the DiT stand-ins
+
+NONE = CacheType.NONE
+DBCache = CacheType.DBCache
+
+Pattern_0 = ForwardPattern.Pattern_0
+Pattern_1 = ForwardPattern.Pattern_1
+Pattern_2 = ForwardPattern.Pattern_2
+Pattern_3 = ForwardPattern.Pattern_3
+Pattern_4 = ForwardPattern.Pattern_4
+Pattern_5 = ForwardPattern.Pattern_5
 
 __version__ = "0.1.0"

@@ -11,3 +11,5 @@ from .cache_types import CacheType, block_range, cache_type
 from .calibrators import (Calibrator, CalibratorBase, CalibratorConfig, TaylorSeerCalibrator,
                           TaylorSeerCalibratorConfig, TaylorSeerState)
 from .forward_pattern import ForwardPattern
+from .load_configs import (load_attn_backend_config, load_cache_config, load_configs, load_options,
+                           load_parallelism_config, load_quantize_config)

@@ -106,11 +106,18 @@ def refresh_context(transformer: torch.nn.Module, **force_refresh_kwargs):
   generation when the transformer is driven without a pipeline."""
   if force_refresh_kwargs:
     if "cache_config" not in force_refresh_kwargs:
-      known = {f for f in DBCacheConfig.__dataclass_fields__}
-      loose = {k: force_refresh_kwargs.pop(k) for k in list(force_refresh_kwargs) if k in known}
-      if loose:
-        # only the given fields override the context's current config
-        force_refresh_kwargs["cache_config"] = DBCacheConfig().empty(**loose)
+      # loose fields (`num_inference_steps=50`, `enable_taylorseer=True`, ...): only what is named overrides
+      # the context's current configuration (src/cache_dit/caching/cache_interface.py:514-525)
+      from .load_configs import load_cache_config
+      cache_config, calibrator_config = load_cache_config(force_refresh_kwargs, reset=True)
+      force_refresh_kwargs["cache_config"] = cache_config
+      if calibrator_config is not None:
+        force_refresh_kwargs["calibrator_config"] = calibrator_config
+    else:
+      extra = set(force_refresh_kwargs) - {"cache_config", "calibrator_config", "verbose"}
+      if extra:
+        logger.warning(f"force_refresh_kwargs contains cache_config, please put the extra kwargs: {extra} "
+                       "into cache_config directly. Otherwise, these kwargs will be ignored.")
   CachedAdapter.maybe_refresh_context(transformer, **force_refresh_kwargs)
 
 

@@ -5,7 +5,7 @@ import logging
 
 import torch
 
-from .config import ParallelismConfig
+from .config import ParallelismBackend, ParallelismConfig
 
 logger = logging.getLogger("cache_dit_b200")
 

@@ -15,7 +15,9 @@ What it does
   * TaylorSeer known-answer case.
 
 Outputs: tests/golden/cache_steps.json, tests/golden/cache_outputs.npz,
-         tests/golden/block_runs.json, tests/golden/block_outputs.npz, tests/golden/taylor_kat.json
+         tests/golden/block_runs.json, tests/golden/block_outputs.npz, tests/golden/taylor_kat.json,
+         tests/golden/host_tables.json, tests/golden/load_configs.json (tests/config_cases.py through the
+         reference's `load_cache_config` / `load_parallelism_config`)
 """
 from __future__ import annotations
 
@@ -188,9 +190,15 @@ def main():
   ap = argparse.ArgumentParser()
   ap.add_argument("--reference", required=True)
   ap.add_argument("--only", nargs="*", default=None)
+  ap.add_argument("--load-configs-only", action="store_true", help="write load_configs.json and nothing else")
   args = ap.parse_args()
   torch.set_num_threads(os.cpu_count() or 1)
   cache_dit = import_reference(args.reference)
+  from tests import config_cases
+  json.dump(config_cases.run_cases(cache_dit), open(os.path.join(HERE, "load_configs.json"), "w"), indent=1,
+            sort_keys=True)
+  if args.load_configs_only:
+    return
 
   steps_path = os.path.join(HERE, "cache_steps.json")
   out_path = os.path.join(HERE, "cache_outputs.npz")
