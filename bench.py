@@ -500,7 +500,17 @@ def cpu_baseline(sample_only=False, hits=None):
   import numpy as np
   from oracle import cache_oracle as O
   from oracle import fp8_oracle as F
-  torch.set_num_threads(os.cpu_count() or 1)
+  cores = os.cpu_count() or 1
+  torch.set_num_threads(cores)
+  # the launcher of multi-rank runs exports OMP_NUM_THREADS=1, which the BLAS under numpy reads at import:
+  # lift its pool back to all host cores for this arm, and report the threads it really has
+  try:
+    from threadpoolctl import threadpool_info, threadpool_limits
+    threadpool_limits(limits=cores)
+    blas = [p["num_threads"] for p in threadpool_info() if p.get("user_api") == "blas"]
+    cores = max(blas) if blas else cores
+  except ImportError:
+    cores = int(os.environ.get("OMP_NUM_THREADS", cores))
   rng = np.random.RandomState(0)
   S, C = 4608, 3072
   prev = O.round_bf16(rng.randn(1, S, C).astype(np.float32))
@@ -536,7 +546,7 @@ def cpu_baseline(sample_only=False, hits=None):
     hits = 14  # hit count of the reference's synthetic cache-step schedule (2 hits, 1 miss after warm-up)
   per_generation = (STEPS_PER_GENERATION - hits) * (computed + t_update) + hits * (cached + t_apply) \
       + (STEPS_PER_GENERATION - 8) * t_check
-  return {"value": STEPS_PER_GENERATION / per_generation, "unit": "steps/s", "cores": os.cpu_count(),
+  return {"value": STEPS_PER_GENERATION / per_generation, "unit": "steps/s", "cores": cores,
           "kind": "port",
           "sample": ("numpy restatement: cache check/update/apply at [1,4608,3072] bf16 + FP8 linears of one "
                      "double and one single block, extrapolated to 19+38 blocks and a 28-step schedule with the "
