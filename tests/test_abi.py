@@ -56,3 +56,36 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
   monkeypatch.setattr(_native, "LIB_PATH", str(tmp_path / "nope.so"))
   with pytest.raises(_native.NativeLibraryError):
     _native.lib()
+
+
+C_CONSUMER = r"""
+#include <stdio.h>
+#include "cache_dit_b200.h"
+int main(void) {
+  /* metadata and argument validation: no CUDA call is reached */
+  if (cdb_abi_version() < 1) return 2;
+  if (cdb_rel_l1(NULL, NULL, NULL, NULL, 0, 1, NULL, NULL, 0, NULL) != 1) return 3;
+  if (cdb_fp8_gemm_rowscaled(NULL, NULL, NULL, NULL, NULL, NULL, 1, 8, 16, 8, NULL, NULL) != 1) return 4;
+  printf("%s|%d\n", cdb_status_string(0), (int)cdb_rel_l1_scratch_bytes());
+  return 0;
+}
+"""
+
+
+def test_plain_c_program_includes_header_and_links(library, tmp_path):
+  """The boundary is C, not C++: a C99 translation unit includes the header with -pedantic, links the shared
+  library and calls it (what a cgo / JNI / FFI binding does)."""
+  import shutil
+  import subprocess
+  from cache_dit_b200 import _native
+  if shutil.which("gcc") is None:
+    pytest.skip("no gcc")
+  src = tmp_path / "consumer.c"
+  src.write_text(C_CONSUMER)
+  exe = tmp_path / "consumer"
+  libdir = os.path.dirname(_native.LIB_PATH)
+  subprocess.run(["gcc", "-std=c99", "-Wall", "-Wextra", "-Werror", "-pedantic", "-I", os.path.dirname(HEADER), str(src),
+                  "-o", str(exe), "-L", libdir, "-l:" + os.path.basename(_native.LIB_PATH), "-Wl,-rpath," + libdir],
+                 check=True, capture_output=True)
+  out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.strip()
+  assert out.split("|")[0] == "ok" and int(out.split("|")[1]) >= 16
