@@ -423,7 +423,8 @@ def run_ours(args):
     r.enabled = False
   stepper.i = STEPS_PER_GENERATION
   nat.gemm_timer = []
-  for _ in range(min(args.steps, STEPS_PER_GENERATION)):
+  instrumented_steps = min(args.steps, STEPS_PER_GENERATION)
+  for _ in range(instrumented_steps):
     stepper.step()
   torch.cuda.synchronize()
   records, nat.gemm_timer = nat.gemm_timer, None
@@ -472,6 +473,10 @@ def run_ours(args):
                  "peak_burst": round(fp8_lib[0], 1) if fp8_lib else None,
                  "frac_of_burst": round(achieved / fp8_lib[0], 3) if fp8_lib else None,
                  "frac_of_nominal_4500": round(achieved / FP8_NOMINAL_TFLOPS, 3), "launches": len(records),
+                 "avg_launch_us": round(1e3 * gemm_ms / max(len(records), 1), 2),
+                 # time inside these launches per step / the timed region's time per step (compare with the
+                 # kernel's share in the committed ncu launch list)
+                 "share_of_step": round((gemm_ms / max(instrumented_steps, 1)) / (ms / args.steps), 3),
                  "timing": "CUDA events around every GEMM launch in an instrumented repeat of the timed steps",
                  # dram__bytes_read + dram__bytes_write of one launch of the dominant shape class from the
                  # committed ncu capture (profiles/kernels_small_case_ncu_set_full.md): 52.1 MB + 67.9 MB for
