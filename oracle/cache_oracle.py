@@ -122,6 +122,30 @@ def rel_l1(prev: np.ndarray, cur: np.ndarray, dtype: str,
   return float(_scalar(q, dtype))
 
 
+def rel_l1_important_tokens(prev: np.ndarray, cur: np.ndarray, condition: float, dtype: str) -> float:
+  """The token-selective distance of cache_manager.py:588-606 (`important_condition_threshold > 0`).
+
+  Per token, mean|prev - cur| / mean|prev| over the channels; when any token exceeds `condition` the two
+  means of the relative L1 distance are taken over those tokens only, else over everything.
+  """
+  raw = np.abs(rnd(np.float32(prev) - np.float32(cur), dtype))
+  c = raw.shape[-1]
+  token_df = rnd(np.float32(np.sum(raw, axis=-1, dtype=np.float64) / c), dtype)
+  token_t1 = rnd(np.float32(np.sum(np.abs(prev), axis=-1, dtype=np.float64) / c), dtype)
+  with np.errstate(divide="ignore", invalid="ignore"):
+    token_diff = rnd(np.float32(token_df) / np.float32(token_t1), dtype)
+  chosen = token_diff > np.float32(condition)
+  if chosen.sum() > 0:
+    d, p = raw[chosen], np.abs(prev)[chosen]
+  else:
+    d, p = raw, np.abs(prev)
+  md = _scalar(np.float32(np.sum(d, dtype=np.float64) / d.size), dtype)
+  mp = _scalar(np.float32(np.sum(p, dtype=np.float64) / p.size), dtype)
+  with np.errstate(divide="ignore", invalid="ignore"):
+    q = np.float32(md) / np.float32(mp)
+  return float(_scalar(q, dtype))
+
+
 def taylor_series(derivs: Sequence[Optional[np.ndarray]], elapsed: int, dtype: str):
   """TaylorSeerState.approximate, taylorseer.py:91-104, with its per-op rounding.
 
@@ -255,10 +279,13 @@ class OracleContext:
   """Restates CachedContext + the CachedContextManager methods the block runner calls."""
 
   def __init__(self, cache_config: Optional[dict] = None, calibrator_config: Optional[dict] = None,
-               dtype: str = "fp32", shards: Optional[int] = None):
+               dtype: str = "fp32", shards: Optional[int] = None, extra_config: Optional[dict] = None):
     self._init = (copy.deepcopy(cache_config), copy.deepcopy(calibrator_config), dtype, shards)
     self.cfg = dict(DEFAULT_CACHE_CONFIG)
     self.cfg.update(cache_config or {})
+    # ExtraCacheConfig (cache_config.py:188-211): off by default
+    self.extra = dict(downsample_factor=1, important_condition_threshold=0.0)
+    self.extra.update(extra_config or {})
     self.cal = None
     if calibrator_config is not None:
       self.cal = dict(DEFAULT_CALIBRATOR_CONFIG)
@@ -317,7 +344,7 @@ class OracleContext:
               self.cfg_accumulated_cached_steps, self.accumulated_executed_steps,
               self.accumulated_transformer_executed_steps)
     cache_config, calibrator_config, dtype, shards = self._init
-    self.__init__(cache_config, calibrator_config, dtype, shards)
+    self.__init__(cache_config, calibrator_config, dtype, shards, dict(self.extra))
     if keep is not None:
       (self.cached_steps, self.cfg_cached_steps, self.residual_diffs, self.cfg_residual_diffs,
        self.accumulated_cached_steps, self.cfg_accumulated_cached_steps,
@@ -424,8 +451,10 @@ class OracleContext:
     return k + "_cfg" if self.is_cfg_step() else k
 
   def set_Fn_buffer(self, buf, prefix):
+    """cache_manager.py:641-657: with a down-sampling factor k only every k-th channel is kept."""
     if buf is not None:
-      self.buffers[self._key(prefix)] = buf
+      k = self.extra["downsample_factor"]
+      self.buffers[self._key(prefix)] = np.ascontiguousarray(buf[..., ::k]) if k > 1 else buf
 
   def get_Fn_buffer(self, prefix):
     return self.buffers.get(self._key(prefix))
@@ -475,6 +504,8 @@ class OracleContext:
     if (self.cfg["enable_separate_cfg"] and self.is_cfg_step()
         and not self.cfg["cfg_diff_compute_separate"] and step in self.residual_diffs):
       diff = self.residual_diffs[step]
+    elif self.extra["important_condition_threshold"] > 0.0:
+      diff = rel_l1_important_tokens(prev, cur, self.extra["important_condition_threshold"], self.dtype)
     else:
       diff = rel_l1(prev, cur, self.dtype, self.shards)
     self.add_residual_diff(diff)
@@ -511,6 +542,9 @@ class OracleContext:
       threshold = self.cfg["residual_diff_threshold"]
     if threshold <= 0.0:
       return False
+    k = self.extra["downsample_factor"]
+    if k > 1 and "Bn" not in prefix:  # cache_manager.py:937-940
+      states = np.ascontiguousarray(states[..., ::k])
     prev = self.get_Bn_buffer(prefix) if "Bn" in prefix else self.get_Fn_buffer(prefix)
     return prev is not None and self.similarity(prev, states, threshold)
 

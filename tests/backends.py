@@ -27,7 +27,8 @@ def stats_dict(cached_steps, residual_diffs, cfg_cached_steps, cfg_residual_diff
 class OracleBackend:
 
   def __init__(self, sc: dict, shards=None):
-    self.ctx = O.OracleContext(sc["cache_config"], sc["calibrator_config"], sc["dtype"], shards)
+    self.ctx = O.OracleContext(sc["cache_config"], sc["calibrator_config"], sc["dtype"], shards,
+                               sc.get("extra_config"))
 
   def _p(self, encoder=False):
     kind = "residual" if self.ctx.is_cache_residual(encoder) else "hidden_states"
@@ -86,8 +87,9 @@ class ProductBackend:
     self.device = device
     self.parallelized = parallelized
     self.mgr = cd.CachedContextManager("scenario", persistent_context=True)
+    extra = {"extra_cache_config": cd.ExtraCacheConfig(**sc["extra_config"])} if sc.get("extra_config") else {}
     self.mgr.new_context(name="ctx", cache_config=cd.DBCacheConfig(**cc),
-                         calibrator_config=None if cal is None else cd.TaylorSeerCalibratorConfig(**cal))
+                         calibrator_config=None if cal is None else cd.TaylorSeerCalibratorConfig(**cal), **extra)
 
   def _p(self, encoder=False):
     res = self.mgr.is_encoder_cache_residual() if encoder else self.mgr.is_cache_residual()

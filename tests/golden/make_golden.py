@@ -88,9 +88,13 @@ class ReferenceBackend:
     cc.setdefault("enable_separate_cfg", False)
     cal = sc["calibrator_config"]
     self.mgr = CachedContextManager("golden", persistent_context=True)
+    extra = {}
+    if sc.get("extra_config"):
+      from cache_dit.caching.cache_contexts.cache_config import ExtraCacheConfig
+      extra["extra_cache_config"] = ExtraCacheConfig(**sc["extra_config"])
     self.mgr.new_context(
       name="ctx", cache_config=DBCacheConfig(**cc),
-      calibrator_config=None if cal is None else TaylorSeerCalibratorConfig(**cal))
+      calibrator_config=None if cal is None else TaylorSeerCalibratorConfig(**cal), **extra)
 
   def _p(self, encoder=False):
     res = self.mgr.is_encoder_cache_residual() if encoder else self.mgr.is_cache_residual()

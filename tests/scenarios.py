@@ -104,6 +104,32 @@ SCENARIOS: List[dict] = [
   dict(name="force_refresh_hint", shape=(1, 16, 32), enc_shape=None, dtype="fp32", steps=20,
        seed=20, noise=0.03, cache_config=dict(max_warmup_steps=2, force_refresh_step_hint=10),
        calibrator_config=dict(taylorseer_order=1), full_outputs=True),
+  dict(name="force_refresh_repeat", shape=(1, 16, 32), enc_shape=None, dtype="fp32", steps=24,
+       seed=21, noise=0.03,
+       cache_config=dict(max_warmup_steps=2, force_refresh_step_hint=7, force_refresh_step_policy="repeat"),
+       calibrator_config=dict(taylorseer_order=1), full_outputs=True),
+  dict(name="separate_cfg_first", shape=(1, 16, 32), enc_shape=(1, 3, 32), dtype="fp32", steps=14,
+       seed=22, noise=0.03,
+       cache_config=dict(max_warmup_steps=2, enable_separate_cfg=True, cfg_compute_first=True,
+                         cfg_diff_compute_separate=False),
+       calibrator_config=dict(taylorseer_order=1), full_outputs=True),
+  # The highest order the kernels take.
+  dict(name="small_bf16_o4", shape=(1, 21, 64), enc_shape=(1, 4, 64), dtype="bf16", steps=26, seed=23,
+       noise=0.02, cache_config=dict(max_warmup_steps=6), calibrator_config=dict(taylorseer_order=4),
+       full_outputs=True),
+  # Extra options of the similarity check (off by default): channel sub-sampling of the indicator and
+  # the token-selective distance.
+  dict(name="extra_downsample", shape=(1, 16, 32), enc_shape=None, dtype="fp32", steps=20, seed=24,
+       noise=0.03, cache_config=dict(max_warmup_steps=2), extra_config=dict(downsample_factor=4),
+       calibrator_config=dict(taylorseer_order=1), full_outputs=True),
+  dict(name="extra_important_tokens", shape=(2, 16, 32), enc_shape=None, dtype="fp32", steps=20, seed=25,
+       noise=0.03, cache_config=dict(max_warmup_steps=2, residual_diff_threshold=0.1),
+       extra_config=dict(important_condition_threshold=0.06),
+       calibrator_config=dict(taylorseer_order=1), full_outputs=True),
+  dict(name="extra_important_tokens_none_chosen", shape=(1, 16, 32), enc_shape=None, dtype="fp32", steps=12,
+       seed=26, noise=0.01, cache_config=dict(max_warmup_steps=2),
+       extra_config=dict(important_condition_threshold=0.9),
+       calibrator_config=dict(taylorseer_order=1), full_outputs=True),
 ]
 
 BY_NAME: Dict[str, dict] = {s["name"]: s for s in SCENARIOS}
