@@ -292,7 +292,8 @@ def _graph_us(fn, n=4, reps=5):
 def fp8_linear_sweep(device):
   """The FP8 w8a8 per-token linear on the sweep shapes (activations N(0,1) with 0.1 % outliers x20,
   weights N(0, 0.02) quantized per output row): TFLOP/s of the whole linear (activation quantization
-  + GEMM), of the GEMM alone, and of the library's row-wise `torch._scaled_mm` on the same operands."""
+  + GEMM), of the GEMM alone without and with a bias, and of the library's row-wise `torch._scaled_mm` on the
+  same operands."""
   from cache_dit_b200 import _native as nat
   out = {}
   g = torch.Generator(device=device).manual_seed(0)
@@ -315,7 +316,10 @@ def fp8_linear_sweep(device):
       flops = 2.0 * M * N * K
       t_lin = _graph_us(linear)
       t_gemm = _graph_us(lambda: nat.fp8_gemm_rowscaled(aq, sa, wq, sw, None, y))
-      entry = {"linear_tflops": round(flops / t_lin / 1e6, 1), "gemm_tflops": round(flops / t_gemm / 1e6, 1)}
+      bias = (0.1 * torch.randn(N, device=device, generator=g)).to(torch.bfloat16)
+      t_bias = _graph_us(lambda: nat.fp8_gemm_rowscaled(aq, sa, wq, sw, bias, y))
+      entry = {"linear_tflops": round(flops / t_lin / 1e6, 1), "gemm_tflops": round(flops / t_gemm / 1e6, 1),
+               "gemm_with_bias_tflops": round(flops / t_bias / 1e6, 1)}
       try:
         sa2, sw2 = sa.view(M, 1), sw.view(1, N)
         t_lib = _graph_us(lambda: torch._scaled_mm(aq, wq.t(), scale_a=sa2, scale_b=sw2, out_dtype=torch.bfloat16))
