@@ -3,7 +3,6 @@ logic (state machine, adapters, block runner).  It is installed with
 `cache_dit_b200.caching.step_ops.set_ops` by a fixture and never ships."""
 from __future__ import annotations
 
-import math
 
 import numpy as np
 import torch

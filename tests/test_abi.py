@@ -1,5 +1,4 @@
 """The C-ABI library loads without a GPU and exports every symbol the header declares."""
-import ctypes
 import os
 import re
 
