@@ -109,12 +109,21 @@ def wan_case(rank, world):
   return _sharded_vs_single(world, build, WanDenoisePipeline, 0.3)
 
 
+def config_case(rank, world):
+  """A configuration dictionary with `ulysses_size: auto` resolves to the number of ranks."""
+  loaded = cd.load_configs({"cache_config": {"Fn_compute_blocks": 1, "enable_taylorseer": True},
+                            "parallelism_config": {"ulysses_size": "auto", "ulysses_anything": True}})
+  p = loaded["parallelism_config"]
+  return dict(ulysses_size=p.ulysses_size, anything=bool(p.ulysses_anything), backend=str(p.backend),
+              exchange=p.exchange_mode(), order=loaded["calibrator_config"].taylorseer_order)
+
+
 def main():
   dist.init_process_group("gloo")
   rank, world = dist.get_rank(), dist.get_world_size()
   step_ops.set_ops(OracleStepOps())
   result = dict(rank=rank, decision=decision_case(rank, world), flux=flux_case(rank, world),
-                qwen=qwen_case(rank, world), wan=wan_case(rank, world))
+                qwen=qwen_case(rank, world), wan=wan_case(rank, world), config=config_case(rank, world))
   with open(os.path.join(sys.argv[1], f"rank{rank}.json"), "w") as f:
     json.dump(result, f)
   dist.barrier()

@@ -55,3 +55,8 @@ def test_other_model_plans_match_single_rank(results, model):
       # the shard-size imbalance (1 token in 25) times the spread of per-token means otherwise
       assert abs(f["diffs_sharded"][k] - v) <= 2e-2 * abs(v) + 1e-9
   assert results[0][model]["cached_sharded"] == results[1][model]["cached_sharded"]
+
+
+def test_auto_parallel_size_is_the_world_size(results):
+  for r in results:
+    assert r["config"] == dict(ulysses_size=2, anything=True, backend="CACHE_DIT", exchange="nccl", order=1)
