@@ -210,16 +210,67 @@ def fp8_quant_rows(x2d, q, scale, preop=PRE_NONE, mod_shift=None, mod_scale=None
   check(st, "cdb_fp8_quant_rows")
 
 
-_status_words = {}
+# One 32-byte "mailbox" per device holds everything the host reads back once per step, so that a single
+# small device-to-host copy carries the two means of the relative-L1 check AND the latched status of
+# every bounded device-side wait:
+#   int32 words  [0:2] the two float32 means   [2] GEMM status word   [4:6] PeerSync {epoch, status}
+_mailboxes = {}
+MAILBOX_WORDS = 8
+MAILBOX_GEMM_STATUS = 2
+MAILBOX_PEER_STATUS = 5
+_peer_sync_claimed = set()
+
+
+class DeviceTimeoutError(RuntimeError):
+  """A bounded wait inside a kernel ran out (CDB_ERR_DEVICE_TIMEOUT): results after it are not valid."""
+
+
+def _device_index(device) -> int:
+  return device.index if device.index is not None else torch.cuda.current_device()
+
+
+def device_mailbox(device) -> torch.Tensor:
+  idx = _device_index(device)
+  box = _mailboxes.get(idx)
+  if box is None:
+    box = torch.zeros(MAILBOX_WORDS, dtype=torch.int32, device=device)
+    _mailboxes[idx] = box
+  return box
+
+
+def mailbox_means(device) -> torch.Tensor:
+  """float32[2] view of the mailbox: where `rel_l1` leaves the two local means."""
+  return device_mailbox(device)[0:2].view(torch.float32)
 
 
 def gemm_status_word(device) -> torch.Tensor:
-  idx = device.index if device.index is not None else torch.cuda.current_device()
-  w = _status_words.get(idx)
-  if w is None:
-    w = torch.zeros(1, dtype=torch.int32, device=device)
-    _status_words[idx] = w
-  return w
+  return device_mailbox(device)[MAILBOX_GEMM_STATUS:MAILBOX_GEMM_STATUS + 1]
+
+
+def claim_peer_sync(device):
+  """The mailbox's PeerSync words for the first exchange object of a device (its latched status then
+  travels with the per-step copy); None when they are taken (further exchanges keep their own)."""
+  idx = _device_index(device)
+  if idx in _peer_sync_claimed:
+    return None
+  _peer_sync_claimed.add(idx)
+  sync = device_mailbox(device)[4:6]
+  sync.zero_()
+  return sync
+
+
+def release_peer_sync(device):
+  _peer_sync_claimed.discard(_device_index(device))
+
+
+def raise_on_device_status(gemm_status: int, peer_status: int):
+  """Turn the latched status words (host copies) into the C ABI's CDB_ERR_DEVICE_TIMEOUT as an exception."""
+  if gemm_status != 0:
+    raise DeviceTimeoutError(f"CDB_ERR_DEVICE_TIMEOUT: a bounded wait inside the FP8 GEMM ran out (code {gemm_status}); "
+                             "the products launched since are incomplete")
+  if peer_status != 0:
+    raise DeviceTimeoutError(f"CDB_ERR_DEVICE_TIMEOUT: the signal of peer {peer_status - 1} did not arrive within the "
+                             "timeout of the head/token exchange; later blocks ran unsynchronised")
 
 
 def fp8_gemm_rowscaled(a_q, a_scale, w_q, w_scale, bias, out):
@@ -252,6 +303,12 @@ def fp8_gemm_rowscaled(a_q, a_scale, w_q, w_scale, bias, out):
 def gemm_device_status(device) -> int:
   """Non-zero if a bounded wait inside the GEMM kernel expired since the last reset (syncs)."""
   return int(gemm_status_word(device).item())
+
+
+def check_device_status(device):
+  """Read the device's latched status words now (synchronises) and raise DeviceTimeoutError if one is set."""
+  host = device_mailbox(device).cpu()
+  raise_on_device_status(int(host[MAILBOX_GEMM_STATUS]), int(host[MAILBOX_PEER_STATUS]))
 
 
 def qk_norm_rope(x, norm_weight, cos, sin, out, pos_offset: int, heads: int, eps: float):

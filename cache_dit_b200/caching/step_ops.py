@@ -51,18 +51,16 @@ class DeviceStepOps:
   name = "sm_100a"
 
   def __init__(self):
-    self._means = {}   # device index -> float32[2] device tensor
-    self._pinned = {}  # device index -> float32[2] pinned host tensor
+    self._pinned = {}  # device index -> int32[8] pinned host image of the device's mailbox
 
   # ---- buffers ---------------------------------------------------------------------------
   def _means_buffer(self, device: torch.device) -> torch.Tensor:
+    """The two float32 means live in the device's mailbox (`_native.device_mailbox`), next to the latched
+    status words of the bounded device-side waits, so that one copy brings all of them to the host."""
     idx = device.index if device.index is not None else torch.cuda.current_device()
-    buf = self._means.get(idx)
-    if buf is None:
-      buf = torch.zeros(2, dtype=torch.float32, device=device)
-      self._means[idx] = buf
-      self._pinned[idx] = torch.zeros(2, dtype=torch.float32).pin_memory()
-    return buf
+    if idx not in self._pinned:
+      self._pinned[idx] = torch.zeros(_native.MAILBOX_WORDS, dtype=torch.int32).pin_memory()
+    return _native.mailbox_means(device)
 
   def empty_like(self, t: torch.Tensor) -> torch.Tensor:
     return torch.empty(t.shape, dtype=t.dtype, device=t.device)
@@ -77,7 +75,8 @@ class DeviceStepOps:
                    residual_out: Optional[torch.Tensor], group=None) -> Tuple[float, float, int]:
     """One fused pass, then the single host synchronisation of the step.
 
-    Returns (mean|prev - r|, mean|prev|, world) where r = cur - base (or cur); with a process
+    Raises `_native.DeviceTimeoutError` if a bounded wait of an earlier kernel (FP8 GEMM pipeline, peer
+    exchange) ran out.  Returns (mean|prev - r|, mean|prev|, world) where r = cur - base (or cur); with a process
     group the two local means are summed over the ranks by ONE all-reduce of two float32 and
     `world` is the number of ranks (the caller divides and rounds like ReduceOp.AVG would,
     src/cache_dit/caching/cache_contexts/cache_manager.py:612-614)."""
@@ -91,9 +90,13 @@ class DeviceStepOps:
         dist.all_reduce(means, op=dist.ReduceOp.SUM, group=group if group is not True else None)
     idx = cur.device.index if cur.device.index is not None else torch.cuda.current_device()
     host = self._pinned[idx]
-    host.copy_(means, non_blocking=True)
+    host.copy_(_native.device_mailbox(cur.device), non_blocking=True)
     torch.cuda.current_stream(cur.device).synchronize()
-    return float(host[0]), float(host[1]), world
+    # the same 32 bytes carry the status words: a wait that ran out since the last step invalidates what
+    # was computed after it, so the step fails here instead of producing silently wrong latents
+    _native.raise_on_device_status(int(host[_native.MAILBOX_GEMM_STATUS]), int(host[_native.MAILBOX_PEER_STATUS]))
+    m = host[0:2].view(torch.float32)
+    return float(m[0]), float(m[1]), world
 
   # ---- Taylor ------------------------------------------------------------------------------
   def taylor_apply(self, hidden: Optional[torch.Tensor], derivs: Sequence[torch.Tensor],

@@ -171,7 +171,8 @@ static int launch_rel_l1_variant(const typename A::T* c, const typename A::T* b,
                                  typename A::T* r, int64_t n, float* means, RelL1Scratch* scratch,
                                  cudaStream_t st) {
   auto kernel = rel_l1_kernel<A, A1, U, HB, HP, WR>;
-  static const int64_t wave = resident_ctas(kernel, RL_THREADS);
+  static PerDevice wave_of;
+  const int64_t wave = wave_of.get([&] { return resident_ctas(kernel, RL_THREADS); });
   const int64_t nchunk = n / (U * A::N);
   int64_t want = (nchunk + (int64_t)RL_THREADS * RL_UNROLL - 1) / ((int64_t)RL_THREADS * RL_UNROLL);
   int64_t cap = wave < RL_MAX_CLUSTERS * RL_CLUSTER ? wave : RL_MAX_CLUSTERS * RL_CLUSTER;
@@ -317,7 +318,8 @@ template <class A, class A1, int U, int TERMS, bool ADD, bool EX>
 static void launch_apply_variant(const typename A::T* h, const ApplyArgs& a, typename A::T* o, int64_t n,
                                  cudaStream_t st) {
   auto kernel = taylor_apply_kernel<A, A1, U, TERMS, ADD, EX>;
-  static const int64_t wave = resident_ctas(kernel, EW_THREADS);
+  static PerDevice wave_of;
+  const int64_t wave = wave_of.get([&] { return resident_ctas(kernel, EW_THREADS); });
   const int64_t nchunk = n / (U * A::N);
   int64_t want = (nchunk + (int64_t)EW_THREADS * EW_UNROLL - 1) / ((int64_t)EW_THREADS * EW_UNROLL);
   int64_t g = want < wave ? want : wave;
@@ -350,7 +352,8 @@ template <class A, class A1, int U, int NEW, bool HB, bool WY, bool P2>
 static void launch_update_variant(const typename A::T* af, const typename A::T* bf, const UpdateArgs& a,
                                   float window, int64_t n, cudaStream_t st) {
   auto kernel = taylor_update_kernel<A, A1, U, NEW, HB, WY, P2>;
-  static const int64_t wave = resident_ctas(kernel, EW_THREADS);
+  static PerDevice wave_of;
+  const int64_t wave = wave_of.get([&] { return resident_ctas(kernel, EW_THREADS); });
   const int64_t nchunk = n / (U * A::N);
   int64_t want = (nchunk + (int64_t)EW_THREADS * EW_UNROLL - 1) / ((int64_t)EW_THREADS * EW_UNROLL);
   int64_t g = want < wave ? want : wave;
@@ -524,6 +527,18 @@ extern "C" int cdb_rel_l1_static(const void* cur, const void* base, const void* 
     cdb::set_error_text("cdb_rel_l1_static: n exceeds CDB_REL_L1_STATIC_MAX_ELEMS (2^30 elements); "
                         "use cdb_rel_l1 with caller-provided scratch for larger tensors");
     return CDB_ERR_TOO_LARGE;
+  }
+  // The array's address is per device and is looked up for the CURRENT device, so the tensors must live
+  // there too: with another device current the kernel would be handed that device's copy of the array.
+  cudaPointerAttributes attr{};
+  int cur_dev = -1;
+  CDB_CUDA_CHECK(cudaGetDevice(&cur_dev));
+  if (cudaPointerGetAttributes(&attr, cur) != cudaSuccess || attr.type != cudaMemoryTypeDevice ||
+      attr.device != cur_dev) {
+    (void)cudaGetLastError();
+    cdb::set_error_text("cdb_rel_l1_static: `cur` is not device memory of the current device; make the "
+                        "device that owns the tensors current before the call");
+    return CDB_ERR_BAD_ARGUMENT;
   }
   RelL1Scratch* sc = nullptr;
   int rc = static_scratch_for_current_device(&sc);

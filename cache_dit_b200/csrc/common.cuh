@@ -27,6 +27,25 @@ void set_error_text(const char* text);
 // Number of SMs of the current device (cached per device).
 int sm_count();
 
+// A value that depends on the device (occupancy, whether a one-time attribute was set), cached per
+// device index: function attributes and occupancy belong to the device that is current at the call, so a
+// process that drives several GPUs must not reuse what it learnt on the first one.
+struct PerDevice {
+  static constexpr int kMax = 64;
+  int64_t value[kMax] = {};
+  bool known[kMax] = {};
+  template <class F>
+  int64_t get(F&& compute) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMax) return compute();
+    if (!known[dev]) {  // concurrent first calls compute the same value twice: harmless
+      value[dev] = compute();
+      known[dev] = true;
+    }
+    return value[dev];
+  }
+};
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // ---- storage-dtype arithmetic policies ------------------------------------------------------

@@ -980,19 +980,22 @@ extern "C" int cdb_fp8_gemm_rowscaled_grouped(const void* problems_v, int count,
   }
   if (n == 0) return CDB_OK;
   if (n == 2 && g[1].M > g[0].M) std::swap(g[0], g[1]);
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  static int mode = 0;  // 0 = choose by shape, 1 = single-CTA kernel, 2 = CTA-pair kernel
-  std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(fp8_gemm_rowscaled_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    SMEM_TOTAL_BYTES);
-    if (attr_err == cudaSuccess)
-      attr_err = cudaFuncSetAttribute(fp8_gemm_rowscaled_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      P_SMEM_TOTAL_BYTES);
-    const char* env = getenv("CDB_GEMM_KERNEL");  // tuning / testing knob: "1cta" | "2cta"
-    if (env && strcmp(env, "1cta") == 0) mode = 1;
-    if (env && strcmp(env, "2cta") == 0) mode = 2;
+  // The opt-in to more than 48 KB of dynamic shared memory is a per-device function attribute.
+  static PerDevice attr_state;
+  const cudaError_t attr_err = (cudaError_t)attr_state.get([]() -> int64_t {
+    cudaError_t e = cudaFuncSetAttribute(fp8_gemm_rowscaled_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         SMEM_TOTAL_BYTES);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(fp8_gemm_rowscaled_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               P_SMEM_TOTAL_BYTES);
+    return (int64_t)e;
   });
+  static const int mode = [] {  // 0 = choose by shape, 1 = single-CTA kernel, 2 = CTA-pair kernel
+    const char* env = getenv("CDB_GEMM_KERNEL");  // tuning / testing knob: "1cta" | "2cta"
+    if (env && strcmp(env, "1cta") == 0) return 1;
+    if (env && strcmp(env, "2cta") == 0) return 2;
+    return 0;
+  }();
   CDB_CUDA_CHECK(attr_err);
   const int sms = sm_count();
   cudaStream_t st = static_cast<cudaStream_t>(stream);

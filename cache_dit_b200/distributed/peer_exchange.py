@@ -61,7 +61,15 @@ class PeerExchange:
     self.ptrs: Dict[str, List[int]] = {}
     flags_ptr, self.flag_ptrs = self._alloc_shared(256)
     self.flags = _as_tensor(flags_ptr, (64, ), torch.int32, self.device)
-    self.sync = torch.zeros(_native.lib().cdb_peer_sync_bytes() // 4, dtype=torch.int32, device=self.device)
+    # {epoch, status}: the first exchange of a device keeps them in the device's mailbox, so that the status
+    # a run-out wait latches reaches the host with the per-step copy of the cache decision
+    # (`DeviceStepOps.rel_l1_means` raises on it); further exchanges on one device keep words of their own
+    assert _native.lib().cdb_peer_sync_bytes() == 8
+    self._mailbox_sync = True
+    self.sync = _native.claim_peer_sync(self.device)
+    if self.sync is None:
+      self._mailbox_sync = False
+      self.sync = torch.zeros(2, dtype=torch.int32, device=self.device)
 
   # ---- collective allocation
   def _alloc_shared(self, nbytes: int) -> Tuple[int, List[int]]:
@@ -190,3 +198,7 @@ class PeerExchange:
       _native.peer_free(p)
     self._owned.clear()
     self.buffers.clear()
+    if self._mailbox_sync:
+      self.sync.zero_()  # a latched status belongs to this exchange, not to whatever runs on the device next
+      _native.release_peer_sync(self.device)
+      self._mailbox_sync = False

@@ -149,13 +149,31 @@ class FusedFloat8Linears(torch.nn.Module):
     return out.split(self.splits, dim=-1)
 
 
+def _members_share_storage(fused: FusedFloat8Linears, linears) -> bool:
+  """True while every member's weight still is the slice of the fused tensors it was made to be."""
+  w = fused.weight_q
+  row = 0
+  for l, n in zip(linears, fused.splits):
+    m = l.weight_q
+    if m.device != w.device or m.data_ptr() != w.data_ptr() + row * fused.in_features or m.shape[0] != n:
+      return False
+    if l.weight_scale.data_ptr() != fused.weight_scale.data_ptr() + row * 4:
+      return False
+    row += n
+  return True
+
+
 def fused_group(linears) -> FusedFloat8Linears:
-  """The fused module of a group of FP8 linears, built on first use and cached on the first member."""
+  """The fused module of a group of FP8 linears, built on first use and cached on the first member.
+
+  The cache is not a registered submodule, so `model.to(...)` or anything else that replaces the members'
+  buffers leaves it behind; the members are the truth then, and the group is rebuilt from them as soon
+  as their storage is no longer the fused one (a pointer comparison per member and call)."""
   head = linears[0]
   key = tuple(id(l) for l in linears)
   cache = head.__dict__.setdefault("_fused_groups", {})
   fused = cache.get(key)
-  if fused is None:
+  if fused is None or not _members_share_storage(fused, linears):
     fused = FusedFloat8Linears(list(linears))
     cache[key] = fused
   return fused

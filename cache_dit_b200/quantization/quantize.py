@@ -63,7 +63,10 @@ def quantize(module: torch.nn.Module, quantize_config: QuantizeConfig = None, **
     for name, sub in list(module.named_modules()):
       if sub.__class__.__name__ in repeated:
         hit = True
-        quantized += _swap_linears(sub, name, quantize_config, skipped)
+        # names are relative to the repeated block ("attn.to_q", not "transformer_blocks.1.attn.to_q"): the
+        # reference quantizes block by block, so `exclude_layers` patterns and a custom `filter_fn(m, name)`
+        # see block-relative names there (quantize_ao.py:128-131, 666-720) and must see the same here
+        quantized += _swap_linears(sub, "", quantize_config, skipped)
     if not hit:
       raise ValueError(f"Regional quantization failed because {repeated} classes are not found in the module.")
   else:

@@ -77,7 +77,10 @@ CDB_API int cdb_rel_l1(const void* cur, const void* base, const void* prev, void
  *
  * Same arithmetic and outputs as cdb_rel_l1 with `prev` given (means[0], means[1], optional
  * residual_out); the reduction scratch is a fixed array inside the library's device image
- * (32 bytes per GPU that loads the library, held until the process exits).
+ * (cdb_rel_l1_scratch_bytes() = 2176 bytes per GPU that loads the library, held until the process exits).
+ *   - The device that owns the tensors must be the current device of the calling thread: the array
+ *     exists once per device and the current device's copy is used.  A `cur` that is not device memory
+ *     of the current device returns CDB_ERR_BAD_ARGUMENT.
  *   - n may not exceed CDB_REL_L1_STATIC_MAX_ELEMS; larger calls return CDB_ERR_TOO_LARGE and the
  *     reason is available from cdb_last_cuda_error().
  *   - The first call on each device looks up the array's device address (with that device

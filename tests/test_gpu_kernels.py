@@ -442,3 +442,31 @@ def test_fp8_quant_pair_equals_separate_launches(nat, preop):
   for job, (q, s) in zip(jobs, want):
     assert torch.equal(job["scale"], s)
     assert torch.equal(job["q"].view(torch.uint8), q.view(torch.uint8))
+
+
+def test_fused_linear_group_follows_its_members_when_they_move():
+  """q/k/v run as one product over concatenated weights that the member layers view.  Moving the model
+  (here: to the CPU and back, which gives the members fresh buffers) must not leave the group computing
+  with the weights it cached before the move."""
+  from cache_dit_b200.quantization.linear import Float8RowwiseLinear, fused_group
+  torch.manual_seed(3)
+  dev = torch.device("cuda")
+  holder = torch.nn.Module()
+  holder.lins = torch.nn.ModuleList(
+    [Float8RowwiseLinear.from_linear(torch.nn.Linear(256, 128).to(torch.bfloat16).to(dev)) for _ in range(3)])
+  x = torch.randn(64, 256, device=dev).to(torch.bfloat16)
+  a_q, a_scale = holder.lins[0].quantize_input(x)
+  separate = [l.forward_quantized(a_q, a_scale, (64, )).clone() for l in holder.lins]
+  first = fused_group(list(holder.lins))
+  outs = first.forward_quantized(a_q, a_scale, (64, ))
+  assert all(torch.equal(o, s) for o, s in zip(outs, separate))
+  assert fused_group(list(holder.lins)) is first  # cached while the members still view its storage
+  holder.to("cpu")
+  holder.to(dev)
+  with torch.no_grad():  # the moved copies are independent now: change one to prove which weights are used
+    holder.lins[1].weight_scale.mul_(2.0)
+  second = fused_group(list(holder.lins))
+  assert second is not first
+  outs = second.forward_quantized(a_q, a_scale, (64, ))
+  separate = [l.forward_quantized(a_q, a_scale, (64, )) for l in holder.lins]
+  assert all(torch.equal(o, s) for o, s in zip(outs, separate))

@@ -111,6 +111,34 @@ def test_flag_protocol_and_bounded_wait(nat):
   assert t0.elapsed_time(t1) < 100.0
 
 
+def test_run_out_wait_reaches_the_host_with_the_step_copy(nat):
+  """The first exchange of a device keeps its {epoch, status} words in the device's mailbox: when a wait
+  runs out (a flag that nothing sets, 20 ms), the next cache check's one small device-to-host copy carries
+  the latched status and the step raises instead of returning means computed on unsynchronised data."""
+  from cache_dit_b200.caching.step_ops import DeviceStepOps
+  dev = torch.device("cuda", torch.cuda.current_device())
+  sync = nat.claim_peer_sync(dev)
+  assert sync is not None, "another exchange still holds the device's mailbox words"
+  try:
+    ops = DeviceStepOps()
+    a = torch.randn(1, 64, 256, device=dev).bfloat16()
+    b = torch.randn(1, 64, 256, device=dev).bfloat16()
+    md, mp, world = ops.rel_l1_means(a, None, b, None)  # nothing latched: the check works
+    assert md > 0 and mp > 0 and world == 1
+    flags = torch.zeros(64, dtype=torch.int32, device=dev)
+    other = torch.zeros(64, dtype=torch.int32, device=dev)
+    nat.peer_signal([flags.data_ptr(), other.data_ptr()], 0, sync, flags)  # rank 1 never signals
+    nat.peer_wait(flags, 2, sync, 20_000_000)
+    with pytest.raises(nat.DeviceTimeoutError, match="peer 1"):
+      ops.rel_l1_means(a, None, b, None)
+    with pytest.raises(nat.DeviceTimeoutError):
+      nat.check_device_status(dev)
+  finally:
+    sync.zero_()
+    nat.release_peer_sync(dev)
+  nat.check_device_status(dev)  # clean again for whatever runs next
+
+
 def _bf16(a):
   import numpy as np
   return torch.from_numpy(np.asarray(a, dtype=np.float32)).to(torch.bfloat16).float().numpy()

@@ -51,3 +51,17 @@ def test_there_is_no_cpu_implementation():
   a = torch.zeros(2, 16, dtype=torch.float8_e4m3fn)
   with pytest.raises(NotImplementedError):
     ops.float8_inference_scaled_mm(a, torch.ones(2, 1), a.t(), torch.ones(1, 2))
+
+
+def test_latched_device_status_becomes_an_exception():
+  """The host image of the per-device mailbox: word 2 = FP8 GEMM status, word 5 = peer-exchange status.
+  Either non-zero value must stop the step (CDB_ERR_DEVICE_TIMEOUT), zero must not."""
+  import pytest
+  from cache_dit_b200 import _native as nat
+  nat.raise_on_device_status(0, 0)
+  with pytest.raises(nat.DeviceTimeoutError, match="FP8 GEMM"):
+    nat.raise_on_device_status(13, 0)
+  with pytest.raises(nat.DeviceTimeoutError, match="peer 2"):
+    nat.raise_on_device_status(0, 3)
+  assert issubclass(nat.DeviceTimeoutError, RuntimeError)
+  assert nat.MAILBOX_GEMM_STATUS == 2 and nat.MAILBOX_PEER_STATUS == 5 and nat.MAILBOX_WORDS * 4 == 32
