@@ -1,25 +1,34 @@
-"""Benchmark of the per-step DiT hot path: FLUX-shape 1024x1024 denoising steps per second.
+"""Benchmark of the per-step DiT hot path: denoising steps per second through `cache_dit_b200.enable_cache`.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config flux|qwen_image|wan]
 
-Workload (BASELINE config 3): random-init FLUX.1-dev-architecture DiT (19 double + 38 single stream
-blocks, hidden 3072, 24 heads x 128), 4096 image + 512 text tokens, 28-step schedule, DBCache F8B0
-rdt 0.08 + TaylorSeer order 1, FP8 w8a8 linears, bf16 activations.  A "step" is one denoising step
-(one transformer call through `cache_dit_b200.enable_cache`); steps are taken from consecutive
-28-step generations, each started with `refresh_context`.
+Workloads (random-init stand-ins of the stated shapes, seeded N(0,1) inputs; no weights, prompts or datasets):
+  flux        FLUX.1-dev shape: 19 double + 38 single stream blocks, hidden 3072, 24 heads x 128, 4096 image +
+              512 text tokens, 28 steps, DBCache F8B0 rdt 0.08 + TaylorSeer order 1, FP8 w8a8 linears.  The
+              default, and the workload of the headline metric on one GPU.
+  qwen_image  Qwen-Image shape: 60 dual-stream blocks, hidden 3072, 6889 image + 256 text tokens (uneven token
+              shards under context parallelism), 50 steps, F8B0 rdt 0.12, separate classifier-free-guidance call.
+  wan         Wan2.1-14B shape: 40 blocks, hidden 5120, 40 heads, FFN 13824, 75600 video + 512 text tokens,
+              40 steps, F1B0 rdt 0.08 + TaylorSeer order 1, separate classifier-free-guidance call.
+A "step" is one denoising step (one transformer call, two with a separate guidance call); steps are taken from
+consecutive generations, each started with `refresh_context`.
 
-For N > 1 (torchrun, one rank per GPU) the sequence is sharded by Ulysses context parallelism
-(head / token exchange by stores into peer memory on one node): total work is fixed, so scaling is
-"strong".  The block segments between the cache decisions replay as CUDA graphs unless --no-graphs.
+For N > 1 (torchrun, one rank per GPU) the sequence is sharded by Ulysses context parallelism (head / token
+exchange by stores into peer memory on one node): total work is fixed, so scaling is "strong".  The block
+segments between the cache decisions replay as CUDA graphs unless --no-graphs.
 Prints ONE JSON line on rank 0:
   value / e2e ........ steps/s with inputs resident in HBM / with per-step host<->device copies
-  roofline ........... every FP8 product of the timed steps (CUDA events, eager repeat) against the
-                       library's sustained FP8 rate measured in the same run
-  roofline_cache_kernels, fp8_linear_sweep, cpu_baseline ... the other two parts of the metric
-                       (cache-check HBM GB/s, FP8 linear TFLOP/s) and the host-core baseline
+  config.hit_mask .... hit (1) / miss (0) of every timed step, checked against the committed single-GPU mask
+  checks ............. latched device status words (FP8 GEMM pipeline waits, peer-exchange waits), finite latents
+  parity (N > 1) ..... one generation with the peer exchange against one with NCCL all-to-all (eager): masks, latents
+  roofline ........... every FP8 product of the timed steps (CUDA events, eager repeat)
+  roofline_cache_kernels, fp8_linear_sweep, cpu_baseline ... the other parts of the metric and the host-core baseline
+A failed check is written into the line ("invalid": reason) and the process exits with status 1.
 
-`--impl reference` times the CPU restatement of the same path (the numpy oracle under oracle/) on
-the host cores, on a bounded sample of the step, and prints the same line with "impl": "reference".
+`--impl reference` times the CPU restatement of the same path (the numpy oracle under oracle/) on the host cores,
+on a bounded sample of the step, and prints the same line with "impl": "reference".
+`--small-case` launches every kernel of the package twice on small inputs (about 1 GB on the device) and exits:
+the program the committed `ncu` summaries under profiles/ were captured from.
 """
 from __future__ import annotations
 
@@ -37,12 +46,10 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
   sys.path.insert(0, ROOT)
 
-STEPS_PER_GENERATION = 28
-METRIC = "flux_1024x1024_denoise_steps_per_s"
-WORKLOAD = ("FLUX.1-dev-shape DiT (19 double + 38 single blocks, hidden 3072, 24x128 heads), 4096 image + "
-            "512 text tokens, 28-step schedule, DBCache F8B0 rdt=0.08 + TaylorSeer O1, FP8 w8a8")
 FP8_NOMINAL_TFLOPS = 4500.0
-
+HBM_NOMINAL_GBS = 8000.0
+MASKS_PATH = os.path.join(ROOT, "tests", "golden", "bench_hit_masks.json")
+TRAFFIC_PATH = os.path.join(ROOT, "profiles", "fp8_gemm_pair_kernel_small_case_ncu.json")
 
 def load_measured_peaks():
   path = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -105,24 +112,130 @@ class ClockSampler:
             "samples": len(sm), "reasons": sorted(reasons)}
 
 
-# ------------------------------------------------------------------------------------ our arm
-def build_model(device, seed=0):
-  import cache_dit_b200 as cd
-  from cache_dit_b200.synthetic import FluxTransformer2DModel
-  torch.manual_seed(seed)
-  with torch.device(device):
-    # calibrated stand-in: smooth time conditioning and small adaLN weights, so that consecutive
-    # steps are as similar as they are for a trained model (hit pattern: two hits, one miss)
-    model = FluxTransformer2DModel(time_scale=1.0, modulation_init_std=0.02).to(torch.bfloat16)
-  model.eval().requires_grad_(False)
-  return cd, model
+# ------------------------------------------------------------------------------------ workloads
+class Workload:
+  """One BASELINE configuration: how to build the stand-in, its cache settings and its synthetic inputs."""
+  name = ""
+  metric = ""
+  description = ""
+  steps_per_generation = 28
+  separate_cfg = False
+  guidance_scale = 4.0
+  model_kwargs = {}
+
+  def model_class(self):
+    raise NotImplementedError
+
+  def build_model(self, device, seed=0):
+    torch.manual_seed(seed)
+    with torch.device(device):
+      # calibrated stand-in: smooth time conditioning and small adaLN weights, so that consecutive steps are
+      # as similar as they are for a trained model (a random-init model of ordinary scale never hits)
+      model = self.model_class()(time_scale=1.0, modulation_init_std=0.02, **self.model_kwargs).to(torch.bfloat16)
+    return model.eval().requires_grad_(False)
+
+  def cache_config(self, cd):
+    raise NotImplementedError
+
+  def calibrator_config(self, cd):
+    return None
+
+  def parallelism_config(self, cd, world, exchange=None):
+    kw = {"exchange": exchange} if exchange else {}
+    return cd.ParallelismConfig(ulysses_size=world, ulysses_anything=True, parallel_kwargs=kw)
+
+  def host_inputs(self):
+    """One generation's inputs in pinned host memory (what a serving process would hold)."""
+    return {k: v.pin_memory() for k, v in self.model_class().example_inputs(device="cpu").items()}
+
+  # shapes the CPU arm needs: (token counts of the streams a block's linears see, hidden, list of per-block
+  # linear shapes as (stream index, K, N)), blocks per computed step, blocks per cached step, cache tensor [S, C]
+  def cpu_shape(self):
+    raise NotImplementedError
 
 
-def host_inputs():
-  """One generation's inputs in pinned host memory (what a serving process would hold)."""
-  from cache_dit_b200.synthetic import FluxTransformer2DModel
-  inp = FluxTransformer2DModel.example_inputs(device="cpu")
-  return {k: v.pin_memory() for k, v in inp.items()}
+class FluxWorkload(Workload):
+  name = "flux"
+  metric = "flux_1024x1024_denoise_steps_per_s"
+  description = ("FLUX.1-dev-shape DiT (19 double + 38 single blocks, hidden 3072, 24x128 heads), 4096 image + "
+                 "512 text tokens, 28-step schedule, DBCache F8B0 rdt=0.08 + TaylorSeer O1, FP8 w8a8")
+  steps_per_generation = 28
+
+  def model_class(self):
+    from cache_dit_b200.synthetic import FluxTransformer2DModel
+    return FluxTransformer2DModel
+
+  def cache_config(self, cd):
+    return cd.DBCacheConfig(Fn_compute_blocks=8, Bn_compute_blocks=0, residual_diff_threshold=0.08, max_warmup_steps=8,
+                            num_inference_steps=self.steps_per_generation, enable_separate_cfg=False)
+
+  def calibrator_config(self, cd):
+    return cd.TaylorSeerCalibratorConfig(taylorseer_order=1)
+
+  def parallelism_config(self, cd, world, exchange=None):
+    kw = {"exchange": exchange} if exchange else {}
+    return cd.ParallelismConfig(ulysses_size=world, parallel_kwargs=kw)
+
+  def cpu_shape(self):
+    double = [(m, 3072, n) for m in (4096, 512) for n in (3072, 3072, 3072, 3072, 12288)] + \
+             [(m, 12288, 3072) for m in (4096, 512)]
+    single = [(4608, 3072, 3072)] * 3 + [(4608, 3072, 12288), (4608, 15360, 3072)]
+    return dict(kinds={"double": double, "single": single}, computed={"double": 19, "single": 38},
+                cached={"double": 8, "single": 0}, cache_tensor=(4608, 3072), calls_per_step=1, warmup=8,
+                taylor=True)
+
+
+class QwenImageWorkload(Workload):
+  name = "qwen_image"
+  metric = "qwen_image_1328x1328_denoise_steps_per_s"
+  description = ("Qwen-Image-shape DiT (60 dual-stream blocks, hidden 3072, 24x128 heads), 6889 image + 256 text "
+                 "tokens, 50-step schedule, DBCache F8B0 rdt=0.12, separate CFG call, FP8 w8a8")
+  steps_per_generation = 50
+  separate_cfg = True
+
+  def model_class(self):
+    from cache_dit_b200.synthetic import QwenImageTransformer2DModel
+    return QwenImageTransformer2DModel
+
+  def cache_config(self, cd):
+    return cd.DBCacheConfig(Fn_compute_blocks=8, Bn_compute_blocks=0, residual_diff_threshold=0.12, max_warmup_steps=8,
+                            num_inference_steps=self.steps_per_generation, enable_separate_cfg=True)
+
+  def cpu_shape(self):
+    double = [(m, 3072, n) for m in (6889, 256) for n in (3072, 3072, 3072, 3072, 12288)] + \
+             [(m, 12288, 3072) for m in (6889, 256)]
+    return dict(kinds={"double": double}, computed={"double": 60}, cached={"double": 8}, cache_tensor=(6889, 3072),
+                calls_per_step=2, warmup=8, taylor=False)
+
+
+class WanWorkload(Workload):
+  name = "wan"
+  metric = "wan_81f_1280x720_denoise_steps_per_s"
+  description = ("Wan2.1-14B-shape video DiT (40 blocks, hidden 5120, 40x128 heads, FFN 13824), 75600 video + 512 "
+                 "text tokens, 40-step schedule, DBCache F1B0 rdt=0.08 + TaylorSeer O1, separate CFG call, FP8 w8a8")
+  steps_per_generation = 40
+  separate_cfg = True
+
+  def model_class(self):
+    from cache_dit_b200.synthetic import WanTransformer3DModel
+    return WanTransformer3DModel
+
+  def cache_config(self, cd):
+    return cd.DBCacheConfig(Fn_compute_blocks=1, Bn_compute_blocks=0, residual_diff_threshold=0.08, max_warmup_steps=8,
+                            num_inference_steps=self.steps_per_generation, enable_separate_cfg=True)
+
+  def calibrator_config(self, cd):
+    return cd.TaylorSeerCalibratorConfig(taylorseer_order=1)
+
+  def cpu_shape(self):
+    v, t = 75600, 512
+    block = [(v, 5120, 5120)] * 4 + [(v, 5120, 5120), (t, 5120, 5120), (t, 5120, 5120), (v, 5120, 5120)] + \
+            [(v, 5120, 13824), (v, 13824, 5120)]
+    return dict(kinds={"block": block}, computed={"block": 40}, cached={"block": 1}, cache_tensor=(v, 5120),
+                calls_per_step=2, warmup=8, taylor=True)
+
+
+WORKLOADS = {w.name: w for w in (FluxWorkload(), QwenImageWorkload(), WanWorkload())}
 
 
 def sigmas(n):
@@ -130,57 +243,105 @@ def sigmas(n):
   return DenoisePipeline.sigmas(n)
 
 
-class Stepper:
-  """Runs denoising steps one at a time across generation boundaries."""
+def committed_masks():
+  """Hit masks of full generations recorded on one B200 (tests/golden/bench_hit_masks.json): the cache decisions
+  every run of the same workload has to reproduce, whatever the number of GPUs."""
+  try:
+    with open(MASKS_PATH) as f:
+      return json.load(f)
+  except OSError:
+    return {}
 
-  def __init__(self, cd, model, dev_inputs):
-    self.cd, self.model = cd, model
-    self.inp = {k: v for k, v in dev_inputs.items() if k != "hidden_states"}
+
+def expected_hits(workload, first_step, count):
+  """[0/1] for `count` consecutive steps starting at step `first_step` of a generation, or None if no mask is
+  committed for the workload."""
+  entry = committed_masks().get(workload.name)
+  if not entry:
+    return None
+  n = workload.steps_per_generation
+  cached = set(entry["cached_steps"])
+  return [1 if ((first_step + i) % n) in cached else 0 for i in range(count)]
+
+
+class Stepper:
+  """Runs denoising steps one at a time across generation boundaries and records each step's cache decision."""
+
+  def __init__(self, cd, model, workload, dev_inputs):
+    self.cd, self.model, self.wl = cd, model, workload
+    self.cond = {k: v for k, v in dev_inputs.items() if k != "hidden_states"}
+    self.neg = None
+    if workload.separate_cfg:  # the unconditional call of classifier-free guidance: an empty (zero) prompt
+      self.neg = dict(self.cond)
+      self.neg["encoder_hidden_states"] = torch.zeros_like(self.cond["encoder_hidden_states"])
     self.x0 = dev_inputs["hidden_states"]
-    self.sig = sigmas(STEPS_PER_GENERATION)
-    self.i = STEPS_PER_GENERATION
+    self.n = workload.steps_per_generation
+    self.sig = sigmas(self.n)
+    self.i = self.n
     self.x = None
-    self.masks = []
+    self.hits = []      # 1 / 0 per step taken, main branch
+    self.cfg_hits = []  # the same for the separate guidance call
+
+  def at_generation_start(self):
+    self.i = self.n
 
   def start_generation(self):
-    if self.i < STEPS_PER_GENERATION and self.i > 0:
-      pass
-    self.cd.refresh_context(self.model, num_inference_steps=STEPS_PER_GENERATION)
+    self.cd.refresh_context(self.model, num_inference_steps=self.n)
     self.x = self.x0.clone()
     self.i = 0
 
   @torch.no_grad()
   def step(self, host=None, host_out=None):
-    if self.i >= STEPS_PER_GENERATION:
+    if self.i >= self.n:
       self.start_generation()
-    kw = self.inp
-    x = self.x
+    cond, neg, x = self.cond, self.neg, self.x
     if host is not None:  # end-to-end: this step's inputs come from pinned host memory
       x = host["latents"].to(x.device, non_blocking=True)
-      kw = {k: v.to(x.device, non_blocking=True) for k, v in host["cond"].items()}
+      cond = {k: v.to(x.device, non_blocking=True) for k, v in host["cond"].items()}
+      if neg is not None:
+        neg = dict(cond)
+        neg["encoder_hidden_states"] = host["neg_encoder"].to(x.device, non_blocking=True)
     t = torch.full((x.shape[0], ), float(self.sig[self.i]), device=x.device)
-    v = self.model(hidden_states=x, timestep=t, **kw)
+    v = self.model(hidden_states=x, timestep=t, **cond)
+    if neg is not None:
+      v_neg = self.model(hidden_states=x, timestep=t, **neg)
+      v = v_neg + self.wl.guidance_scale * (v - v_neg)
     self.x = (x.float() + float(self.sig[self.i + 1] - self.sig[self.i]) * v.float()).to(x.dtype)
     if host_out is not None:  # ... and its result goes back to the host
       host_out.copy_(self.x, non_blocking=True)
       torch.cuda.current_stream().synchronize()
       host["latents"].copy_(host_out)
+    self.hits.append(1 if self.i in getattr(self.model, "_cached_steps", ()) else 0)
+    if neg is not None:
+      self.cfg_hits.append(1 if self.i in getattr(self.model, "_cfg_cached_steps", ()) else 0)
     self.i += 1
-    if self.i == STEPS_PER_GENERATION:
-      self.masks.append(list(getattr(self.model, "_cached_steps", [])))
+
+  def generation(self):
+    """One whole generation from the fixed initial latents; returns (final latents, hit mask, cfg hit mask)."""
+    self.at_generation_start()
+    h0, c0 = len(self.hits), len(self.cfg_hits)
+    for _ in range(self.n):
+      self.step()
+    return self.x.clone(), self.hits[h0:], self.cfg_hits[c0:]
 
 
 def timed(fn, steps, barrier):
+  """`steps` calls of fn between barriers and device synchronisations; returns (total ms, per-call ms) from CUDA
+  events recorded on the launching stream after every call."""
   barrier()
   torch.cuda.synchronize()
-  start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-  start.record()
-  for _ in range(steps):
+  marks = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+  marks[0].record()
+  for i in range(steps):
     fn()
-  end.record()
+    marks[i + 1].record()
   torch.cuda.synchronize()
   barrier()
-  return start.elapsed_time(end)  # ms
+  return marks[0].elapsed_time(marks[-1]), [marks[i].elapsed_time(marks[i + 1]) for i in range(steps)]
+
+
+def mask_string(bits):
+  return "".join(str(b) for b in bits)
 
 
 def fp8_library_peak(device, sustained=True):
@@ -331,6 +492,74 @@ def fp8_linear_sweep(device):
   return out
 
 
+def fp8_comm_block(device, world=2, s_local=2304, heads=24, d=128):
+  """FP8 packing of what crosses NVLink under `ulysses_float8`, one rank's share of the FLUX sequence on two GPUs:
+  this package's kernels (layout change fused into the packing kernel, all destinations emulated by local
+  buffers) beside the reference's Triton ops on the same tensors (`fp8_comm_qkv_permute_quant` / `..._dequant`,
+  `fp8_comm_per_token_quant` / `..._dequant` with the permute copies its caller makes around them,
+  src/cache_dit/distributed/core/_distributed_primitives.py:741-813).  The Triton files are the unmodified
+  reference sources staged under baseline/_ref by tests/golden/make_fp8_comm_fixture.py; absent -> null."""
+  from cache_dit_b200 import _native as nat
+  bf = torch.bfloat16
+  n = heads // world
+  q, k, v = (torch.randn(1, s_local, heads * d, device=device).to(bf) for _ in range(3))
+  rows = s_local  # one sender's rows in each destination
+  q8 = {t: [torch.zeros(rows * n * d // 4, dtype=torch.int32, device=device) for _ in range(world)] for t in "qkv"}
+  sc = {t: [torch.zeros(rows * n, dtype=torch.float32, device=device) for _ in range(world)] for t in "qkv"}
+  # what a rank receives: all tokens of its own heads
+  r8 = {t: torch.zeros(rows * world * n * d // 4, dtype=torch.int32, device=device) for t in "qkv"}
+  rsc = {t: torch.ones(rows * world * n, dtype=torch.float32, device=device) for t in "qkv"}
+  out = {t: torch.empty(1, rows * world, n, d, dtype=bf, device=device) for t in "qkv"}
+  jobs = [dict(x=x, dst_ptrs=[b.data_ptr() for b in q8[t]], dst_batch_stride=rows * n * d, dst_row_offset=0,
+               dst_scale_ptrs=[b.data_ptr() for b in sc[t]]) for t, x in zip("qkv", (q, k, v))]
+  o_loc = torch.randn(1, s_local * world, n, d, device=device).to(bf)
+  o8 = torch.zeros(s_local * world * n * d // 4, dtype=torch.int32, device=device)
+  osc = torch.zeros(s_local * world * n, dtype=bf, device=device)
+  o_out = torch.empty(1, s_local * world, n, d, dtype=bf, device=device)
+  ours = {
+    "qkv_pack": _graph_us(lambda: nat.scatter_heads_multi(jobs, heads)),
+    "qkv_unpack": _graph_us(lambda: nat.fp8_dequant_heads([r8[t] for t in "qkv"], [rsc[t] for t in "qkv"],
+                                                          [out[t] for t in "qkv"], d)),
+    "o_pack": _graph_us(lambda: nat.gather_tokens_fp8(o_loc, [o8.data_ptr()], [osc.data_ptr()], 0)),
+    "o_unpack": _graph_us(lambda: nat.fp8_dequant_heads([o8], [osc], [o_out], d)),
+  }
+  ours = {k_: round(v_, 2) for k_, v_ in ours.items()}
+  ref = None
+  try:
+    sys.path.insert(0, os.path.join(ROOT, "tests", "golden"))
+    import make_fp8_comm_fixture as fixture
+    ops = fixture.reference_ops()
+    if ops is not None:
+      x5 = [t.view(1, s_local, world, n, d) for t in (q, k, v)]
+      packed = [ops.fp8_comm_qkv_permute_quant(x) for x in x5]
+      recv = [p.flatten(0, 1) for p in packed]  # what a rank receives: [W * S, B, N, D + 4]
+      o5 = o_loc.reshape(1, world, s_local, n, d)
+      o_packed = ops.fp8_comm_per_token_quant(o5.permute(1, 3, 0, 2, 4).contiguous())
+
+      def o_unpack():
+        y = ops.fp8_comm_per_token_dequant(o_packed)
+        return y.flatten(0, 1).permute(1, 2, 0, 3).contiguous()
+
+      ref = {
+        "qkv_pack": _graph_us(lambda: [ops.fp8_comm_qkv_permute_quant(x) for x in x5]),
+        "qkv_unpack": _graph_us(lambda: [ops.fp8_comm_qkv_permute_dequant(r) for r in recv]),
+        "o_pack": _graph_us(lambda: ops.fp8_comm_per_token_quant(o5.permute(1, 3, 0, 2, 4).contiguous())),
+        "o_unpack": _graph_us(o_unpack),
+      }
+      ref = {k_: round(v_, 2) for k_, v_ in ref.items()}
+  except Exception as e:  # the staged files or Triton are missing: the block reports this package's side only
+    ref = None
+    err = f"{type(e).__name__}: {e}"[:200]
+  block = {"case": f"bf16 q, k, v [1, {s_local}, {heads}x{d}] and attention output [1, {s_local * world}, {n}, {d}]: "
+                   f"one rank of {world}", "ours_us": ours, "reference_triton_us": ref}
+  if ref:
+    block["reference_over_ours"] = {k_: round(ref[k_] / ours[k_], 2) for k_ in ours}
+    block["total_reference_over_ours"] = round(sum(ref.values()) / sum(ours.values()), 2)
+  elif "err" in locals():
+    block["reference_unavailable"] = err
+  return block
+
+
 def eager_cache_ops_us(device, S=4096, C=3072):
   """The reference's eager PyTorch op sequences for the same four steps on the GPU (the kernels to
   beat): similarity = sub, abs, mean, abs, mean (src/cache_dit/caching/cache_contexts/cache_manager.py:609-619);
@@ -359,8 +588,21 @@ def eager_cache_ops_us(device, S=4096, C=3072):
           "taylor_apply_o1": round(_graph_us(apply), 2), "taylor_update_o1": round(_graph_us(update), 2)}
 
 
+def _kind_of_step(hit, cfg_hit):
+  if cfg_hit is None:
+    return "cached" if hit else "computed"
+  return {0: "computed", 1: "one_call_cached", 2: "cached"}[hit + cfg_hit]
+
+
+def _switch_exchange(cd, model, workload, world, mode):
+  """Re-plan the context-parallel exchange of `model` ("peer" | "nccl"); collective."""
+  model.disable_context_parallel()
+  model.enable_context_parallel(workload.parallelism_config(cd, world, exchange=mode))
+
+
 def run_ours(args):
   import torch.distributed as dist
+  wl = WORKLOADS[args.config]
   world = int(os.environ.get("WORLD_SIZE", "1"))
   rank = int(os.environ.get("RANK", "0"))
   local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -373,61 +615,65 @@ def run_ours(args):
     dist.init_process_group("nccl", device_id=device)
   barrier = (lambda: dist.barrier()) if world > 1 else (lambda: None)
 
+  import cache_dit_b200 as cd
   from cache_dit_b200 import _native as nat
   nat.lib()
-  cd, model = build_model(device)
-  cd.enable_cache(model,
-                  cache_config=cd.DBCacheConfig(Fn_compute_blocks=8, Bn_compute_blocks=0, residual_diff_threshold=0.08,
-                                                max_warmup_steps=8, num_inference_steps=STEPS_PER_GENERATION,
-                                                enable_separate_cfg=False),
-                  calibrator_config=cd.TaylorSeerCalibratorConfig(taylorseer_order=1),
-                  parallelism_config=cd.ParallelismConfig(ulysses_size=world) if world > 1 else None,
+  model = wl.build_model(device)
+  cd.enable_cache(model, cache_config=wl.cache_config(cd), calibrator_config=wl.calibrator_config(cd),
+                  parallelism_config=wl.parallelism_config(cd, world) if world > 1 else None,
                   quantize_config=cd.QuantizeConfig(quant_type="float8_per_row"))
   if not args.no_graphs:
     cd.enable_cuda_graphs(model)  # block segments between the cache decisions replay as CUDA graphs
-  host = host_inputs()
+  host = wl.host_inputs()
   dev_inputs = {k: v.to(device) for k, v in host.items()}
-  stepper = Stepper(cd, model, dev_inputs)
+  stepper = Stepper(cd, model, wl, dev_inputs)
+  n_gen = wl.steps_per_generation
+  steps = args.steps if args.steps is not None else (2 * n_gen if wl.name == "flux" else n_gen)
+  warmup = max(3, args.warmup if args.warmup is not None else (n_gen if wl.name == "flux" else 5))
 
-  warmup = max(3, args.warmup)
   for _ in range(warmup):
     stepper.step()
   torch.cuda.synchronize()
-  # -------- timed region 1: inputs resident in HBM
-  stepper.i = STEPS_PER_GENERATION  # start the timed region at a generation boundary
-  stepper.masks.clear()
+  # -------- timed region 1: inputs resident in HBM; starts at a generation boundary
+  stepper.at_generation_start()
   sampler = ClockSampler(local_rank)
   if rank == 0:
     sampler.start()
   launches0 = nat.launch_count
   if args.profile_timed_region:
     torch.cuda.profiler.start()
-  ms = timed(stepper.step, args.steps, barrier)
+  h0, c0 = len(stepper.hits), len(stepper.cfg_hits)
+  ms, per_step = timed(stepper.step, steps, barrier)
   if args.profile_timed_region:
     torch.cuda.profiler.stop()
   launches = nat.launch_count - launches0
   clocks = sampler.stop() if rank == 0 else {}
-  masks = [list(m) for m in stepper.masks]
+  hits, cfg_hits = stepper.hits[h0:], stepper.cfg_hits[c0:]
+  finite = bool(torch.isfinite(stepper.x).all().item())
   # -------- timed region 2: end to end with host buffers
   host_state = {"latents": host["hidden_states"].clone().pin_memory(),
                 "cond": {k: v for k, v in host.items() if k != "hidden_states"}}
+  if wl.separate_cfg:
+    host_state["neg_encoder"] = torch.zeros_like(host["encoder_hidden_states"]).pin_memory()
   host_out = torch.empty_like(host_state["latents"]).pin_memory()
-  stepper.i = STEPS_PER_GENERATION
+  stepper.at_generation_start()
   for _ in range(3):
     stepper.step(host_state, host_out)
-  stepper.i = STEPS_PER_GENERATION
+  stepper.at_generation_start()
   host_state["latents"].copy_(host["hidden_states"])
-  ms_e2e = timed(lambda: stepper.step(host_state, host_out), args.steps, barrier)
+  ms_e2e, _ = timed(lambda: stepper.step(host_state, host_out), steps, barrier)
   h2d = sum(v.numel() * v.element_size() for v in host.values())
+  if wl.separate_cfg:
+    h2d += host_state["neg_encoder"].numel() * host_state["neg_encoder"].element_size()
   d2h = host_out.numel() * host_out.element_size()
   # -------- instrumented repeat of region 1: per-launch durations of the dominant kernel (FP8 GEMM)
   # (eager launches: events cannot bracket single kernels inside a graph replay)
   runners = cd.graph_runners(model)
   for r in runners:
     r.enabled = False
-  stepper.i = STEPS_PER_GENERATION
+  stepper.at_generation_start()
   nat.gemm_timer = []
-  instrumented_steps = min(args.steps, STEPS_PER_GENERATION)
+  instrumented_steps = min(steps, n_gen, 28)
   for _ in range(instrumented_steps):
     stepper.step()
   torch.cuda.synchronize()
@@ -437,75 +683,151 @@ def run_ours(args):
   gemm_ms = sum(s.elapsed_time(e) for s, e, _ in records)
   gemm_flops = sum(f for _, _, f in records)
 
+  # -------- self-checks: latched status words of the bounded device-side waits, finite latents, hit mask
+  box = nat.device_mailbox(device).cpu()
+  check = torch.tensor([float(box[nat.MAILBOX_GEMM_STATUS] != 0), float(box[nat.MAILBOX_PEER_STATUS] != 0),
+                        float(not finite)], device=device, dtype=torch.float64)
   times = torch.tensor([ms, ms_e2e], device=device, dtype=torch.float64)
   if world > 1:
     dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    dist.all_reduce(check, op=dist.ReduceOp.MAX)  # any rank's failure is the run's failure
   ms, ms_e2e = float(times[0]), float(times[1])
+  checks = {"gemm_device_status_ok": check[0].item() == 0, "peer_exchange_status_ok": check[1].item() == 0,
+            "latents_finite": check[2].item() == 0}
+  expected = expected_hits(wl, 0, steps)
+  checks["hit_mask_equals_committed_single_gpu_mask"] = None if expected is None else (hits == expected)
+
+  # -------- parity of the exchange (N > 1): the peer-memory exchange against NCCL all-to-all, eager
+  parity = None
+  if world > 1 and not args.no_parity:
+    p_steps = args.parity_steps if args.parity_steps else (n_gen if wl.name != "wan" else 12)
+    p_steps = min(p_steps, n_gen)
+
+    def partial_generation():
+      stepper.at_generation_start()
+      a, b = len(stepper.hits), len(stepper.cfg_hits)
+      for _ in range(p_steps):
+        stepper.step()
+      return stepper.x.clone(), stepper.hits[a:], stepper.cfg_hits[b:]
+
+    lat_peer, m_peer, mc_peer = partial_generation()
+    for r in runners:
+      r.enabled = False  # graphs were captured with the peer buffers' addresses: never replayed from here on
+    _switch_exchange(cd, model, wl, world, "nccl")
+    lat_nccl, m_nccl, mc_nccl = partial_generation()
+    rel = float((lat_peer.float() - lat_nccl.float()).norm() / lat_nccl.float().norm())
+    parity = {"against": "NCCL all-to-all exchange, eager launches, same seed", "steps": p_steps,
+              "mask_equal": m_peer == m_nccl and mc_peer == mc_nccl, "latents_rel_l2": rel,
+              "latents_within_2e-2": rel <= 2e-2, "hit_mask": mask_string(m_peer)}
+    exp_p = expected_hits(wl, 0, p_steps)
+    if exp_p is not None:
+      parity["mask_equals_committed_single_gpu_mask"] = m_peer == exp_p
+
   if rank != 0:
     if world > 1:
       dist.destroy_process_group()
-    return
+    return 0
   peaks, peak_kind = load_measured_peaks()
+  extras = (not args.skip_extras) and wl.name == "flux"
   cache_roof = None
-  fp8_burst = fp8_library_peak(device, sustained=False) if not args.skip_extras else None
-  if not args.skip_extras:  # before the 2-second GEMM loop below heats the part
+  fp8_burst = fp8_library_peak(device, sustained=False) if extras else None
+  if extras:  # before the 2-second GEMM loop below heats the part
     cache_roof = {"flux_image_stream_1x4096x3072": cache_kernel_rooflines(device, peaks["hbm_gbs"]),
                   "wan_rank_shard_1x9450x5120": cache_kernel_rooflines(device, peaks["hbm_gbs"], 9450, 5120, 3),
                   "eager_torch_ops_us_1x4096x3072": eager_cache_ops_us(device)}
     sweep = fp8_linear_sweep(device)
-  fp8_lib = fp8_library_peak(device) if not args.skip_extras else None
+    comm = fp8_comm_block(device)
+  fp8_lib = fp8_library_peak(device) if extras else None
   if fp8_lib and fp8_burst:
     fp8_lib = (max(fp8_lib[0], fp8_burst[0]), fp8_lib[1])
   achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
-  # the GEMM launches are timed inside long steps under the power cap: the sustained library figure
-  # is the like-for-like denominator, the burst figure is reported beside it
-  peak = fp8_lib[1] if fp8_lib else FP8_NOMINAL_TFLOPS
-  line = {
-    "metric": METRIC, "value": args.steps / (ms * 1e-3), "unit": "steps/s", "n_gpus": world, "steps": args.steps,
-    "warmup": warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
-    "vs_baseline": None, "dtype": "bf16 activations, fp8 e4m3 linears (fp32 accumulate)", "data": "synthetic",
-    "config": {"workload": WORKLOAD, "parallelism": f"ulysses{world}" if world > 1 else "single",
-               "l2_policy": "inputs larger than L2: ~12 GB of FP8 weights streamed per computed step",
-               "cuda_graphs": (not args.no_graphs), "cached_steps_per_generation": masks[:2]},
-    "e2e": {"value": args.steps / (ms_e2e * 1e-3), "unit": "steps/s", "h2d_bytes_per_step": h2d,
-            "d2h_bytes_per_step": d2h},
-    "gpu_launches": launches, "clocks": clocks,
-    "roofline": {"bound": "tensor", "kernel": "fp8_gemm_rowscaled_pair_kernel + fp8_gemm_rowscaled_kernel + fp8_gemv_rowscaled_kernel (every cdb_fp8_gemm_rowscaled launch of the step)", "achieved": round(achieved, 1),
-                 "peak": round(peak, 1), "unit": "TFLOP/s", "frac": round(achieved / peak, 3),
-                 "peak_source": "torch._scaled_mm e4m3 8192^3 per-tensor back to back for 2 s (sustained), "
-                 "measured in this run" if fp8_lib else "nominal dense FP8",
-                 "peak_burst": round(fp8_lib[0], 1) if fp8_lib else None,
-                 "frac_of_burst": round(achieved / fp8_lib[0], 3) if fp8_lib else None,
-                 "frac_of_nominal_4500": round(achieved / FP8_NOMINAL_TFLOPS, 3), "launches": len(records),
-                 "avg_launch_us": round(1e3 * gemm_ms / max(len(records), 1), 2),
-                 # time inside these launches per step / the timed region's time per step (compare with the
-                 # kernel's share in the committed ncu launch list)
-                 "share_of_step": round((gemm_ms / max(instrumented_steps, 1)) / (ms / args.steps), 3),
-                 "timing": "CUDA events around every GEMM launch in an instrumented repeat of the timed steps",
-                 # dram__bytes_read + dram__bytes_write of one launch of the dominant shape class from the
-                 # committed ncu capture (profiles/kernels_small_case_ncu_set_full.md): 52.1 MB + 67.9 MB for
-                 # 165.1 MB of operands and output (part of the output is still in L2 when the kernel ends)
-                 "traffic": 120.0e6, "traffic_case": "ncu, pair kernel, M=4608 N=12288 K=3072 (a single-stream MLP-in product)"},
+  # Dense FP8 runs at twice the dense bf16 rate on this part, and the peaks file measures bf16 with the vendor
+  # library: the denominator is 2 x its sustained figure (the GEMM launches are timed inside long steps under
+  # the power cap); the burst figure and the library's own FP8 product measured in this run are printed beside it.
+  peak = 2.0 * peaks["bf16_tflops_sustained"]
+  peak_burst = 2.0 * peaks["bf16_tflops"]
+  traffic = None
+  traffic_case = None
+  try:
+    with open(TRAFFIC_PATH) as f:
+      cap = json.load(f)
+    traffic = cap["dram_bytes_read"] + cap["dram_bytes_write"]
+    traffic_case = cap["case"]
+  except (OSError, KeyError, ValueError):
+    pass
+  by_kind = {}
+  for i, t in enumerate(per_step):
+    by_kind.setdefault(_kind_of_step(hits[i], cfg_hits[i] if cfg_hits else None), []).append(t)
+  roofline = {
+    "bound": "tensor",
+    "kernel": "fp8_gemm_rowscaled_pair_kernel + fp8_gemm_rowscaled_kernel + fp8_gemv_rowscaled_kernel (every "
+              "cdb_fp8_gemm_rowscaled launch of the step)",
+    "achieved": round(achieved, 1), "peak": round(peak, 1), "unit": "TFLOP/s", "frac": round(achieved / peak, 3),
+    "peak_source": f"2 x bf16_tflops_sustained of MEASURED_PEAKS.json ({peak_kind})",
+    "frac_of_2x_bf16_sustained": round(achieved / peak, 3), "frac_of_2x_bf16_burst": round(achieved / peak_burst, 3),
+    "frac_of_nominal_4500": round(achieved / FP8_NOMINAL_TFLOPS, 3),
+    "library_fp8_sustained": round(fp8_lib[1], 1) if fp8_lib else None,
+    "library_fp8_burst": round(fp8_lib[0], 1) if fp8_lib else None,
+    "frac_of_library_fp8_sustained": round(achieved / fp8_lib[1], 3) if fp8_lib else None,
+    "launches": len(records), "avg_launch_us": round(1e3 * gemm_ms / max(len(records), 1), 2),
+    # time inside these launches per step / the timed region's time per step (compare with the kernel's share in
+    # the committed launch list)
+    "share_of_step": round((gemm_ms / max(instrumented_steps, 1)) / (ms / steps), 3),
+    "timing": "CUDA events around every GEMM launch in an instrumented (eager) repeat of the timed steps",
+    "traffic": traffic, "traffic_case": traffic_case,
   }
-  if not args.skip_extras:
+  line = {
+    "metric": wl.metric, "value": steps / (ms * 1e-3), "unit": "steps/s", "n_gpus": world, "steps": steps,
+    "warmup": warmup, "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "strong",
+    "vs_baseline": None, "dtype": "bf16 activations, fp8 e4m3 linears (fp32 accumulate)", "data": "synthetic",
+    "config": {"workload": wl.description, "parallelism": f"ulysses{world}" if world > 1 else "single",
+               "l2_policy": "inputs larger than L2: the FP8 weights of the model are streamed every computed step",
+               "cuda_graphs": (not args.no_graphs), "hit_mask": mask_string(hits),
+               "cfg_hit_mask": mask_string(cfg_hits) if cfg_hits else None,
+               "first_timed_step": 0, "steps_per_generation": n_gen},
+    "ms_per_step_by_kind": {k: round(sum(v) / len(v), 3) for k, v in sorted(by_kind.items())},
+    "steps_by_kind": {k: len(v) for k, v in sorted(by_kind.items())},
+    "ms_computed_step": round(sum(by_kind["computed"]) / len(by_kind["computed"]), 3) if "computed" in by_kind else None,
+    "ms_cached_step": round(sum(by_kind["cached"]) / len(by_kind["cached"]), 3) if "cached" in by_kind else None,
+    "e2e": {"value": steps / (ms_e2e * 1e-3), "unit": "steps/s", "h2d_bytes_per_step": h2d,
+            "d2h_bytes_per_step": d2h},
+    "gpu_launches": launches, "clocks": clocks, "checks": checks, "roofline": roofline,
+  }
+  if parity is not None:
+    line["parity"] = parity
+  if extras:
+    for group in cache_roof.values():
+      for entry in group.values():
+        if isinstance(entry, dict) and "achieved" in entry:
+          entry["frac_of_nominal_8000"] = round(entry["achieved"] / HBM_NOMINAL_GBS, 3)
     line["roofline_cache_kernels"] = cache_roof
     line["fp8_linear_sweep"] = sweep
+    line["fp8_comm"] = comm
     line["roofline_cache_kernels"]["peak_source"] = f"{peak_kind} copy bandwidth (1 Gi-element copy)"
-    line["cpu_baseline"] = cpu_baseline(sample_only=True, hits=len(masks[0]) if masks else None)
+    if world == 1:
+      line["cpu_baseline"] = cpu_baseline(wl, hits, cfg_hits or None)
+  failed = [k for k, v in checks.items() if v is False]
+  if parity is not None:
+    failed += [f"parity.{k}" for k in ("mask_equal", "latents_within_2e-2", "mask_equals_committed_single_gpu_mask")
+               if parity.get(k) is False]
+  if failed:
+    line["invalid"] = "failed checks: " + ", ".join(failed)
   if world > 1:
     dist.destroy_process_group()
   print(json.dumps(line), flush=True)
+  return 1 if failed else 0
 
 
 # ------------------------------------------------------------------------------------ CPU arm
-def cpu_baseline(sample_only=False, hits=None):
-  """The reference's path restated on the CPU (numpy oracle), timed on this host's cores.
+def cpu_baseline(wl, hits=None, cfg_hits=None):
+  """The reference's path restated on the CPU (numpy oracle under oracle/), timed on this host's cores.
 
-  Sample: the cache ops of one step at full size (bf16 [1, 4608, 3072]: check, TaylorSeer update,
-  TaylorSeer apply) and the FP8 linears of ONE double-stream and ONE single-stream block at 4608
-  tokens (dynamic per-token quantization + dequantized fp32 product).  A computed step is then
-  19 double + 38 single blocks, a cached step is the first 8 double blocks + apply; attention (a
-  library call on both sides) is left out of the CPU figure, which flatters the CPU."""
+  Sample: the cache ops of one step (check, TaylorSeer update + apply, or plain residual store + add) on a bf16
+  tensor of the workload's width and at most 9450 rows, and the FP8 linears (dynamic per-token quantization +
+  dequantized fp32 product) of ONE block of each kind on at most 2304 rows per product; both scale linearly in
+  the row count and are scaled to the workload's rows.  A computed call runs all blocks, a cached call the first
+  Fn blocks + the apply; attention (a library call on both sides) is left out of the CPU figure, which flatters
+  the CPU.  The step mix is the one given by `hits` (the GPU run's timed steps)."""
   import numpy as np
   from oracle import cache_oracle as O
   from oracle import fp8_oracle as F
@@ -520,84 +842,193 @@ def cpu_baseline(sample_only=False, hits=None):
     cores = max(blas) if blas else cores
   except ImportError:
     cores = int(os.environ.get("OMP_NUM_THREADS", cores))
+  shape = wl.cpu_shape()
   rng = np.random.RandomState(0)
-  S, C = 4608, 3072
-  prev = O.round_bf16(rng.randn(1, S, C).astype(np.float32))
-  cur = O.round_bf16(prev + 0.05 * rng.randn(1, S, C).astype(np.float32))
+  S, C = shape["cache_tensor"]
+  Ss = min(S, 9450)
+  row_scale = S / Ss
+  prev = O.round_bf16(rng.randn(1, Ss, C).astype(np.float32))
+  cur = O.round_bf16(prev + 0.05 * rng.randn(1, Ss, C).astype(np.float32))
   t0 = time.perf_counter()
   O.rel_l1(prev, cur, "bf16")
-  t_check = time.perf_counter() - t0
-  t0 = time.perf_counter()
-  ladder = O.taylor_derivatives(O.residual(cur, prev, "bf16"), [prev, None], 3, True, "bf16")
-  t_update = time.perf_counter() - t0
-  t0 = time.perf_counter()
-  O.apply_add(O.taylor_series(ladder, 2, "bf16"), cur, "bf16")
-  t_apply = time.perf_counter() - t0
+  t_check = (time.perf_counter() - t0) * row_scale
+  if shape["taylor"]:
+    t0 = time.perf_counter()
+    ladder = O.taylor_derivatives(O.residual(cur, prev, "bf16"), [prev, None], 3, True, "bf16")
+    t_store = (time.perf_counter() - t0) * row_scale
+    t0 = time.perf_counter()
+    O.apply_add(O.taylor_series(ladder, 2, "bf16"), cur, "bf16")
+    t_apply = (time.perf_counter() - t0) * row_scale
+  else:
+    t0 = time.perf_counter()
+    res = O.residual(cur, prev, "bf16")
+    t_store = (time.perf_counter() - t0) * row_scale
+    t0 = time.perf_counter()
+    O.apply_add(res, cur, "bf16")
+    t_apply = (time.perf_counter() - t0) * row_scale
+
+  linear_cache = {}
 
   def linear(m, k, n):
-    x = O.round_bf16(rng.randn(m, k).astype(np.float32))
-    w = O.round_bf16((0.02 * rng.randn(n, k)).astype(np.float32))
-    wc, ws = F.quantize_rows(w)  # weights are quantized once at load: not timed
-    t = time.perf_counter()
-    ac, asc = F.quantize_rows(x)
-    F.scaled_mm(ac, asc, wc, ws)
-    return time.perf_counter() - t
+    ms = min(m, 2304)
+    key = (ms, k, n)
+    if key not in linear_cache:
+      x = O.round_bf16(rng.randn(ms, k).astype(np.float32))
+      w = O.round_bf16((0.02 * rng.randn(n, k)).astype(np.float32))
+      wc, ws = F.quantize_rows(w)  # weights are quantized once at load: not timed
+      t = time.perf_counter()
+      ac, asc = F.quantize_rows(x)
+      F.scaled_mm(ac, asc, wc, ws)
+      linear_cache[key] = time.perf_counter() - t
+    return linear_cache[key] * (m / ms)
 
-  # double block: image (4096 tokens) and text (512) streams, each q,k,v,out (3072x3072) + MLP 3072<->12288
-  t_double = 0.0
-  for m in (4096, 512):
-    t_double += 4 * linear(m, 3072, 3072) + linear(m, 3072, 12288) + linear(m, 12288, 3072)
-  # single block: q,k,v + MLP-in on 4608 tokens, then 15360 -> 3072
-  t_single = 3 * linear(4608, 3072, 3072) + linear(4608, 3072, 12288) + linear(4608, 15360, 3072)
-  computed = 19 * t_double + 38 * t_single
-  cached = 8 * t_double
-  if hits is None:
-    hits = 14  # hit count of the reference's synthetic cache-step schedule (2 hits, 1 miss after warm-up)
-  per_generation = (STEPS_PER_GENERATION - hits) * (computed + t_update) + hits * (cached + t_apply) \
-      + (STEPS_PER_GENERATION - 8) * t_check
-  return {"value": STEPS_PER_GENERATION / per_generation, "unit": "steps/s", "cores": cores,
-          "kind": "port",
-          "sample": ("numpy restatement: cache check/update/apply at [1,4608,3072] bf16 + FP8 linears of one "
-                     "double and one single block, extrapolated to 19+38 blocks and a 28-step schedule with the "
-                     f"GPU run's hit count ({hits}); attention excluded"),
-          "seconds": {"check": t_check, "update": t_update, "apply": t_apply, "double_block_linears": t_double,
-                      "single_block_linears": t_single}}
+  t_kind = {kind: sum(linear(*lin) for lin in lins) for kind, lins in shape["kinds"].items()}
+  computed_call = sum(shape["computed"][k] * t for k, t in t_kind.items())
+  cached_call = sum(shape["cached"][k] * t for k, t in t_kind.items())
+  n = wl.steps_per_generation
+  if hits is None:  # no GPU run at hand: the committed mask, else two hits and one miss after the warm-up
+    hits = expected_hits(wl, 0, n) or [1 if (i >= shape["warmup"] and (i - shape["warmup"]) % 3 != 2) else 0 for i in range(n)]
+  branches = [hits] + ([cfg_hits if cfg_hits is not None else hits] if shape["calls_per_step"] == 2 else [])
+  total = 0.0
+  for i in range(len(hits)):
+    for branch in branches:
+      total += (cached_call + t_apply) if branch[i] else (computed_call + t_store)
+      if (i % n) >= shape["warmup"]:
+        total += t_check
+  return {"value": len(hits) / total, "unit": "steps/s", "cores": cores, "kind": "port",
+          "sample": (f"numpy restatement: cache check/store/apply at [1,{Ss},{C}] bf16 (scaled to {S} rows) + FP8 linears of "
+                     f"one block of each kind at <= 2304 rows per product (scaled to the workload's rows), extrapolated by "
+                     f"block counts to the hit mask {mask_string(hits)}; attention excluded"),
+          "seconds": {"check": t_check, "store": t_store, "apply": t_apply, "computed_call": computed_call,
+                      "cached_call": cached_call, **{f"{k}_block_linears": v for k, v in t_kind.items()}}}
 
 
 def run_reference(args):
   rank = int(os.environ.get("RANK", "0"))
   if rank != 0:
-    return
-  base = cpu_baseline()
+    return 0
+  wl = WORKLOADS[args.config]
+  n_gen = wl.steps_per_generation
+  steps = args.steps if args.steps is not None else (2 * n_gen if wl.name == "flux" else n_gen)
+  # the same step mix as the GPU arm times: steps 0 .. K-1 of consecutive generations with the committed hit mask
+  hits = expected_hits(wl, 0, steps)
+  base = cpu_baseline(wl, hits, None)
   line = {
-    "impl": "reference", "metric": METRIC, "value": base["value"], "unit": "steps/s", "n_gpus": args.gpus,
-    "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 / base["value"], "higher_is_better": True,
+    "impl": "reference", "metric": wl.metric, "value": base["value"], "unit": "steps/s", "n_gpus": args.gpus,
+    "steps": steps, "warmup": args.warmup if args.warmup is not None else 0, "ms_per_step": 1e3 / base["value"],
+    "higher_is_better": True,
     "scaling": "strong", "vs_baseline": None, "dtype": "fp32 arithmetic on e4m3 / bf16 values", "data": "synthetic",
-    "config": {"workload": WORKLOAD, "parallelism": "host cores"},
+    "config": {"workload": wl.description, "parallelism": "host cores",
+               "hit_mask": mask_string(hits) if hits is not None else None, "first_timed_step": 0,
+               "steps_per_generation": n_gen,
+               "timing": "bounded sample of the step, extrapolated (see cpu_baseline.sample); not a run of all steps"},
     "cpu_baseline": base,
     "e2e": {"value": base["value"], "unit": "steps/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     "gpu_launches": 0,
   }
   print(json.dumps(line), flush=True)
+  return 0
+
+
+# ------------------------------------------------------------------------------------ small case for ncu
+def small_case():
+  """Small launches of every kernel of the package (about 1 GB on the device), twice each (the first pass pays
+  one-time set-up); a 256 MB buffer is overwritten before every launch so that DRAM counters are not flattered
+  by L2 hits.  This is the program of the committed `ncu` captures."""
+  from cache_dit_b200 import _native as nat
+  nat.lib()
+  dev = "cuda"
+  bf = torch.bfloat16
+  S, C = 8192, 3072  # bf16 [1, 8192, 3072] = 50 MB per tensor: 2-5 tensors per kernel > L2
+  mk = lambda *s: torch.randn(*s, device=dev).to(bf)
+  h, h0, p, d = mk(1, S, C), mk(1, S, C), mk(1, S, C), mk(1, S, C)
+  o, o2 = torch.empty_like(h), torch.empty_like(h)
+  means = torch.zeros(2, device=dev)
+  flush = torch.empty(1 << 28, dtype=torch.uint8, device=dev)
+  M, K, N = 4608, 3072, 12288
+  x = mk(M, K)
+  w = (0.02 * torch.randn(N, K, device=dev)).to(bf)
+  aq = torch.empty(M, K, device=dev, dtype=torch.float8_e4m3fn)
+  sa = torch.empty(M, device=dev)
+  wq = torch.empty(N, K, device=dev, dtype=torch.float8_e4m3fn)
+  sw = torch.empty(N, device=dev)
+  out = torch.empty(M, N, device=dev, dtype=bf)
+  nat.fp8_quant_rows(w, wq, sw)
+  # rank-shard GEMM (single-CTA kernel): 576 rows = one rank of eight
+  xs = mk(576, K)
+  aqs = torch.empty(576, K, device=dev, dtype=torch.float8_e4m3fn)
+  sas = torch.empty(576, device=dev)
+  outs = torch.empty(576, N, device=dev, dtype=bf)
+  nat.fp8_quant_rows(xs, aqs, sas)
+  # producer-fused quantization inputs
+  mod = mk(1, 6 * K)
+  wide = mk(M, 21504)  # fused q/k/v + MLP-in output of a single-stream block
+  attn = mk(M, K)
+  aq2 = torch.empty(M, K + 12288, device=dev, dtype=torch.float8_e4m3fn)
+  aq3 = torch.empty(M, 12288, device=dev, dtype=torch.float8_e4m3fn)
+  # glue
+  H, D = 24, 128
+  cos, sin, wn = mk(M, D), mk(M, D), mk(D)
+  joint = torch.empty(1, M, H, D, device=dev, dtype=bf)
+  joint_k = torch.empty_like(joint)
+  # one-row product (modulation linear): the weight-streaming kernel
+  x1 = mk(1, K)
+  aq1 = torch.empty(1, K, device=dev, dtype=torch.float8_e4m3fn)
+  sa1 = torch.empty(1, device=dev)
+  out1 = torch.empty(1, N, device=dev, dtype=bf)
+  nat.fp8_quant_rows(x1, aq1, sa1)
+  xg, yg = mk(1, M, K), mk(1, M, K)
+  launches = [
+    lambda: nat.rel_l1(h, None, p, None, means),
+    lambda: nat.rel_l1(h, h0, p, o, means),
+    lambda: nat.taylor_apply(h, [p, d], [1.0, 1.0], [1.0, 2.0], True, o),
+    lambda: nat.taylor_update(h, h0, [p], [o, o2], 1, 3.0),
+    lambda: nat.fp8_quant_rows(x, aq, sa),
+    lambda: nat.fp8_quant_rows(x, aq, sa, nat.PRE_LAYERNORM_MOD, mod[:, :K], mod[:, K:2 * K], M, 1e-6),
+    lambda: nat.fp8_quant_rows(wide[:, 9216:], aq3, sa, nat.PRE_GELU_TANH),
+    lambda: nat.fp8_quant_rows_concat_gelu(attn, wide[:, 9216:], aq2, sa),
+    lambda: nat.scatter_heads_multi([
+      dict(x=wide[None, :, :K], norm_weight=wn, cos=cos, sin=sin, table_row_offset=0, dst_ptrs=[joint.data_ptr()],
+           dst_batch_stride=joint.stride(0), dst_row_offset=0, eps=1e-6),
+      dict(x=wide[None, :, K:2 * K], norm_weight=wn, cos=cos, sin=sin, table_row_offset=0,
+           dst_ptrs=[joint_k.data_ptr()], dst_batch_stride=joint.stride(0), dst_row_offset=0, eps=1e-6)], H),
+    lambda: nat.gated_residual(xg, mod[:, 2 * K:3 * K], yg),
+    lambda: nat.fp8_gemm_rowscaled(aq, sa, wq, sw, None, out),
+    lambda: nat.fp8_gemm_rowscaled(aqs, sas, wq, sw, None, outs),
+    lambda: nat.fp8_gemm_rowscaled(aq1, sa1, wq, sw, None, out1),
+  ]
+  for _ in range(2):
+    for launch in launches:
+      flush.zero_()
+      launch()
+  torch.cuda.synchronize()
+  nat.check_device_status(torch.device("cuda", torch.cuda.current_device()))
+  print("small case ok", means.tolist(), flush=True)
+  return 0
 
 
 def main():
   ap = argparse.ArgumentParser()
   ap.add_argument("--gpus", type=int, default=1)
-  ap.add_argument("--steps", type=int, default=2 * STEPS_PER_GENERATION)
-  ap.add_argument("--warmup", type=int, default=STEPS_PER_GENERATION)
+  ap.add_argument("--steps", type=int, default=None, help="timed steps (default: two generations of flux, one of the others)")
+  ap.add_argument("--warmup", type=int, default=None)
   ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+  ap.add_argument("--config", choices=sorted(WORKLOADS), default="flux")
   ap.add_argument("--no-graphs", action="store_true", help="issue every kernel from Python instead of replaying CUDA graphs")
+  ap.add_argument("--no-parity", action="store_true", help="N > 1: leave out the peer-exchange vs NCCL all-to-all generations")
+  ap.add_argument("--parity-steps", type=int, default=0, help="N > 1: steps of each parity generation (default: a whole one; 12 for wan)")
   ap.add_argument("--profile-timed-region", action="store_true",
                   help="bracket the first timed region with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
   ap.add_argument("--skip-extras", action="store_true",
-                  help="leave out the cache-kernel microbenchmarks, the FP8 library peak and the CPU sample")
+                  help="leave out the cache-kernel microbenchmarks, the FP8 sweep, the library peak and the CPU sample")
+  ap.add_argument("--small-case", action="store_true", help="launch every kernel twice on small inputs and exit (for ncu)")
   args = ap.parse_args()
+  if args.small_case:
+    return small_case()
   if args.impl == "reference":
-    run_reference(args)
-  else:
-    run_ours(args)
+    return run_reference(args)
+  return run_ours(args)
 
 
 if __name__ == "__main__":
-  main()
+  sys.exit(main())

@@ -74,12 +74,36 @@ def e4m3_decode(codes: np.ndarray) -> np.ndarray:
   return (sign * val).astype(np.float32)
 
 
-def quantize_rows(x: np.ndarray) -> Tuple[np.ndarray, np.ndarray]:
-  """x [rows, cols] (float32 holding bf16 values) -> (e4m3 byte codes, float32 scales)."""
+SCALE_RULES = ("fp32_reciprocal", "fp32_division", "bf16")
+
+
+def row_scales(x: np.ndarray, rule: str = "fp32_reciprocal") -> np.ndarray:
+  """Per-row scale under one of the ways `amax / 448` can be carried out.
+
+  fp32_reciprocal  amax * fl32(1/448) in float32: what PyTorch's CUDA kernels give for `amax.float() / 448.0`
+                   (the pinned rule, see the header)
+  fp32_division    the correctly rounded float32 quotient amax / 448 (differs in the last bit at most)
+  bf16             amax kept in the input dtype and divided there, i.e. the quotient rounded to bf16 and then
+                   widened: what a quantizer that never leaves bf16 would produce (scales move by up to 2^-9)
+  The alternatives exist to BOUND what the unpinned part of the rule (torchao cannot be run here) can cost; the
+  product path and every parity test use the first."""
   x = np.asarray(x, dtype=np.float32)
   amax = np.max(np.abs(x), axis=1).astype(np.float32)
-  scale = (amax * (np.float32(1.0) / E4M3_MAX)).astype(np.float32)
-  scale = np.where(scale == 0, np.float32(1.0), scale).astype(np.float32)
+  if rule == "fp32_reciprocal":
+    scale = (amax * (np.float32(1.0) / E4M3_MAX)).astype(np.float32)
+  elif rule == "fp32_division":
+    scale = (amax / E4M3_MAX).astype(np.float32)
+  elif rule == "bf16":
+    scale = round_bf16((amax * (np.float32(1.0) / E4M3_MAX)).astype(np.float32))
+  else:
+    raise ValueError(f"unknown scale rule {rule!r}")
+  return np.where(scale == 0, np.float32(1.0), scale).astype(np.float32)
+
+
+def quantize_rows(x: np.ndarray, rule: str = "fp32_reciprocal") -> Tuple[np.ndarray, np.ndarray]:
+  """x [rows, cols] (float32 holding bf16 values) -> (e4m3 byte codes, float32 scales)."""
+  x = np.asarray(x, dtype=np.float32)
+  scale = row_scales(x, rule)
   q = e4m3_round((x / scale[:, None]).astype(np.float32))
   return e4m3_encode(q), scale
 
@@ -113,8 +137,9 @@ def scaled_mm(a_codes: np.ndarray, a_scale: np.ndarray, w_codes: np.ndarray, w_s
   return round_bf16(out.astype(np.float32))
 
 
-def fp8_linear(x: np.ndarray, w: np.ndarray, bias: Optional[np.ndarray] = None) -> np.ndarray:
+def fp8_linear(x: np.ndarray, w: np.ndarray, bias: Optional[np.ndarray] = None,
+               rule: str = "fp32_reciprocal") -> np.ndarray:
   """Dynamic per-token activation quantization + per-output-row weight quantization + product."""
-  a_codes, a_scale = quantize_rows(x)
-  w_codes, w_scale = quantize_rows(w)
+  a_codes, a_scale = quantize_rows(x, rule)
+  w_codes, w_scale = quantize_rows(w, rule)
   return scaled_mm(a_codes, a_scale, w_codes, w_scale, bias)

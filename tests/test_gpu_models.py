@@ -147,3 +147,49 @@ def test_flux_full_size_generation_kernels_vs_oracle_ops():
     assert abs(s_k.residual_diffs[k] - v) <= 1e-3 * abs(v) + 1e-12
   rel = np.linalg.norm(got - want) / np.linalg.norm(want)
   assert np.isfinite(got).all() and rel < 2e-2, rel
+
+
+def test_final_latents_against_library_fp8_linears():
+  """Product path (fused producers, this package's quantization + tcgen05 GEMM) against the same model whose
+  FP8 linears are PyTorch library ops (`torch._scaled_mm` row-wise on torch-quantized operands) and whose block
+  glue is eager PyTorch: same cache decisions, final latents within 2e-2 relative L2 after 24 steps.  Unlike the
+  oracle-backed runs, the two arms share no FP8 arithmetic, so the error of the FP8 linears accumulating through
+  the blocks is part of what is compared."""
+  from cache_dit_b200.synthetic import FluxDenoisePipeline, FluxTransformer2DModel
+  from tests.library_fp8 import LibraryFloat8Linear, swap_repeated_block_linears
+
+  def build():
+    torch.manual_seed(0)
+    with torch.device("cuda"):
+      model = FluxTransformer2DModel(num_layers=4, num_single_layers=6, dim=256, heads=4, in_channels=16,
+                                     joint_attention_dim=64, pooled_projection_dim=32, axes_dims_rope=(8, 28, 28),
+                                     time_scale=1.0, modulation_init_std=0.02).to(torch.bfloat16)
+    inputs = FluxTransformer2DModel.example_inputs(height=256, width=256, text_tokens=16, in_channels=16,
+                                                   joint_attention_dim=64, pooled_projection_dim=32)
+    return model.eval().requires_grad_(False), inputs
+
+  def generate(library: bool):
+    model, inputs = build()
+    if library:
+      assert swap_repeated_block_linears(model) > 0
+      assert isinstance(model.transformer_blocks[0].attn.to_q, LibraryFloat8Linear)
+    pipe = FluxDenoisePipeline(model, inputs)
+    cd.enable_cache(pipe, cache_config=cd.DBCacheConfig(Fn_compute_blocks=2, max_warmup_steps=4,
+                                                        residual_diff_threshold=0.13),
+                    calibrator_config=cd.TaylorSeerCalibratorConfig(taylorseer_order=1),
+                    quantize_config=None if library else cd.QuantizeConfig(quant_type="float8_per_row"))
+    if not library:
+      assert isinstance(model.transformer_blocks[0].attn.to_q, cd.Float8RowwiseLinear)
+      assert model._quantize_stats["quantized"] > 0
+    out = pipe(num_inference_steps=24)
+    stats = cd.summary(pipe, logging=False)[-1]
+    cd.disable_cache(pipe)
+    return out.float().cpu().numpy(), stats
+
+  got, s_ours = generate(False)
+  want, s_lib = generate(True)
+  assert s_ours.cached_steps == s_lib.cached_steps and len(s_ours.cached_steps) >= 4
+  for k, v in s_lib.residual_diffs.items():
+    assert abs(s_ours.residual_diffs[k] - v) <= 2e-2 * abs(v) + 1e-12  # diffs now carry the FP8 differences too
+  rel = np.linalg.norm(got - want) / np.linalg.norm(want)
+  assert np.isfinite(got).all() and 0.0 < rel < 2e-2, rel

@@ -193,3 +193,99 @@ def test_fp8_wire_format_matches_restatement(nat, world, tokens, heads, d):
     q = FO.e4m3_round((src * inv).astype(np.float32))
     want = _bf16((q * _bf16(s)).astype(np.float32))
     np.testing.assert_array_equal(oout[r][0].float().cpu().numpy(), want)
+
+
+# ---------------------------------------------------------------------------- against the reference's own Triton kernels
+import os
+
+COMM_FIXTURE = os.path.join(os.path.dirname(__file__), "golden", "fp8_comm_reference.npz")
+
+
+@pytest.fixture(scope="module")
+def comm_fixture():
+  """Wire bytes and unpacked values that the reference's `fp8_comm_*` Triton ops produced on a B200 for small
+  seeded inputs (generator: tests/golden/make_fp8_comm_fixture.py)."""
+  import numpy as np
+  return np.load(COMM_FIXTURE)
+
+
+def _bits_to_bf16(bits):
+  import numpy as np
+  return torch.from_numpy(np.ascontiguousarray(bits).view(np.int16)).view(torch.bfloat16)
+
+
+def _codes_close(got, want):
+  """e4m3 byte codes: equal, except where the two implementations' float32 division differs in the last bits and
+  the quotient sits on a rounding boundary (then one code step apart).  Returns the mismatch fraction."""
+  import numpy as np
+  from oracle import fp8_oracle as FO
+  diff = got != want
+  if diff.any():
+    gv, wv = FO.e4m3_decode(got[diff]), FO.e4m3_decode(want[diff])
+    step = np.maximum(np.abs(gv), np.abs(wv)) * 2.0**-3 + 2.0**-9
+    assert np.all(np.abs(gv - wv) <= step), "codes differ by more than one e4m3 step"
+  return float(diff.mean())
+
+
+@pytest.mark.parametrize("case", ["w2_d64", "w4_d128", "w8_d128"])
+def test_qkv_wire_values_match_reference_triton_kernels(nat, comm_fixture, case):
+  """`cdb_scatter_heads_multi` with FP8 destinations + `cdb_fp8_dequant_heads` against the reference's
+  `fp8_comm_qkv_permute_quant` / `fp8_comm_qkv_permute_dequant` (src/cache_dit/kernels/triton/_float8_comm.py:78-148):
+  same codes and float32 scales per (token, head) for every destination rank, same unpacked bf16 values.  The byte
+  LAYOUT differs on purpose: the reference packs the scale behind each head's codes for one all-to-all message,
+  here codes and scales land in two buffers of the destination GPU."""
+  import numpy as np
+  fx = comm_fixture
+  x = _bits_to_bf16(fx[f"qkv.{case}.x"]).cuda()  # [B, S, W, N, D]
+  B, S, W, N, D = x.shape
+  wire = fx[f"qkv.{case}.wire"]  # [W, S, B, N, D + 4] bytes
+  want_codes = np.ascontiguousarray(wire[..., :D].transpose(0, 2, 1, 3, 4))  # [W, B, S, N, D]
+  want_scale = np.ascontiguousarray(wire[..., D:]).view(np.float32)[..., 0].transpose(0, 2, 1, 3)  # [W, B, S, N]
+  q8 = [torch.zeros(B * S * N * D // 4, dtype=torch.int32, device="cuda") for _ in range(W)]
+  sc = [torch.zeros(B * S * N, dtype=torch.float32, device="cuda") for _ in range(W)]
+  nat.scatter_heads_multi([dict(x=x.reshape(B, S, W * N * D), dst_ptrs=[t.data_ptr() for t in q8],
+                                dst_batch_stride=S * N * D, dst_row_offset=0,
+                                dst_scale_ptrs=[t.data_ptr() for t in sc])], W * N)
+  out = [torch.empty(B, S, N, D, dtype=torch.bfloat16, device="cuda") for _ in range(W)]
+  for w in range(W):
+    nat.fp8_dequant_heads([q8[w]], [sc[w]], [out[w]], D)
+  torch.cuda.synchronize()
+  want_deq = fx[f"qkv.{case}.dequant"]  # [W, B, S, N, D] bf16 bits
+  worst = 0.0
+  for w in range(W):
+    got_scale = sc[w].cpu().numpy().reshape(B, S, N)
+    np.testing.assert_allclose(got_scale, want_scale[w], rtol=3e-7, atol=0)  # float32 division: last-bit freedom
+    got_codes = q8[w].cpu().numpy().view(np.uint8).reshape(B, S, N, D)
+    worst = max(worst, _codes_close(got_codes, want_codes[w]))
+    same = (got_codes == want_codes[w]).all(axis=-1) & (got_scale == want_scale[w])
+    got_bits = out[w].view(torch.int16).cpu().numpy().view(np.uint16)
+    np.testing.assert_array_equal(got_bits[same], want_deq[w][same])  # identical wire values unpack identically
+  assert worst <= 1e-3, worst
+
+
+@pytest.mark.parametrize("case", ["d64", "d128"])
+def test_output_wire_values_match_reference_triton_kernels(nat, comm_fixture, case):
+  """`cdb_gather_tokens_fp8` + `cdb_fp8_dequant_heads` against the reference's `fp8_comm_per_token_quant` /
+  `fp8_comm_per_token_dequant` (src/cache_dit/kernels/triton/_float8_comm.py:5-76): codes and the bf16 scale per
+  (token, head), and the unpacked values."""
+  import numpy as np
+  fx = comm_fixture
+  x = _bits_to_bf16(fx[f"o.{case}.x"]).cuda()  # [R, D]: R (token, head) rows
+  R, D = x.shape
+  wire = fx[f"o.{case}.wire"]  # [R, D + 2]
+  want_codes = wire[:, :D]
+  want_scale_bits = np.ascontiguousarray(wire[:, D:]).view(np.uint16)[:, 0]
+  o8 = torch.zeros(R * D // 4, dtype=torch.int32, device="cuda")
+  osc = torch.zeros(R, dtype=torch.bfloat16, device="cuda")
+  nat.gather_tokens_fp8(x.reshape(1, R, 1, D), [o8.data_ptr()], [osc.data_ptr()], 0)
+  out = torch.empty(1, R, 1, D, dtype=torch.bfloat16, device="cuda")
+  nat.fp8_dequant_heads([o8], [osc], [out], D)
+  torch.cuda.synchronize()
+  got_scale_bits = osc.view(torch.int16).cpu().numpy().view(np.uint16)
+  assert np.mean(got_scale_bits != want_scale_bits) <= 0.02  # bf16 rounding of a float32 quotient with last-bit freedom
+  got_codes = o8.cpu().numpy().view(np.uint8).reshape(R, D)
+  assert _codes_close(got_codes, want_codes) <= 1e-3
+  same = (got_codes == want_codes).all(axis=-1) & (got_scale_bits == want_scale_bits)
+  got_bits = out.view(torch.int16).cpu().numpy().view(np.uint16).reshape(R, D)
+  np.testing.assert_array_equal(got_bits[same], fx[f"o.{case}.dequant"][same])
+  assert same.mean() > 0.9
