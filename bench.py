@@ -311,9 +311,13 @@ class Stepper:
       host_out.copy_(self.x, non_blocking=True)
       torch.cuda.current_stream().synchronize()
       host["latents"].copy_(host_out)
-    self.hits.append(1 if self.i in getattr(self.model, "_cached_steps", ()) else 0)
+    # this step's cache decision(s), read from the live context (the `_cached_steps` attributes of the module
+    # are only published when a generation ends)
+    ctx = self.model._context_manager.current_context
+    self.hits.append(1 if self.i in ctx.main.cached_steps else 0)
     if neg is not None:
-      self.cfg_hits.append(1 if self.i in getattr(self.model, "_cfg_cached_steps", ()) else 0)
+      self.cfg_hits.append(1 if self.i in ctx.cfg.cached_steps else 0)
+    self.diffs = ctx.main.residual_diffs
     self.i += 1
 
   def generation(self):
@@ -649,6 +653,7 @@ def run_ours(args):
   launches = nat.launch_count - launches0
   clocks = sampler.stop() if rank == 0 else {}
   hits, cfg_hits = stepper.hits[h0:], stepper.cfg_hits[c0:]
+  diffs_seen = dict(getattr(stepper, "diffs", {}))
   finite = bool(torch.isfinite(stepper.x).all().item())
   # -------- timed region 2: end to end with host buffers
   host_state = {"latents": host["hidden_states"].clone().pin_memory(),
@@ -784,7 +789,8 @@ def run_ours(args):
                "l2_policy": "inputs larger than L2: the FP8 weights of the model are streamed every computed step",
                "cuda_graphs": (not args.no_graphs), "hit_mask": mask_string(hits),
                "cfg_hit_mask": mask_string(cfg_hits) if cfg_hits else None,
-               "first_timed_step": 0, "steps_per_generation": n_gen},
+               "first_timed_step": 0, "steps_per_generation": n_gen,
+               "residual_diffs_of_last_generation": {k: round(float(v), 4) for k, v in dict(diffs_seen).items()}},
     "ms_per_step_by_kind": {k: round(sum(v) / len(v), 3) for k, v in sorted(by_kind.items())},
     "steps_by_kind": {k: len(v) for k, v in sorted(by_kind.items())},
     "ms_computed_step": round(sum(by_kind["computed"]) / len(by_kind["computed"]), 3) if "computed" in by_kind else None,

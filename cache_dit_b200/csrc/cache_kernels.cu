@@ -31,6 +31,21 @@ static int64_t resident_ctas(K kernel, int threads) {
   return (int64_t)per_sm * sm_count();
 }
 
+// CTAs of a cluster kernel that are guaranteed to be resident together (whole clusters).
+template <class K>
+static int64_t resident_cluster_ctas(K kernel, int threads, int cluster) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3((unsigned)(cluster * 4096));
+  cfg.blockDim = dim3((unsigned)threads);
+  int clusters = 0;
+  if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) == cudaSuccess && clusters >= 1)
+    return (int64_t)clusters * cluster;
+  (void)cudaGetLastError();
+  // fall back to half of the per-SM figure, rounded to whole clusters: conservative on purpose
+  const int64_t ctas = resident_ctas(kernel, threads) / 2;
+  return ctas / cluster * cluster >= cluster ? ctas / cluster * cluster : cluster;
+}
+
 // ------------------------------------------------------------------------------------------
 // relative-L1 reduction
 // ------------------------------------------------------------------------------------------
@@ -39,16 +54,24 @@ constexpr int RL_CLUSTER = 2;        // CTA pair: always fits (SMs come in TPC p
 constexpr int RL_MAX_CLUSTERS = 1024;
 constexpr int RL_UNROLL = 2;
 
-constexpr int RL_SLOTS = 16;         // accumulator slots, one 128-byte line each
+// Reduction scratch: one record per cluster = the pair's two sums as fp64 bit patterns.  A word of all-zero
+// bits means "not written yet" (a sum that is exactly zero is stored as -0.0, which has a non-zero pattern),
+// so the data is its own ready flag: writers need no fence, no atomic and no ticket, and the folding CTA
+// puts the zeros back when it has read a word, which is the state the next launch expects.
+constexpr int RL_FOLD_WORDS = 2 * RL_MAX_CLUSTERS / RL_THREADS;  // words per thread of the folding CTA
 struct RelL1Scratch {
-  unsigned int ticket;  // clusters finished in the current launch; self-resetting
-  unsigned int pad[31];
-  // fp64 accumulators of the two sums, self-resetting.  Clusters add into slot (cluster id % 16):
-  // all clusters finish within a microsecond of each other, and ~1800 atomics on one line would
-  // queue in a single L2 slice for longer than the last CTA's stream takes.
-  struct __align__(128) Slot { double sum[2]; double pad[14]; } slot[RL_SLOTS];
+  unsigned long long partial[RL_MAX_CLUSTERS][2];
 };
+constexpr unsigned long long RL_FOLD_LIMIT_NS = 2000000000ull;
 
+__device__ __forceinline__ unsigned long long ld_relaxed_u64(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_relaxed_u64(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
 template <class A, int U, bool HAS_BASE, bool HAS_PREV, bool WRITE_RES>
 __device__ __forceinline__ void rel_l1_chunk(const typename A::T* cur, const typename A::T* base,
                                              const typename A::T* prev, typename A::T* res,
@@ -75,6 +98,8 @@ __global__ void __cluster_dims__(RL_CLUSTER, 1, 1) __launch_bounds__(RL_THREADS)
                   const typename A::T* __restrict__ prev, typename A::T* __restrict__ res, int64_t n,
                   float* __restrict__ means, RelL1Scratch* __restrict__ scratch) {
   constexpr int W = U * A::N;  // elements per chunk
+  pdl_launch_dependents();
+  pdl_wait_prior();
   const int64_t nchunk = n / W;
   const int64_t stride = (int64_t)gridDim.x * RL_THREADS;
   // Two accumulators per sum, one per unrolled lane, so the adds do not serialise.
@@ -122,47 +147,75 @@ __global__ void __cluster_dims__(RL_CLUSTER, 1, 1) __launch_bounds__(RL_THREADS)
   cluster.sync();  // hardware cluster barrier: every CTA of the pair arrives exactly once
   if (rank != 0) return;
 
-  // One thread per cluster adds the pair's sums to its slot's two fp64 accumulators (each addend is an fp32
-  // value, so the order of the additions changes the fp64 total by ~1e-16 relative at most, far
-  // below the final rounding to the storage dtype), then takes a ticket.  Whoever draws the last
-  // ticket publishes the means and leaves the scratch zeroed for the next launch.  The whole tail
-  // is two L2 round trips; nothing waits on anything.
-  if (warp != 0) return;
-  const unsigned nclusters = gridDim.x / RL_CLUSTER;
-  unsigned t = 0;
-  if (lane == 0) {
+  // The pair's leader publishes its two fp64 sums with two plain 8-byte stores (single-copy atomic; the value
+  // is its own ready flag, see RelL1Scratch).  Nothing is waited for: every cluster but the first is done here.
+  const unsigned cid = blockIdx.x / RL_CLUSTER;
+  if (threadIdx.x == 0) {
     double td = 0.0, tp = 0.0;
 #pragma unroll
     for (int r = 0; r < RL_CLUSTER; ++r) {
       td += s_cta[r][0];
       tp += s_cta[r][1];
     }
-    RelL1Scratch::Slot* mine = &scratch->slot[(blockIdx.x / RL_CLUSTER) % RL_SLOTS];
-    atomicAdd(&mine->sum[0], td);
-    atomicAdd(&mine->sum[1], tp);
-    __threadfence();
-    t = atomicAdd(&scratch->ticket, 1u);
+    st_relaxed_u64(&scratch->partial[cid][0], (unsigned long long)__double_as_longlong(td == 0.0 ? -0.0 : td));
+    st_relaxed_u64(&scratch->partial[cid][1], (unsigned long long)__double_as_longlong(tp == 0.0 ? -0.0 : tp));
   }
-  t = __shfl_sync(0xffffffffu, t, 0);
-  if (t != nclusters - 1) return;
-  // last cluster: lanes 0..15 fetch-and-clear one slot each, fp64 butterfly, lane 0 publishes
-  __threadfence();
-  double sd_all = 0.0, sp_all = 0.0;
-  if (lane < RL_SLOTS) {
-    sd_all = __longlong_as_double(
-        (long long)atomicExch(reinterpret_cast<unsigned long long*>(&scratch->slot[lane].sum[0]), 0ull));
-    sp_all = __longlong_as_double(
-        (long long)atomicExch(reinterpret_cast<unsigned long long*>(&scratch->slot[lane].sum[1]), 0ull));
+  if (cid != 0) return;
+
+  // Cluster 0's leader CTA folds: its 256 threads read all records at once (one L2 round trip when the other
+  // clusters are done, which they are within a microsecond: the grid is one resident wave of equal shares),
+  // re-reading the few that are still zero.  The wait is bounded: after RL_FOLD_LIMIT_NS without a record the
+  // means are published as NaN, which no threshold comparison accepts.  The fold order is fixed (word index,
+  // then a shuffle tree), so the result does not depend on arrival order at all.
+  const unsigned words = 2 * (gridDim.x / RL_CLUSTER);
+  unsigned long long* flat = &scratch->partial[0][0];
+  unsigned long long v[RL_FOLD_WORDS];
+#pragma unroll
+  for (int k = 0; k < RL_FOLD_WORDS; ++k) {
+    const unsigned w = threadIdx.x + k * RL_THREADS;
+    v[k] = w < words ? ld_relaxed_u64(flat + w) : 1ull;
+  }
+  bool timed_out = false;
+  unsigned long long t0 = 0;
+#pragma unroll
+  for (int k = 0; k < RL_FOLD_WORDS; ++k) {
+    const unsigned w = threadIdx.x + k * RL_THREADS;
+    for (unsigned it = 0; v[k] == 0ull && !timed_out; ++it) {
+      v[k] = ld_relaxed_u64(flat + w);
+      if ((it & 63u) == 63u) {
+        unsigned long long now;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+        if (t0 == 0) t0 = now;
+        else if (now - t0 > RL_FOLD_LIMIT_NS) timed_out = true;
+      }
+    }
+  }
+  // RL_THREADS is even, so a thread's words all have its own parity: even threads hold |prev - r| sums, odd
+  // threads |prev| sums
+  double acc = 0.0;
+#pragma unroll
+  for (int k = 0; k < RL_FOLD_WORDS; ++k) {
+    const unsigned w = threadIdx.x + k * RL_THREADS;
+    if (w < words) {
+      acc += __longlong_as_double((long long)v[k]);
+      st_relaxed_u64(flat + w, 0ull);  // leave the scratch zeroed for the next launch
+    }
   }
 #pragma unroll
-  for (int o = RL_SLOTS / 2; o > 0; o >>= 1) {
-    sd_all += __shfl_xor_sync(0xffffffffu, sd_all, o);
-    sp_all += __shfl_xor_sync(0xffffffffu, sp_all, o);
-  }
-  if (lane == 0) {
-    means[0] = A::round1((float)(sd_all / (double)n));
-    means[1] = A::round1((float)(sp_all / (double)n));
-    scratch->ticket = 0;
+  for (int o = 16; o >= 2; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);  // lanes of equal parity
+  __shared__ double s_fold[RL_THREADS / 32][2];
+  __shared__ int s_timeout;
+  if (threadIdx.x == 0) s_timeout = 0;
+  __syncthreads();
+  if (lane < 2) s_fold[warp][lane] = acc;
+  if (timed_out) s_timeout = 1;
+  __syncthreads();
+  if (threadIdx.x < 2) {
+    double tot = 0.0;
+#pragma unroll
+    for (int i = 0; i < RL_THREADS / 32; ++i) tot += s_fold[i][threadIdx.x];
+    const float mean = s_timeout ? __int_as_float(0x7fc00000) : A::round1((float)(tot / (double)n));
+    means[threadIdx.x] = mean;
   }
 }
 
@@ -171,16 +224,17 @@ static int launch_rel_l1_variant(const typename A::T* c, const typename A::T* b,
                                  typename A::T* r, int64_t n, float* means, RelL1Scratch* scratch,
                                  cudaStream_t st) {
   auto kernel = rel_l1_kernel<A, A1, U, HB, HP, WR>;
+  // the folding CTA waits for the other clusters' records, so the whole grid must be resident at once:
+  // the wave is what the cluster occupancy query promises, never more
   static PerDevice wave_of;
-  const int64_t wave = wave_of.get([&] { return resident_ctas(kernel, RL_THREADS); });
+  const int64_t wave = wave_of.get([&] { return resident_cluster_ctas(kernel, RL_THREADS, RL_CLUSTER); });
   const int64_t nchunk = n / (U * A::N);
   int64_t want = (nchunk + (int64_t)RL_THREADS * RL_UNROLL - 1) / ((int64_t)RL_THREADS * RL_UNROLL);
   int64_t cap = wave < RL_MAX_CLUSTERS * RL_CLUSTER ? wave : RL_MAX_CLUSTERS * RL_CLUSTER;
   int64_t grid = want < cap ? want : cap;
   grid = grid / RL_CLUSTER * RL_CLUSTER;
   if (grid < RL_CLUSTER) grid = RL_CLUSTER;
-  kernel<<<(unsigned)grid, RL_THREADS, 0, st>>>(c, b, p, r, n, means, scratch);
-  CDB_CUDA_CHECK(cudaGetLastError());
+  CDB_CUDA_CHECK(launch_pdl(kernel, dim3((unsigned)grid), dim3(RL_THREADS), 0, st, c, b, p, r, n, means, scratch));
   return CDB_OK;
 }
 
@@ -245,6 +299,8 @@ __global__ void __launch_bounds__(EW_THREADS)
     taylor_apply_kernel(const typename A::T* __restrict__ hidden, const __grid_constant__ ApplyArgs a,
                         typename A::T* __restrict__ out, int64_t n) {
   constexpr int W = U * A::N;
+  pdl_launch_dependents();
+  pdl_wait_prior();
   const int64_t nchunk = n / W;
   const int64_t stride = (int64_t)gridDim.x * EW_THREADS;
   int64_t i = (int64_t)blockIdx.x * EW_THREADS + threadIdx.x;
@@ -296,6 +352,8 @@ __global__ void __launch_bounds__(EW_THREADS)
     taylor_update_kernel(const typename A::T* __restrict__ after, const typename A::T* __restrict__ before,
                          const __grid_constant__ UpdateArgs a, float window, float inv_window, int64_t n) {
   constexpr int W = U * A::N;
+  pdl_launch_dependents();
+  pdl_wait_prior();
   const int64_t nchunk = n / W;
   const int64_t stride = (int64_t)gridDim.x * EW_THREADS;
   int64_t i = (int64_t)blockIdx.x * EW_THREADS + threadIdx.x;
@@ -323,7 +381,7 @@ static void launch_apply_variant(const typename A::T* h, const ApplyArgs& a, typ
   const int64_t nchunk = n / (U * A::N);
   int64_t want = (nchunk + (int64_t)EW_THREADS * EW_UNROLL - 1) / ((int64_t)EW_THREADS * EW_UNROLL);
   int64_t g = want < wave ? want : wave;
-  kernel<<<(unsigned)(g < 1 ? 1 : g), EW_THREADS, 0, st>>>(h, a, o, n);
+  (void)launch_pdl(kernel, dim3((unsigned)(g < 1 ? 1 : g)), dim3(EW_THREADS), 0, st, h, a, o, n);
 }
 
 template <class A, class A1, int U>
@@ -357,7 +415,7 @@ static void launch_update_variant(const typename A::T* af, const typename A::T* 
   const int64_t nchunk = n / (U * A::N);
   int64_t want = (nchunk + (int64_t)EW_THREADS * EW_UNROLL - 1) / ((int64_t)EW_THREADS * EW_UNROLL);
   int64_t g = want < wave ? want : wave;
-  kernel<<<(unsigned)(g < 1 ? 1 : g), EW_THREADS, 0, st>>>(af, bf, a, window, 1.0f / window, n);
+  (void)launch_pdl(kernel, dim3((unsigned)(g < 1 ? 1 : g)), dim3(EW_THREADS), 0, st, af, bf, a, window, 1.0f / window, n);
 }
 
 template <class A, class A1, int U>

@@ -46,6 +46,36 @@ struct PerDevice {
   }
 };
 
+// Launch with the programmatic-stream-serialization attribute: the kernel's CTAs may be scheduled while the
+// previous kernel of the stream is still finishing (once all of ITS blocks have called
+// griddepcontrol.launch_dependents or exited), which hides the launch gap between two short kernels.  A kernel
+// launched this way must execute griddepcontrol.wait before its first access to global memory.  Works in
+// stream capture (the dependency becomes a programmatic edge of the graph).  CDB_PDL=0 turns it off.
+bool pdl_enabled();
+template <class... KArgs, class... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                              Args... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+#ifdef __CUDACC__
+// Device side of programmatic dependent launch: let the next kernel of the stream be scheduled while this one
+// runs, and wait for the previous kernel (and its memory) before touching global memory.  Both are no-ops for a
+// launch without the programmatic-serialization attribute.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait_prior() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+#endif
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // ---- storage-dtype arithmetic policies ------------------------------------------------------

@@ -22,6 +22,7 @@
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
 
+#include <atomic>
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
@@ -182,7 +183,9 @@ __device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
 // Instruction descriptor, kind::f8f6f4: D = fp32, A = B = e4m3, both K-major, dense.
 //   bits [4,6) D format (1 = f32)   [7,10) A format (0 = e4m3)   [10,13) B format (0 = e4m3)
 //   bit 15 / 16 A / B major (0 = K) [17,23) N >> 3               [24,29) M >> 4
-constexpr uint32_t IDESC_E4M3_F32 = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+constexpr uint32_t idesc_e4m3_f32(int m, int n) {
+  return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
 
 // AND-reduction of a predicate over the 128 epilogue threads (named barrier 1).
 __device__ __forceinline__ bool epi_all(bool pred) {
@@ -218,20 +221,49 @@ __device__ __forceinline__ void bulk_wait_group_read() {
 __device__ __forceinline__ void bulk_wait_group_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
-// One epilogue warp's share of a tile: 32 accumulator rows (TMEM lanes) x BN columns.  Per block of
+// One epilogue warp's share of a tile: 32 accumulator rows (TMEM lanes) x `bn` columns.  Per block of
 // 64 columns: two tcgen05.ld, scale + bias, bf16 pack, 16-byte shared stores at the 128-byte-swizzled
 // position (chunk ^ (row % 8)): conflict-free, then one TMA store.  The tensor map clips rows >= M
 // and columns >= N.  `blocks_done` counts this warp's stores so the two staging blocks alternate.
-__device__ __forceinline__ void epilogue_rows(const CUtensorMap* map_out, uint8_t* staging, uint32_t taddr, float rs,
+// A tile width that is not a multiple of 64 leaves a last block of 16, 32 or 48 columns: a 64-column TMA
+// store would spill into the neighbouring tile's columns, so that block goes out as 16-byte global stores
+// straight from the registers.
+__device__ __forceinline__ void epilogue_rows(const CUtensorMap* map_out, __nv_bfloat16* out, int64_t ld_out,
+                                              uint8_t* staging, uint32_t taddr, float rs,
                                               const float* s_colscale, const __nv_bfloat16* s_bias, int row0,
-                                              int n0, int M, int N, int lane, uint32_t& blocks_done) {
+                                              int n0, int M, int N, int bn, int lane, uint32_t& blocks_done) {
   if (row0 >= M) return;  // the whole 32-row slice is padding
 #pragma unroll 1
-  for (int cblk = 0; cblk < BN; cblk += OUT_BOX_COLS) {
+  for (int cblk = 0; cblk < bn; cblk += OUT_BOX_COLS) {
     if (n0 + cblk >= N) break;
+    const int valid = min(OUT_BOX_COLS, bn - cblk);  // warp-uniform
     uint32_t acc[2][32];
     tmem_ld_32x32b_x32(taddr + cblk, acc[0]);
-    tmem_ld_32x32b_x32(taddr + cblk + 32, acc[1]);
+    if (valid > 32) tmem_ld_32x32b_x32(taddr + cblk + 32, acc[1]);
+    if (valid < OUT_BOX_COLS) {
+      tmem_ld_wait();
+      const int row = row0 + lane;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const int cb = cblk + h * 32 + g * 8;
+          if (h * 32 + g * 8 < valid && n0 + cb < N && row < M) {
+            uint32_t w[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int c = cb + 2 * j;
+              const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(s_bias + c));
+              const float v0 = __uint_as_float(acc[h][g * 8 + 2 * j]) * rs * s_colscale[c] + b.x;
+              const float v1 = __uint_as_float(acc[h][g * 8 + 2 * j + 1]) * rs * s_colscale[c + 1] + b.y;
+              w[j] = pack_bf16x2(v0, v1);
+            }
+            *reinterpret_cast<uint4*>(out + (int64_t)row * ld_out + n0 + cb) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+      }
+      continue;
+    }
     uint8_t* block = staging + (blocks_done & 1u) * OUT_BLOCK_BYTES;
     if (lane == 0) bulk_wait_group_read<1>();  // the store that used this block two blocks ago is done reading
     __syncwarp();
@@ -275,9 +307,16 @@ struct GemmProblem {
   const float* sa;
   const float* sw;
   const __nv_bfloat16* bias;
+  __nv_bfloat16* out;  // for the ragged last column block of a tile (see epilogue_rows)
+  int64_t ld_out;
   int M, N, K;
   int m_tiles, n_tiles, k_blocks, group_m;
   int tile_begin;  // index of this problem's first tile in the launch's tile sequence
+  // Tile width in columns: a multiple of 16 up to BN, chosen on the host so that the tile count fills whole
+  // waves of SMs (single-CTA kernel; the CTA-pair kernel always uses BN).  `idesc` is the instruction
+  // descriptor for that width.
+  int bn;
+  uint32_t idesc;
 };
 struct GemmProblems {
   GemmProblem p[MAX_PROBLEMS];
@@ -321,6 +360,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int num_tiles = ps.num_tiles;
+  pdl_launch_dependents();  // a following kernel launched as a programmatic dependent may be scheduled early
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -361,7 +401,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         const int k_blocks = pr->k_blocks;
         int mi, ni;
         tile_coords(local, pr->m_tiles, pr->n_tiles, pr->group_m, mi, ni);
-        const int m0 = mi * BM, n0 = ni * BN;
+        const int m0 = mi * BM, n0 = ni * pr->bn;
+        const uint32_t stage_tx = A_STAGE_BYTES + (uint32_t)pr->bn * BK;  // the weight box has `bn` rows
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
@@ -369,7 +410,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
           if (!ok) break;
           uint8_t* a_dst = smem + s * STAGE_BYTES;
           uint8_t* b_dst = a_dst + A_STAGE_BYTES;
-          mbar_expect_tx(&gb->full[s], STAGE_BYTES);
+          mbar_expect_tx(&gb->full[s], stage_tx);
           tma_load_2d(&pr->map_a, &gb->full[s], a_dst, kb * BK, m0);
           tma_load_2d(&pr->map_w, &gb->full[s], b_dst, kb * BK, n0);
         }
@@ -400,7 +441,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         tcgen05_fence_after();
         const uint32_t tmem_d = tmem_base + buf * BN;
         int local;
-        const int k_blocks = problem_of(ps, tile, local)->k_blocks;
+        const GemmProblem* pr = problem_of(ps, tile, local);
+        const int k_blocks = pr->k_blocks;
+        const uint32_t idesc = pr->idesc;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
@@ -415,7 +458,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
           for (int k = 0; k < BK / UMMA_K; ++k) {
             // advance 32 bytes along K inside the swizzle span: +2 in the (addr >> 4) field
             umma_f8(tmem_d, adesc + (uint64_t)(k * (UMMA_K >> 4)), bdesc + (uint64_t)(k * (UMMA_K >> 4)),
-                    IDESC_E4M3_F32, (kb | k) != 0 ? 1u : 0u);
+                    idesc, (kb | k) != 0 ? 1u : 0u);
           }
           tcgen05_commit(&gb->empty[s]);  // frees the stage once these MMAs retire
         }
@@ -438,12 +481,13 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       const __nv_bfloat16* bias = pr->bias;
       int mi, ni;
       tile_coords(local, pr->m_tiles, pr->n_tiles, pr->group_m, mi, ni);
-      const int m0 = mi * BM, n0 = ni * BN;
+      const int bn = pr->bn;
+      const int m0 = mi * BM, n0 = ni * bn;
       const uint32_t buf = local_tile & 1u;
       const uint32_t use = local_tile >> 1;
       // (1) the previous tile's readers of the staged column scales are done
       asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
-      for (int c = et; c < BN; c += EPI_THREADS) {
+      for (int c = et; c < bn; c += EPI_THREADS) {
         const int col = n0 + c;
         s_colscale[c] = col < N ? __ldg(sw + col) : 0.f;
         s_bias[c] = (bias != nullptr && col < N) ? bias[col] : __float2bfloat16(0.f);
@@ -458,8 +502,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       const int row = m0 + quarter * 32 + lane;
       const float rs = row < M ? __ldg(sa + row) : 0.f;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
-      epilogue_rows(&pr->map_out, s_staging + quarter * 2 * OUT_BLOCK_BYTES, taddr, rs, s_colscale, s_bias,
-                    m0 + quarter * 32, n0, M, N, lane, blocks_done);
+      epilogue_rows(&pr->map_out, pr->out, pr->ld_out, s_staging + quarter * 2 * OUT_BLOCK_BYTES, taddr, rs,
+                    s_colscale, s_bias, m0 + quarter * 32, n0, M, N, bn, lane, blocks_done);
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&gb->acc_empty[buf]);
@@ -504,8 +548,7 @@ constexpr int P_SMEM_TILE_BYTES = P_STAGES * P_STAGE_BYTES;
 constexpr int P_SMEM_TOTAL_BYTES =
     1024 + P_SMEM_TILE_BYTES + OUT_STAGING_BYTES + BN * 4 + BN * 2 + (int)sizeof(PairBarriers);
 static_assert(P_SMEM_TOTAL_BYTES <= 232448, "exceeds the 227 KB of shared memory a CTA can opt in to");
-constexpr uint32_t IDESC_E4M3_F32_M256 =
-    (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(P_BM >> 4) << 24);
+constexpr uint32_t IDESC_E4M3_F32_M256 = idesc_e4m3_f32(P_BM, BN);
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -581,6 +624,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
   const int num_tiles = ps.num_tiles;
   const int pair_id = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
+  pdl_launch_dependents();  // a following kernel launched as a programmatic dependent may be scheduled early
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < P_STAGES; ++s) {
@@ -723,8 +767,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
       const int row = m0 + quarter * 32 + lane;
       const float rs = row < M ? __ldg(sa + row) : 0.f;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
-      epilogue_rows(&pr->map_out, s_staging + quarter * 2 * OUT_BLOCK_BYTES, taddr, rs, s_colscale, s_bias,
-                    m0 + quarter * 32, n0, M, N, lane, blocks_done);
+      epilogue_rows(&pr->map_out, pr->out, pr->ld_out, s_staging + quarter * 2 * OUT_BLOCK_BYTES, taddr, rs,
+                    s_colscale, s_bias, m0 + quarter * 32, n0, M, N, BN, lane, blocks_done);
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&gb->acc_empty[buf]), 0));
@@ -947,6 +991,55 @@ static int check_problem(const cdb_gemm_problem_abi& g) {
   return CDB_OK;
 }
 
+// Tuning / testing knob: a fixed tile width (0 = choose by the cost model).  Initialised from CDB_GEMM_BN.
+static std::atomic<int> g_forced_tile_cols{[] {
+  const char* env = getenv("CDB_GEMM_BN");
+  const int v = env ? atoi(env) : 0;
+  return (v >= 16 && v <= BN && v % 16 == 0) ? v : 0;
+}()};
+
+extern "C" int cdb_tuning_set_gemm_tile_cols(int cols) {
+  if (cols != 0 && (cols < 16 || cols > BN || cols % 16 != 0)) return CDB_ERR_BAD_ARGUMENT;
+  g_forced_tile_cols.store(cols, std::memory_order_relaxed);
+  return CDB_OK;
+}
+
+// Tile width of the single-CTA kernel for one launch.  With 128-row tiles a rank shard of a context-parallel
+// run has only 3-18 row tiles, and at the full width of 256 columns the tile count often leaves most of the
+// last wave idle (576 x 3072: 60 tiles on 148 SMs; 576 x 9216: 180 tiles = 1.2 waves).  A narrower tile costs
+// operand bandwidth per flop (the A tile is re-read for fewer columns) but fills the waves, so the width is the
+// multiple of 16 that minimises a small cost model:
+//     waves x (K blocks x cycles per K block + epilogue) with
+//     cycles per K block = max(tensor time 2 x bn, operand bytes (16 KB + 128 x bn) / ~100 bytes per clock).
+// The full width wins ties and anything within 3 %, so tall problems keep the shape they were tuned with.
+static int choose_tile_cols(const cdb_gemm_problem_abi* g, int n, int sms) {
+  const int forced = g_forced_tile_cols.load(std::memory_order_relaxed);
+  if (forced) return forced;
+  auto cost_of = [&](int bn) {
+    int64_t tiles = 0;
+    double per_tile = 0.0;
+    for (int i = 0; i < n; ++i) {
+      const int64_t mt = (g[i].M + BM - 1) / BM, nt = (g[i].N + bn - 1) / bn, kb = (g[i].K + BK - 1) / BK;
+      tiles += mt * nt;
+      const double tensor = 2.0 * bn, ingest = (A_STAGE_BYTES + 128.0 * bn) / 100.0;
+      const double t = kb * (tensor > ingest ? tensor : ingest) + 150.0 * ((bn + 63) / 64);
+      per_tile = t > per_tile ? t : per_tile;
+    }
+    const int64_t waves = (tiles + sms - 1) / sms;
+    return waves * per_tile + 3000.0;
+  };
+  int best = BN;
+  double best_cost = 0.97 * cost_of(BN);
+  for (int bn = BN - 16; bn >= 64; bn -= 16) {
+    const double c = cost_of(bn);
+    if (c < best_cost) {
+      best = bn;
+      best_cost = c;
+    }
+  }
+  return best;
+}
+
 static int launch_few_rows(const cdb_gemm_problem_abi& g, int sms, cudaStream_t st) {
   const uint8_t* ap = static_cast<const uint8_t*>(g.a_q);
   const uint8_t* wp = static_cast<const uint8_t*>(g.w_q);
@@ -1004,12 +1097,13 @@ extern "C" int cdb_fp8_gemm_rowscaled_grouped(const void* problems_v, int count,
   // 1152, 576) the single-CTA kernel's 128-row tiles waste less and measured 4-25 % faster
   const bool pair = mode == 2 || (mode == 0 && g[0].M >= 4096 && CDB_GEMM_DEFAULT_PAIR);
   const int64_t tile_rows = pair ? P_BM : BM;
+  const int bn = pair ? BN : choose_tile_cols(g, n, sms);
   GemmProblems ps{};
   ps.count = n;
   int64_t tiles = 0;
   for (int i = 0; i < n; ++i) {
     GemmProblem& o = ps.p[i];
-    const uint32_t a_box = pair ? 128 : BM, w_box = pair ? 128 : BN;
+    const uint32_t a_box = pair ? 128 : BM, w_box = pair ? 128 : (uint32_t)bn;
     if (!operand_map(&o.map_a, g[i].a_q, (uint64_t)g[i].M, (uint64_t)g[i].K, a_box) ||
         !operand_map(&o.map_w, g[i].w_q, (uint64_t)g[i].N, (uint64_t)g[i].K, w_box) ||
         !output_map(&o.map_out, g[i].out, (uint64_t)g[i].M, (uint64_t)g[i].N, (uint64_t)g[i].ld_out)) {
@@ -1023,7 +1117,11 @@ extern "C" int cdb_fp8_gemm_rowscaled_grouped(const void* problems_v, int count,
     o.N = (int)g[i].N;
     o.K = (int)g[i].K;
     o.m_tiles = (int)((g[i].M + tile_rows - 1) / tile_rows);
-    o.n_tiles = (int)((g[i].N + BN - 1) / BN);
+    o.out = static_cast<__nv_bfloat16*>(g[i].out);
+    o.ld_out = g[i].ld_out;
+    o.bn = bn;
+    o.idesc = idesc_e4m3_f32(BM, bn);
+    o.n_tiles = (int)((g[i].N + bn - 1) / bn);
     o.k_blocks = (int)((g[i].K + BK - 1) / BK);
     o.group_m = tile_group_rows(o.m_tiles);
     o.tile_begin = (int)tiles;

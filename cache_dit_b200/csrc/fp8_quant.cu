@@ -95,6 +95,8 @@ __global__ void __launch_bounds__(Q_CTA)
     fp8_quant_rows_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int cols, int64_t ld_x,
                           const QuantFuse f, uint8_t* __restrict__ q, float* __restrict__ scale) {
   constexpr int RPC = Q_CTA / TPR;  // rows per CTA and iteration
+  pdl_launch_dependents();
+  pdl_wait_prior();
   __shared__ float s_red[3][Q_CTA / 32];
   int slot = 0;
   const int npack = cols >> 3;
@@ -303,16 +305,17 @@ template <int TPR, int VPT, int PREOP>
 static void launch_quant_variant(const __nv_bfloat16* xp, int64_t rows, int cols, int64_t ld_x, const QuantFuse& f,
                                  uint8_t* qp, float* scale, cudaStream_t st) {
   auto kernel = fp8_quant_rows_kernel<TPR, VPT, PREOP>;
-  static int per_sm = 0;
-  if (per_sm == 0) {
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, Q_CTA, 0) != cudaSuccess || per_sm < 1)
-      per_sm = 1;
-  }
+  static PerDevice per_sm_of;
+  const int64_t per_sm = per_sm_of.get([&]() -> int64_t {
+    int v = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&v, kernel, Q_CTA, 0) != cudaSuccess || v < 1) v = 1;
+    return v;
+  });
   constexpr int RPC = Q_CTA / TPR;
   const int64_t want = (rows + RPC - 1) / RPC;
   const int64_t wave = (int64_t)per_sm * sm_count();
   const unsigned grid = (unsigned)(want < wave ? want : wave);
-  kernel<<<grid, Q_CTA, 0, st>>>(xp, rows, cols, ld_x, f, qp, scale);
+  (void)launch_pdl(kernel, dim3(grid), dim3(Q_CTA), 0, st, xp, rows, cols, ld_x, f, qp, scale);
 }
 
 template <int PREOP>

@@ -21,6 +21,8 @@ __global__ void __launch_bounds__(256)
     gated_residual_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ y, int64_t ld_y,
                           const __nv_bfloat16* __restrict__ gate, int64_t ld_gate, __nv_bfloat16* __restrict__ out,
                           int64_t rows, int64_t rows_per_batch, int cols) {
+  pdl_launch_dependents();
+  pdl_wait_prior();
   const int packs = cols >> 3;
   const int64_t total = rows * packs;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
@@ -52,6 +54,8 @@ struct GatedJobs {
   GatedJob job[2];
 };
 __global__ void __launch_bounds__(256) gated_residual_pair_kernel(const __grid_constant__ GatedJobs jobs, int cols) {
+  pdl_launch_dependents();
+  pdl_wait_prior();
   const GatedJob& j = jobs.job[blockIdx.y];
   const int packs = cols >> 3;
   const int64_t total = j.rows * packs;
@@ -105,11 +109,10 @@ extern "C" int cdb_gated_residual(const void* x, const void* y, int64_t ld_y, co
   const int64_t total = rows * (cols / 8);
   int64_t blocks = (total + 255) / 256;
   const int64_t cap = (int64_t)sm_count() * 8;
-  gated_residual_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(y), ld_y,
-      static_cast<const __nv_bfloat16*>(gate), ld_gate, static_cast<__nv_bfloat16*>(out), rows, rows_per_batch,
-      (int)cols);
-  CDB_CUDA_CHECK(cudaGetLastError());
+  CDB_CUDA_CHECK(launch_pdl(gated_residual_kernel, dim3((unsigned)(blocks < cap ? blocks : cap)), dim3(256), 0,
+                            static_cast<cudaStream_t>(stream), static_cast<const __nv_bfloat16*>(x),
+                            static_cast<const __nv_bfloat16*>(y), ld_y, static_cast<const __nv_bfloat16*>(gate), ld_gate,
+                            static_cast<__nv_bfloat16*>(out), rows, rows_per_batch, (int)cols));
   return CDB_OK;
 }
 
@@ -136,7 +139,7 @@ extern "C" int cdb_gated_residual_pair(const void* x, const void* y, int64_t ld_
   const int64_t blocks = (big + 255) / 256;
   const int64_t cap = (int64_t)sm_count() * 8;
   const dim3 grid((unsigned)(blocks < cap ? blocks : cap), 2);
-  gated_residual_pair_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(jobs, (int)cols);
-  CDB_CUDA_CHECK(cudaGetLastError());
+  CDB_CUDA_CHECK(launch_pdl(gated_residual_pair_kernel, grid, dim3(256), 0, static_cast<cudaStream_t>(stream), jobs,
+                            (int)cols));
   return CDB_OK;
 }

@@ -1,5 +1,6 @@
 // Library-wide plumbing of the C ABI: version, status text, error capture, device queries.
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "common.cuh"
@@ -14,6 +15,14 @@ void set_cuda_error(cudaError_t e, const char* where) {
 }
 
 void set_error_text(const char* text) { snprintf(g_cuda_error, sizeof(g_cuda_error), "%s", text ? text : ""); }
+
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* env = getenv("CDB_PDL");
+    return !(env && env[0] == '0');
+  }();
+  return on;
+}
 
 int sm_count() {
   static int cached[64];

@@ -62,7 +62,9 @@ CDB_API const char* cdb_last_cuda_error(void);
  * all-reduces (cache_manager.py:612-614) and then divides (cache_manager.py:619).
  * `scratch` is device memory of at least cdb_rel_l1_scratch_bytes() bytes, 128-byte aligned, that
  * must be zero-filled once before its first use; the kernel leaves it zeroed for the next launch.
- * Launches that share one scratch buffer must be ordered on one stream.
+ * Launches that share one scratch buffer must be ordered on one stream.  One CTA of the launch collects
+ * the other clusters' partial sums from the scratch with a bounded wait (2 s); should that wait ever
+ * run out, both means are NaN.
  * ---------------------------------------------------------------------------------------- */
 CDB_API size_t cdb_rel_l1_scratch_bytes(void);
 CDB_API int cdb_rel_l1(const void* cur, const void* base, const void* prev, void* residual_out,
@@ -77,7 +79,7 @@ CDB_API int cdb_rel_l1(const void* cur, const void* base, const void* prev, void
  *
  * Same arithmetic and outputs as cdb_rel_l1 with `prev` given (means[0], means[1], optional
  * residual_out); the reduction scratch is a fixed array inside the library's device image
- * (cdb_rel_l1_scratch_bytes() = 2176 bytes per GPU that loads the library, held until the process exits).
+ * (cdb_rel_l1_scratch_bytes() = 16384 bytes per GPU that loads the library, held until the process exits).
  *   - The device that owns the tensors must be the current device of the calling thread: the array
  *     exists once per device and the current device's copy is used.  A `cur` that is not device memory
  *     of the current device returns CDB_ERR_BAD_ARGUMENT.
@@ -199,6 +201,12 @@ CDB_API int cdb_fp8_gemm_rowscaled(const void* a_q, const float* a_scale, const 
                            const float* w_scale, const void* bias, void* out, int64_t M,
                            int64_t N, int64_t K, int64_t ld_out, int32_t* status_word,
                            void* stream);
+
+/* Tuning knob (no counterpart in the reference): the single-CTA tile kernel (M < 4096) picks its tile width,
+ * a multiple of 16 columns up to 256, from a cost model so that the tiles fill whole waves of SMs; a non-zero
+ * `cols` fixes the width for every later launch of the process, 0 restores the model.  The environment variable
+ * CDB_GEMM_BN sets the initial value.  Results do not depend on the width (bitwise). */
+CDB_API int cdb_tuning_set_gemm_tile_cols(int cols);
 
 /* ------------------------------------------------------------------------------------------
  * Transformer-block glue between the FP8 linears.  No counterpart in the reference: there these

@@ -241,6 +241,43 @@ def test_fp8_gemm_matches_oracle(nat, M, N, K, bias):
   assert rel_fro(got, ref) < 8e-2
 
 
+@pytest.mark.parametrize("M,N,K,bias", [(576, 3072, 3072, True), (576, 9216, 1024, False), (70, 1000, 256, True),
+                                        (1152, 3080, 512, False)])
+def test_fp8_gemm_result_is_independent_of_the_tile_width(nat, M, N, K, bias):
+  """The single-CTA kernel picks its tile width (a multiple of 16 columns) so that tiles fill whole waves of
+  SMs.  Every width must give the bits the full width gives: widths that end on a 64-column store boundary,
+  widths with a ragged last block of 16 / 32 / 48 columns (written with plain stores), N not a multiple of
+  the width, a strided output, and what the cost model itself picks."""
+  x_d, _ = activations(M, K, M + K)
+  w_d, _ = activations(N, K, N + K)
+  g = torch.Generator().manual_seed(5)
+  b = torch.randn(N, generator=g).to(torch.bfloat16).cuda() if bias else None
+  aq = torch.empty(M, K, dtype=torch.float8_e4m3fn, device="cuda")
+  sa = torch.empty(M, dtype=torch.float32, device="cuda")
+  wq = torch.empty(N, K, dtype=torch.float8_e4m3fn, device="cuda")
+  sw = torch.empty(N, dtype=torch.float32, device="cuda")
+  nat.fp8_quant_rows(x_d, aq, sa)
+  nat.fp8_quant_rows(w_d, wq, sw)
+  lib = nat.lib()
+  try:
+    assert lib.cdb_tuning_set_gemm_tile_cols(256) == 0
+    want = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    nat.fp8_gemm_rowscaled(aq, sa, wq, sw, b, want)
+    torch.cuda.synchronize()
+    assert torch.isfinite(want).all()
+    for cols in (0, 16, 64, 80, 96, 112, 128, 160, 176, 192, 208, 224, 240):
+      assert lib.cdb_tuning_set_gemm_tile_cols(cols) == 0
+      wide = torch.full((M, N + 24), float("nan"), dtype=torch.bfloat16, device="cuda")
+      nat.fp8_gemm_rowscaled(aq, sa, wq, sw, b, wide[:, 8:8 + N])
+      torch.cuda.synchronize()
+      assert torch.equal(wide[:, 8:8 + N], want), cols
+      assert torch.isnan(wide[:, :8]).all() and torch.isnan(wide[:, 8 + N:]).all(), cols  # nothing written outside
+    assert lib.cdb_tuning_set_gemm_tile_cols(24) != 0 and lib.cdb_tuning_set_gemm_tile_cols(272) != 0
+  finally:
+    lib.cdb_tuning_set_gemm_tile_cols(0)
+  assert nat.gemm_device_status(want.device) == 0
+
+
 def test_fp8_gemm_strided_output_and_back_to_back(nat):
   M, N, K = 256, 512, 256
   x_d, _ = activations(M, K, 1)
