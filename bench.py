@@ -688,6 +688,41 @@ def run_ours(args):
   gemm_ms = sum(s.elapsed_time(e) for s, e, _ in records)
   gemm_flops = sum(f for _, _, f in records)
 
+  # -------- optional: per-kernel time table of this rank (CUPTI activity records through torch.profiler; not ncu:
+  # a profiler that serialises one rank's kernels would let the peers' bounded waits run out)
+  if args.profile_launches:
+    from torch.profiler import ProfilerActivity, profile
+    for r in runners:
+      r.enabled = False
+    stepper.at_generation_start()
+    for _ in range(3):
+      stepper.step()
+    torch.cuda.synchronize()
+    barrier()
+    prof = profile(activities=[ProfilerActivity.CUDA]) if rank == 0 else None
+    if prof is not None:
+      prof.__enter__()
+    profiled = 0
+    while profiled < 2 or (stepper.hits[-1] == 0 and profiled < n_gen - 4):  # two computed steps, then up to the first hit
+      stepper.step()
+      profiled += 1
+    torch.cuda.synchronize()
+    if prof is not None:
+      prof.__exit__(None, None, None)
+      rows = sorted(((e.key, e.count, e.device_time_total) for e in prof.key_averages() if e.device_time_total > 0),
+                    key=lambda r_: -r_[2])
+      total = sum(r_[2] for r_ in rows)
+      os.makedirs(os.path.dirname(os.path.abspath(args.profile_launches)), exist_ok=True)
+      with open(args.profile_launches, "w") as f:
+        f.write(f"# per-kernel device time, rank 0 of {world}, config {wl.name}, {profiled} eager steps "
+                f"(hits: {mask_string(stepper.hits[-profiled:])}); total {total / 1e3:.3f} ms\n")
+        f.write("| kernel | launches | total ms | share % | avg us |\n|---|---|---|---|---|\n")
+        for name, cnt, t in rows[:40]:
+          f.write(f"| `{name[:100]}` | {cnt} | {t / 1e3:.3f} | {100 * t / total:.1f} | {t / cnt:.2f} |\n")
+    for r in runners:
+      r.enabled = True
+    barrier()
+
   # -------- self-checks: latched status words of the bounded device-side waits, finite latents, hit mask
   box = nat.device_mailbox(device).cpu()
   check = torch.tensor([float(box[nat.MAILBOX_GEMM_STATUS] != 0), float(box[nat.MAILBOX_PEER_STATUS] != 0),
@@ -1027,6 +1062,8 @@ def main():
                   help="bracket the first timed region with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
   ap.add_argument("--skip-extras", action="store_true",
                   help="leave out the cache-kernel microbenchmarks, the FP8 sweep, the library peak and the CPU sample")
+  ap.add_argument("--profile-launches", default="", metavar="FILE",
+                  help="after the timed regions, write rank 0's per-kernel device-time table (torch.profiler, eager steps) to FILE")
   ap.add_argument("--small-case", action="store_true", help="launch every kernel twice on small inputs and exit (for ncu)")
   args = ap.parse_args()
   if args.small_case:

@@ -13,6 +13,7 @@
 // hardware ops.
 #include <cooperative_groups.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -37,6 +38,13 @@ static int64_t resident_cluster_ctas(K kernel, int threads, int cluster) {
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3((unsigned)(cluster * 4096));
   cfg.blockDim = dim3((unsigned)threads);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)cluster;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
   int clusters = 0;
   if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) == cudaSuccess && clusters >= 1)
     return (int64_t)clusters * cluster;
@@ -50,7 +58,8 @@ static int64_t resident_cluster_ctas(K kernel, int threads, int cluster) {
 // relative-L1 reduction
 // ------------------------------------------------------------------------------------------
 constexpr int RL_THREADS = 256;
-constexpr int RL_CLUSTER = 2;        // CTA pair: always fits (SMs come in TPC pairs)
+constexpr int RL_CLUSTER = 2;        // default cluster: a CTA pair always fits (SMs come in TPC pairs)
+constexpr int RL_CLUSTER_MAX = 8;    // largest cluster the kernel's shared buffers allow (CDB_RL_CLUSTER = 1, 2, 4, 8)
 constexpr int RL_MAX_CLUSTERS = 1024;
 constexpr int RL_UNROLL = 2;
 
@@ -93,7 +102,7 @@ __device__ __forceinline__ void rel_l1_chunk(const typename A::T* cur, const typ
 
 // A = vector policy with U units per 16 bytes, A1 = its one-element twin for the ragged tail.
 template <class A, class A1, int U, bool HAS_BASE, bool HAS_PREV, bool WRITE_RES>
-__global__ void __cluster_dims__(RL_CLUSTER, 1, 1) __launch_bounds__(RL_THREADS)
+__global__ void __launch_bounds__(RL_THREADS)
     rel_l1_kernel(const typename A::T* __restrict__ cur, const typename A::T* __restrict__ base,
                   const typename A::T* __restrict__ prev, typename A::T* __restrict__ res, int64_t n,
                   float* __restrict__ means, RelL1Scratch* __restrict__ scratch) {
@@ -124,14 +133,16 @@ __global__ void __cluster_dims__(RL_CLUSTER, 1, 1) __launch_bounds__(RL_THREADS)
   float d = warp_sum(sd[0] + sd[1]);
   float p = warp_sum(sp[0] + sp[1]);
   __shared__ float s_warp[RL_THREADS / 32][2];  // RL_THREADS / 32 <= 32 warps
-  __shared__ double s_cta[RL_CLUSTER][2];  // only rank 0's copy is read; slot r is written by rank r
+  __shared__ double s_cta[RL_CLUSTER_MAX][2];  // only rank 0's copy is read; slot r is written by rank r
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if (lane == 0) {
     s_warp[warp][0] = d;
     s_warp[warp][1] = p;
   }
   __syncthreads();
+  // The cluster size is a launch attribute (1 = no clusters): the kernel adapts to what it was launched with.
   cg::cluster_group cluster = cg::this_cluster();
+  const unsigned csize = cluster.num_blocks();
   const unsigned rank = cluster.block_rank();
   if (warp == 0) {
     float bd = lane < RL_THREADS / 32 ? s_warp[lane][0] : 0.f;
@@ -139,21 +150,20 @@ __global__ void __cluster_dims__(RL_CLUSTER, 1, 1) __launch_bounds__(RL_THREADS)
     bd = warp_sum(bd);
     bp = warp_sum(bp);
     if (lane == 0) {
-      double* dst = cluster.map_shared_rank(&s_cta[0][0], 0);  // rank 0's copy of s_cta
+      double* dst = csize > 1 ? cluster.map_shared_rank(&s_cta[0][0], 0) : &s_cta[0][0];  // rank 0's copy of s_cta
       dst[rank * 2 + 0] = (double)bd;
       dst[rank * 2 + 1] = (double)bp;
     }
   }
-  cluster.sync();  // hardware cluster barrier: every CTA of the pair arrives exactly once
+  if (csize > 1) cluster.sync();  // hardware cluster barrier: every CTA of the cluster arrives exactly once
   if (rank != 0) return;
 
   // The pair's leader publishes its two fp64 sums with two plain 8-byte stores (single-copy atomic; the value
   // is its own ready flag, see RelL1Scratch).  Nothing is waited for: every cluster but the first is done here.
-  const unsigned cid = blockIdx.x / RL_CLUSTER;
+  const unsigned cid = blockIdx.x / csize;
   if (threadIdx.x == 0) {
     double td = 0.0, tp = 0.0;
-#pragma unroll
-    for (int r = 0; r < RL_CLUSTER; ++r) {
+    for (unsigned r = 0; r < csize; ++r) {
       td += s_cta[r][0];
       tp += s_cta[r][1];
     }
@@ -167,7 +177,7 @@ __global__ void __cluster_dims__(RL_CLUSTER, 1, 1) __launch_bounds__(RL_THREADS)
   // re-reading the few that are still zero.  The wait is bounded: after RL_FOLD_LIMIT_NS without a record the
   // means are published as NaN, which no threshold comparison accepts.  The fold order is fixed (word index,
   // then a shuffle tree), so the result does not depend on arrival order at all.
-  const unsigned words = 2 * (gridDim.x / RL_CLUSTER);
+  const unsigned words = 2 * (gridDim.x / csize);
   unsigned long long* flat = &scratch->partial[0][0];
   unsigned long long v[RL_FOLD_WORDS];
 #pragma unroll
@@ -219,22 +229,36 @@ __global__ void __cluster_dims__(RL_CLUSTER, 1, 1) __launch_bounds__(RL_THREADS)
   }
 }
 
+// Cluster size of the reduction (CDB_RL_CLUSTER = 1, 2, 4 or 8; default RL_CLUSTER).
+static int rel_l1_cluster() {
+  static const int c = [] {
+    const char* env = getenv("CDB_RL_CLUSTER");
+    const int v = env ? atoi(env) : RL_CLUSTER;
+    return (v == 1 || v == 2 || v == 4 || v == 8) ? v : RL_CLUSTER;
+  }();
+  return c;
+}
+
 template <class A, class A1, int U, bool HB, bool HP, bool WR>
 static int launch_rel_l1_variant(const typename A::T* c, const typename A::T* b, const typename A::T* p,
                                  typename A::T* r, int64_t n, float* means, RelL1Scratch* scratch,
                                  cudaStream_t st) {
   auto kernel = rel_l1_kernel<A, A1, U, HB, HP, WR>;
+  const int cluster = HP ? rel_l1_cluster() : 1;  // without a reduction there is nothing to share
   // the folding CTA waits for the other clusters' records, so the whole grid must be resident at once:
-  // the wave is what the cluster occupancy query promises, never more
+  // the wave is what the occupancy query promises, never more
   static PerDevice wave_of;
-  const int64_t wave = wave_of.get([&] { return resident_cluster_ctas(kernel, RL_THREADS, RL_CLUSTER); });
+  const int64_t wave = wave_of.get([&] {
+    return cluster > 1 ? resident_cluster_ctas(kernel, RL_THREADS, cluster) : resident_ctas(kernel, RL_THREADS);
+  });
   const int64_t nchunk = n / (U * A::N);
   int64_t want = (nchunk + (int64_t)RL_THREADS * RL_UNROLL - 1) / ((int64_t)RL_THREADS * RL_UNROLL);
-  int64_t cap = wave < RL_MAX_CLUSTERS * RL_CLUSTER ? wave : RL_MAX_CLUSTERS * RL_CLUSTER;
+  int64_t cap = wave < (int64_t)RL_MAX_CLUSTERS * cluster ? wave : (int64_t)RL_MAX_CLUSTERS * cluster;
   int64_t grid = want < cap ? want : cap;
-  grid = grid / RL_CLUSTER * RL_CLUSTER;
-  if (grid < RL_CLUSTER) grid = RL_CLUSTER;
-  CDB_CUDA_CHECK(launch_pdl(kernel, dim3((unsigned)grid), dim3(RL_THREADS), 0, st, c, b, p, r, n, means, scratch));
+  grid = grid / cluster * cluster;
+  if (grid < cluster) grid = cluster;
+  CDB_CUDA_CHECK(launch_pdl_cluster(kernel, dim3((unsigned)grid), dim3(RL_THREADS), 0, st, (unsigned)cluster, c, b, p, r,
+                                    n, means, scratch));
   return CDB_OK;
 }
 

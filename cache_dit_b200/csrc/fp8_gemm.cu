@@ -37,7 +37,8 @@ constexpr int BM = 128;          // tile rows   (UMMA M)
 constexpr int BN = 256;          // tile cols   (UMMA N)
 constexpr int BK = 128;          // K bytes per stage = one 128-byte swizzle span of e4m3
 constexpr int UMMA_K = 32;       // K per tcgen05.mma for 8-bit inputs
-constexpr int STAGES = 4;
+constexpr int STAGES = 4;        // stages of the ring at the full tile width
+constexpr int MAX_STAGES = 8;    // narrower tiles have smaller stages: more of them fit the same ring
 constexpr int GEMM_THREADS = 192;
 constexpr int EPI_WARP0 = 2;
 constexpr int EPI_THREADS = 128;
@@ -52,8 +53,8 @@ constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;
 #endif
 
 struct __align__(8) GemmBarriers {
-  uint64_t full[STAGES];       // TMA bytes landed
-  uint64_t empty[STAGES];      // MMAs reading the stage retired
+  uint64_t full[MAX_STAGES];   // TMA bytes landed
+  uint64_t empty[MAX_STAGES];  // MMAs reading the stage retired
   uint64_t acc_full[2];        // accumulator complete in TMEM
   uint64_t acc_empty[2];       // epilogue drained the accumulator
   uint32_t tmem_base;
@@ -322,6 +323,8 @@ struct GemmProblems {
   GemmProblem p[MAX_PROBLEMS];
   int count;
   int num_tiles;
+  int stages;       // single-CTA kernel: stages of the shared-memory ring for this launch's tile width
+  int stage_bytes;  // ... and the size of one (A tile | weight tile) stage
 };
 __device__ __forceinline__ const GemmProblem* problem_of(const GemmProblems& ps, int tile, int& local) {
   const bool second = ps.count > 1 && tile >= ps.p[1].tile_begin;
@@ -363,7 +366,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
   pdl_launch_dependents();  // a following kernel launched as a programmatic dependent may be scheduled early
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
+    for (int s = 0; s < MAX_STAGES; ++s) {
       mbar_init(&gb->full[s], 1);
       mbar_init(&gb->empty[s], 1);
     }
@@ -386,6 +389,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
   tcgen05_fence_after();
   const uint32_t tmem_base = gb->tmem_base;
 
+  const int stages = ps.stages;
+  const int stage_bytes = ps.stage_bytes;
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
@@ -393,34 +398,41 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         asm volatile("prefetch.tensormap [%0];" ::"l"(&ps.p[i].map_a) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&ps.p[i].map_w) : "memory");
       }
-      uint32_t it = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        int local;
-        const GemmProblem* pr = problem_of(ps, tile, local);
-        const int k_blocks = pr->k_blocks;
-        int mi, ni;
-        tile_coords(local, pr->m_tiles, pr->n_tiles, pr->group_m, mi, ni);
-        const int m0 = mi * BM, n0 = ni * pr->bn;
-        const uint32_t stage_tx = A_STAGE_BYTES + (uint32_t)pr->bn * BK;  // the weight box has `bn` rows
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1u;
+    }
+    uint32_t it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      int local;
+      const GemmProblem* pr = problem_of(ps, tile, local);
+      const int k_blocks = pr->k_blocks;
+      int mi, ni;
+      tile_coords(local, pr->m_tiles, pr->n_tiles, pr->group_m, mi, ni);
+      const int m0 = mi * BM, n0 = ni * pr->bn;
+      const uint32_t stage_tx = A_STAGE_BYTES + (uint32_t)pr->bn * BK;  // the weight box has `bn` rows
+      for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        if (lane == 0) {
+          const int s = it % stages;
+          const uint32_t ph = (it / stages) & 1u;
           ok = mbar_wait(&gb->empty[s], ph ^ 1u, gb, status_word, 1);
-          if (!ok) break;
-          uint8_t* a_dst = smem + s * STAGE_BYTES;
-          uint8_t* b_dst = a_dst + A_STAGE_BYTES;
-          mbar_expect_tx(&gb->full[s], stage_tx);
-          tma_load_2d(&pr->map_a, &gb->full[s], a_dst, kb * BK, m0);
-          tma_load_2d(&pr->map_w, &gb->full[s], b_dst, kb * BK, n0);
+          if (ok) {
+            uint8_t* a_dst = smem + s * stage_bytes;
+            uint8_t* b_dst = a_dst + A_STAGE_BYTES;
+            mbar_expect_tx(&gb->full[s], stage_tx);
+            tma_load_2d(&pr->map_a, &gb->full[s], a_dst, kb * BK, m0);
+            tma_load_2d(&pr->map_w, &gb->full[s], b_dst, kb * BK, n0);
+          }
         }
+        ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+        if (!ok) break;
       }
+    }
+    if (lane == 0) {
       // Do not let the CTA retire while bulk copies into its shared memory are in flight:
       // wait (bounded) until every armed stage has landed.
       const uint32_t issued = it;
-      for (uint32_t j = (issued > STAGES ? issued - STAGES : 0); j < issued; ++j) {
-        const int s = j % STAGES;
-        const uint32_t ph = (j / STAGES) & 1u;
+      for (uint32_t j = (issued > (uint32_t)stages ? issued - stages : 0); j < issued; ++j) {
+        const int s = j % stages;
+        const uint32_t ph = (j / stages) & 1u;
         uint64_t t0 = global_timer_ns();
         while (!mbar_try_wait(&gb->full[s], ph)) {
           if (global_timer_ns() - t0 > WAIT_LIMIT_NS) break;
@@ -445,12 +457,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         const int k_blocks = pr->k_blocks;
         const uint32_t idesc = pr->idesc;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1u;
+          const int s = it % stages;
+          const uint32_t ph = (it / stages) & 1u;
           ok = mbar_wait(&gb->full[s], ph, gb, status_word, 3);
           if (!ok) break;
           tcgen05_fence_after();
-          const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
+          const uint32_t a_addr = smem_u32(smem + s * stage_bytes);
           const uint32_t b_addr = a_addr + A_STAGE_BYTES;
           const uint64_t adesc = make_kmajor_sw128_desc(a_addr);
           const uint64_t bdesc = make_kmajor_sw128_desc(b_addr);
@@ -658,29 +670,37 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
         asm volatile("prefetch.tensormap [%0];" ::"l"(&ps.p[i].map_a) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&ps.p[i].map_w) : "memory");
       }
-      uint32_t it = 0;
-      bool ok = true;
-      for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
-        int local;
-        const GemmProblem* pr = problem_of(ps, tile, local);
-        const int k_blocks = pr->k_blocks;
-        int mi, ni;
-        tile_coords(local, pr->m_tiles, pr->n_tiles, pr->group_m, mi, ni);
-        const int m0 = mi * P_BM + (int)rank * 128;
-        const int n0 = ni * BN + (int)rank * 128;
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+    }
+    const int half = (int)rank * 128;  // this CTA's rows of A and its half of the weight tile
+    uint32_t it = 0;
+    bool ok = true;
+    for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
+      int local;
+      const GemmProblem* pr = problem_of(ps, tile, local);
+      const int k_blocks = pr->k_blocks;
+      int mi, ni;
+      tile_coords(local, pr->m_tiles, pr->n_tiles, pr->group_m, mi, ni);
+      const int m0 = mi * P_BM + half;
+      const int n0 = ni * BN + half;
+      for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        if (lane == 0) {
           const int s = it % P_STAGES;
           const uint32_t ph = (it / P_STAGES) & 1u;
           ok = pair_wait(&gb->empty[s], ph ^ 1u, gb, status_word, 11);
-          if (!ok) break;
-          uint8_t* a_dst = smem + s * P_STAGE_BYTES;
-          uint8_t* b_dst = a_dst + P_A_BYTES;
-          if (rank == 0) mbar_expect_tx(&gb->full[s], 2 * P_STAGE_BYTES);  // both CTAs' bytes
-          const uint32_t full_addr = map_to_cta(smem_u32(&gb->full[s]), 0);
-          tma_load_2d_pair(&pr->map_a, full_addr, a_dst, kb * BK, m0);
-          tma_load_2d_pair(&pr->map_w, full_addr, b_dst, kb * BK, n0);
+          if (ok) {
+            uint8_t* a_dst = smem + s * P_STAGE_BYTES;
+            uint8_t* b_dst = a_dst + P_A_BYTES;
+            if (rank == 0) mbar_expect_tx(&gb->full[s], 2 * P_STAGE_BYTES);  // both CTAs' bytes
+            const uint32_t full_addr = map_to_cta(smem_u32(&gb->full[s]), 0);
+            tma_load_2d_pair(&pr->map_a, full_addr, a_dst, kb * BK, m0);
+            tma_load_2d_pair(&pr->map_w, full_addr, b_dst, kb * BK, n0);
+          }
         }
+        ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+        if (!ok) break;
       }
+    }
+    if (lane == 0) {
       // A CTA may not retire while copies into its shared memory are in flight or while the peer's
       // MMAs still read its tiles: wait (bounded) until the consumer has released every stage used.
       const uint32_t issued = it;
@@ -1010,7 +1030,8 @@ extern "C" int cdb_tuning_set_gemm_tile_cols(int cols) {
 // operand bandwidth per flop (the A tile is re-read for fewer columns) but fills the waves, so the width is the
 // multiple of 16 that minimises a small cost model:
 //     waves x (K blocks x cycles per K block + epilogue) with
-//     cycles per K block = max(tensor time 2 x bn, operand bytes (16 KB + 128 x bn) / ~100 bytes per clock).
+//     cycles per K block = max(tensor time 2 x bn, operand bytes (16 KB + 128 x bn) / ~100 bytes per clock,
+//                              load latency / stages of the ring at that width).
 // The full width wins ties and anything within 3 %, so tall problems keep the shape they were tuned with.
 static int choose_tile_cols(const cdb_gemm_problem_abi* g, int n, int sms) {
   const int forced = g_forced_tile_cols.load(std::memory_order_relaxed);
@@ -1022,7 +1043,13 @@ static int choose_tile_cols(const cdb_gemm_problem_abi* g, int n, int sms) {
       const int64_t mt = (g[i].M + BM - 1) / BM, nt = (g[i].N + bn - 1) / bn, kb = (g[i].K + BK - 1) / BK;
       tiles += mt * nt;
       const double tensor = 2.0 * bn, ingest = (A_STAGE_BYTES + 128.0 * bn) / 100.0;
-      const double t = kb * (tensor > ingest ? tensor : ingest) + 150.0 * ((bn + 63) / 64);
+      // the ring hides only `stages` K blocks of load latency (~2400 clocks from issue to use under load)
+      const int stage_bytes = A_STAGE_BYTES + bn * BK;
+      const int stages = SMEM_TILE_BYTES / stage_bytes < MAX_STAGES ? SMEM_TILE_BYTES / stage_bytes : MAX_STAGES;
+      const double latency = 2400.0 / stages;
+      double per_kb = tensor > ingest ? tensor : ingest;
+      per_kb = per_kb > latency ? per_kb : latency;
+      const double t = kb * per_kb + 150.0 * ((bn + 63) / 64);
       per_tile = t > per_tile ? t : per_tile;
     }
     const int64_t waves = (tiles + sms - 1) / sms;
@@ -1129,6 +1156,8 @@ extern "C" int cdb_fp8_gemm_rowscaled_grouped(const void* problems_v, int count,
   }
   if (tiles > INT32_MAX) return CDB_ERR_TOO_LARGE;
   ps.num_tiles = (int)tiles;
+  ps.stage_bytes = A_STAGE_BYTES + bn * BK;
+  ps.stages = SMEM_TILE_BYTES / ps.stage_bytes < MAX_STAGES ? SMEM_TILE_BYTES / ps.stage_bytes : MAX_STAGES;
   if (pair) {
     const int64_t pairs = tiles < sms / 2 ? tiles : sms / 2;
     fp8_gemm_rowscaled_pair_kernel<<<(unsigned)(2 * pairs), GEMM_THREADS, P_SMEM_TOTAL_BYTES, st>>>(ps, status_word);

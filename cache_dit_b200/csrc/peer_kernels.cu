@@ -241,22 +241,39 @@ struct PeerRows {
   int64_t start[PEER_MAX + 1];
 };
 
-__global__ void __launch_bounds__(128)
+constexpr int GT_UNROLL = 4;
+__global__ void __launch_bounds__(256)
     gather_tokens_kernel(const __nv_bfloat16* __restrict__ o, const PeerPtrs dst, const PeerRows rows_of, int world,
                          int my_rank, int64_t batch, int64_t tokens_all, int64_t dst_token_capacity,
                          int heads_per_rank, int heads_all, int head_dim) {
+  // Flat over (row, packet): with few heads per rank a row is short (3 heads x 128 = 48 packets), so a CTA per
+  // row would leave most of its threads idle; here every thread has GT_UNROLL independent 16-byte copies in flight.
   const int row_packets = heads_per_rank * head_dim / 8;
-  const int64_t rows = batch * tokens_all;
-  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
-    const int64_t b = r / tokens_all, s = r - b * tokens_all;
-    int owner = 0;
-    while (owner + 1 < world && s >= rows_of.start[owner + 1]) ++owner;
-    const int64_t local_s = s - rows_of.start[owner];
-    const uint4* src = reinterpret_cast<const uint4*>(o + r * (int64_t)heads_per_rank * head_dim);
-    __nv_bfloat16* base_ptr = static_cast<__nv_bfloat16*>(dst.p[owner]);
-    uint4* out = reinterpret_cast<uint4*>(base_ptr + ((b * dst_token_capacity + local_s) * heads_all +
-                                                      (int64_t)my_rank * heads_per_rank) * head_dim);
-    for (int p = threadIdx.x; p < row_packets; p += blockDim.x) out[p] = __ldcs(src + p);
+  const int64_t total = batch * tokens_all * row_packets;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  const uint4* src = reinterpret_cast<const uint4*>(o);
+  for (int64_t i0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i0 < total; i0 += GT_UNROLL * stride) {
+    uint4 v[GT_UNROLL];
+#pragma unroll
+    for (int u = 0; u < GT_UNROLL; ++u) {
+      const int64_t i = i0 + u * stride;
+      if (i < total) v[u] = __ldcs(src + i);
+    }
+#pragma unroll
+    for (int u = 0; u < GT_UNROLL; ++u) {
+      const int64_t i = i0 + u * stride;
+      if (i >= total) continue;
+      const int64_t r = i / row_packets;
+      const int p = (int)(i - r * row_packets);
+      const int64_t b = r / tokens_all, s = r - b * tokens_all;
+      int owner = 0;
+      while (owner + 1 < world && s >= rows_of.start[owner + 1]) ++owner;
+      const int64_t local_s = s - rows_of.start[owner];
+      __nv_bfloat16* base_ptr = static_cast<__nv_bfloat16*>(dst.p[owner]);
+      uint4* out = reinterpret_cast<uint4*>(base_ptr + ((b * dst_token_capacity + local_s) * heads_all +
+                                                        (int64_t)my_rank * heads_per_rank) * head_dim);
+      out[p] = v[u];
+    }
   }
 }
 
@@ -388,7 +405,9 @@ __global__ void peer_signal_kernel(const PeerPtrs flags, int my_rank, int world,
   }
   __syncthreads();
   if ((int)threadIdx.x < world) {
-    __threadfence_system();
+    // st.release.sys = fence.acq_rel.sys + store: it alone orders everything that happened before this thread
+    // (the earlier kernels' stores to peer memory included: they happen-before through the kernel boundary) in
+    // front of the flag; a __threadfence_system() of its own here was a second 2 us fence per signal
     unsigned int* word = static_cast<unsigned int*>(flags.p[threadIdx.x]) + my_rank;
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(word), "r"(e) : "memory");
   }
@@ -416,7 +435,8 @@ __global__ void peer_wait_kernel(const unsigned int* __restrict__ my_flags, int 
       __nanosleep(200);
     }
   }
-  __threadfence_system();
+  // ld.acquire.sys = load + fence.acq_rel.sys: later reads of this thread, and through the kernel boundary of the
+  // kernels that follow, are ordered behind the flag; no further fence is needed
 }
 
 // signal + wait in one launch (what a rank runs between the phases of the exchange).
@@ -429,9 +449,8 @@ __global__ void peer_barrier_kernel(const PeerPtrs flags, const unsigned int* __
   }
   __syncthreads();
   if ((int)threadIdx.x >= world) return;
-  __threadfence_system();
   unsigned int* word = static_cast<unsigned int*>(flags.p[threadIdx.x]) + my_rank;
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(word), "r"(e) : "memory");
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(word), "r"(e) : "memory");  // release = fence + store
   if (sync->status != 0) return;
   const unsigned int* mine = my_flags + threadIdx.x;
   unsigned long long t0 = 0;
@@ -450,7 +469,6 @@ __global__ void peer_barrier_kernel(const PeerPtrs flags, const unsigned int* __
       __nanosleep(200);
     }
   }
-  __threadfence_system();
 }
 
 }  // namespace cdb
@@ -662,7 +680,9 @@ extern "C" int cdb_gather_tokens(const void* o, void* const* dst_ptrs, int world
   }
   const int64_t rows = batch * tokens_all;
   const int64_t cap = (int64_t)sm_count() * 16;
-  gather_tokens_kernel<<<(unsigned)(rows < cap ? rows : cap), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+  const int64_t packets = rows * (heads_per_rank * head_dim / 8);
+  const int64_t want = (packets + 256 * GT_UNROLL - 1) / (256 * GT_UNROLL);
+  gather_tokens_kernel<<<(unsigned)(want < cap ? want : cap), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(o), dst, rows_of, world, my_rank, batch, tokens_all, dst_token_capacity,
       heads_per_rank, heads_per_rank * world, head_dim);
   CDB_CUDA_CHECK(cudaGetLastError());

@@ -73,11 +73,17 @@ def quantize(module: torch.nn.Module, quantize_config: QuantizeConfig = None, **
     quantized = _swap_linears(module, "", quantize_config, skipped)
   if torch.cuda.is_available():
     torch.cuda.empty_cache()
+  fused_blocks = 0
+  if quantized:
+    # blocks with the attribute layout of the public FLUX blocks get forwards that fuse the producers (adaLN
+    # LayerNorm, GELU, concatenation, QK norm + rotary embedding) into the quantization and glue kernels
+    from .fused_blocks import install_fused_block_forwards
+    fused_blocks = install_fused_block_forwards(module)
   module._is_quantized = True
   module._quantize_config = quantize_config
   module._quantize_type = quantize_config.quant_type
   module._exclude_layers = quantize_config.exclude_layers
-  module._quantize_stats = dict(linear_layers=total, quantized=quantized, skipped=skipped)
+  module._quantize_stats = dict(linear_layers=total, quantized=quantized, skipped=skipped, fused_blocks=fused_blocks)
   if quantize_config.verbose:
     for line in skipped:
       logger.info(line)
@@ -87,6 +93,9 @@ def quantize(module: torch.nn.Module, quantize_config: QuantizeConfig = None, **
 
 
 def remove_quantization_stats(module) -> None:
+  if module is not None and getattr(module, "_quantize_stats", {}).get("fused_blocks"):
+    from .fused_blocks import remove_fused_block_forwards
+    remove_fused_block_forwards(module)
   for attr in ("_is_quantized", "_quantize_config", "_quantize_type", "_exclude_layers", "_quantize_stats"):
     if module is not None and attr in vars(module):
       delattr(module, attr)

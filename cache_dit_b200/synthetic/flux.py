@@ -11,6 +11,7 @@ as one 57-block list, the way the reference adapts FLUX
 """
 from __future__ import annotations
 
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -19,7 +20,7 @@ from torch import nn
 
 from ..caching.block_adapters import BlockAdapter, BlockAdapterRegister
 from ..caching.forward_pattern import ForwardPattern
-from .layers import (RMSNorm, RopeCache, TimestepMLP, UlyssesGroup, concat_gelu_linear, gated_add, gated_add_pair,
+from .layers import (ModulationBank, RMSNorm, RopeCache, TimestepMLP, UlyssesGroup, concat_gelu_linear, gated_add, gated_add_pair,
                      gelu_linear_pair,
                      joint_attention, join_tokens, linear_pair, norm_modulate, norm_modulate_linears,
                      norm_modulate_linears_pair, shared_input_linears, split_tokens, timestep_embedding)
@@ -83,8 +84,12 @@ class FluxTransformerBlock(nn.Module):
 
   def forward(self, hidden_states, encoder_hidden_states, temb, image_rotary_emb):
     a = self.attn
-    # both streams' modulation projections read SiLU(temb): one quantization, one weight-streaming product
-    mod, c_mod = shared_input_linears(F.silu(temb), (self.norm1.linear, self.norm1_context.linear))
+    bank = getattr(self, "mod_bank", None)
+    if bank is not None:  # computed once per step for all blocks, column-sharded over the ranks
+      mod, c_mod = bank.outputs((self.norm1.linear, self.norm1_context.linear))
+    else:
+      # both streams' modulation projections read SiLU(temb): one quantization, one weight-streaming product
+      mod, c_mod = shared_input_linears(F.silu(temb), (self.norm1.linear, self.norm1_context.linear))
     shift, scale, gate, shift_mlp, scale_mlp, gate_mlp = mod.chunk(6, dim=-1)
     c_shift, c_scale, c_gate, c_shift_mlp, c_scale_mlp, c_gate_mlp = c_mod.chunk(6, dim=-1)
     (q, k, v), (cq, ck, cv) = norm_modulate_linears_pair(
@@ -117,7 +122,8 @@ class FluxSingleTransformerBlock(nn.Module):
     a = self.attn
     n_txt = encoder_hidden_states.shape[1]
     x = join_tokens(encoder_hidden_states, hidden_states)
-    shift, scale, gate = self.norm(temb)
+    bank = getattr(self, "mod_bank", None)
+    shift, scale, gate = bank.outputs((self.norm.linear, ))[0].chunk(3, dim=-1) if bank is not None else self.norm(temb)
     q, k, v, mlp = norm_modulate_linears(x, shift, scale, (a.to_q, a.to_k, a.to_v, self.proj_mlp))
     o = joint_attention(((q, a.norm_q), ), ((k, a.norm_k), ), (v, ), image_rotary_emb, a.heads, self.cp)
     y = concat_gelu_linear(o, mlp, self.proj_out)
@@ -174,13 +180,39 @@ class FluxTransformer2DModel(nn.Module):
     self._cp = UlyssesGroup(group, exchange)
     for block in list(self.transformer_blocks) + list(self.single_transformer_blocks):
       block.cp = self._cp
+    self._mod_bank = None
+    self._mod_bank_wanted = self._cp.world > 1 and os.environ.get("CACHE_DIT_B200_MODULATION_BANK", "1") != "0"
 
   def disable_context_parallel(self):
     if self._cp is not None and self._cp.exchange is not None:
       self._cp.exchange.close()
     self._cp = None
+    self._mod_bank = None
+    self._mod_bank_wanted = False
     for block in list(self.transformer_blocks) + list(self.single_transformer_blocks):
       block.cp = None
+      block.mod_bank = None
+
+  def _modulation_for_step(self, temb):
+    """Under context parallelism with FP8 modulation linears: all blocks' modulation vectors as one column-sharded
+    product + all-gather per step (`ModulationBank`) instead of 57 replicated weight-streaming products."""
+    if not getattr(self, "_mod_bank_wanted", False) or not temb.is_cuda:
+      return
+    if self._mod_bank is None:
+      from ..quantization.linear import Float8RowwiseLinear
+      groups = [(b.norm1.linear, b.norm1_context.linear) for b in self.transformer_blocks] + \
+               [(b.norm.linear, ) for b in self.single_transformer_blocks]
+      if not all(isinstance(l, Float8RowwiseLinear) for g in groups for l in g):
+        self._mod_bank_wanted = False
+        return
+      try:
+        self._mod_bank = ModulationBank(groups, self._cp.group)
+      except ValueError:
+        self._mod_bank_wanted = False
+        return
+      for b in list(self.transformer_blocks) + list(self.single_transformer_blocks):
+        b.mod_bank = self._mod_bank
+    self._mod_bank.compute(temb)
 
   def forward(self, hidden_states, encoder_hidden_states, pooled_projections, timestep, img_ids, txt_ids,
               guidance=None):
@@ -196,6 +228,7 @@ class FluxTransformer2DModel(nn.Module):
     if self.guidance_embedder is not None and guidance is not None:
       temb = temb + self.guidance_embedder(timestep_embedding(guidance * 1000.0, 256).to(dt))
     temb = temb + self.text_embedder(pooled_projections)
+    self._modulation_for_step(temb)
     encoder_hidden_states = self.context_embedder(encoder_hidden_states)
     rope = self._rope_cache.get((txt_ids, img_ids), self.axes_dims_rope, dt)
     for block in self.transformer_blocks:

@@ -107,6 +107,55 @@ def concat_gelu_linear(head: torch.Tensor, tail: torch.Tensor, linear: nn.Module
   return linear(torch.cat([head, F.gelu(tail, approximate="tanh")], dim=-1))
 
 
+class ModulationBank:
+  """Every adaLN modulation projection of a model as ONE weight-streaming product per step, column-sharded over
+  the ranks of a context-parallel group.
+
+  The projections read only SiLU(temb), which is known when a step starts and is the same on every rank, so under
+  context parallelism each rank would stream all of their weights (2.1 GB for the FLUX shape: the one part of a
+  step that does not shrink with the number of GPUs).  Here rank r computes columns [r, r + 1) * cols / W of the
+  concatenated projection and one all-gather hands every rank the whole vector; the blocks then take views of it.
+  Same kernel, same arithmetic per column as the per-block products: results are bitwise unchanged.
+  The output lives in one buffer that is overwritten every step, so captured block graphs read it in place."""
+
+  def __init__(self, groups: Sequence[Sequence[nn.Module]], group=None):
+    import torch.distributed as dist
+    self.group = group
+    self.world = dist.get_world_size(group)
+    self.rank = dist.get_rank(group)
+    self.linears = [l for g in groups for l in g]
+    self.fused = fused_group(self.linears)
+    self.cols = self.fused.out_features
+    if self.cols % (self.world * 8) != 0:
+      raise ValueError("the concatenated modulation width must divide by 8 x the number of ranks")
+    self.per_rank = self.cols // self.world
+    self.offsets = {}
+    start = 0
+    for l in self.linears:
+      self.offsets[id(l)] = (start, l.out_features)
+      start += l.out_features
+    self._out = None
+
+  def compute(self, temb: torch.Tensor) -> None:
+    import torch.distributed as dist
+    x = F.silu(temb)
+    a_q, a_scale = self.linears[0].quantize_input(x)
+    lo, hi = self.rank * self.per_rank, (self.rank + 1) * self.per_rank
+    f = self.fused
+    local = torch.empty((a_q.shape[0], self.per_rank), dtype=torch.bfloat16, device=x.device)
+    _native.fp8_gemm_rowscaled(a_q, a_scale, f.weight_q[lo:hi], f.weight_scale[lo:hi],
+                               None if f.bias is None else f.bias[lo:hi], local)
+    if self._out is None or self._out.shape[0] != local.shape[0]:
+      self._out = torch.empty((local.shape[0], self.cols), dtype=torch.bfloat16, device=x.device)
+      self._gathered = torch.empty((self.world, local.shape[0], self.per_rank), dtype=torch.bfloat16, device=x.device)
+    dist.all_gather_into_tensor(self._gathered, local, group=self.group)
+    self._out.view(local.shape[0], self.world, self.per_rank).copy_(self._gathered.permute(1, 0, 2))
+
+  def outputs(self, linears: Sequence[nn.Module]) -> List[torch.Tensor]:
+    """Views [batch, out_features] of the gathered vector for the given member linears."""
+    return [self._out[:, o:o + n] for o, n in (self.offsets[id(l)] for l in linears)]
+
+
 class RMSNorm(nn.Module):
 
   def __init__(self, dim: int, eps: float = 1e-6):

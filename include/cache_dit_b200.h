@@ -207,7 +207,6 @@ CDB_API int cdb_fp8_gemm_rowscaled(const void* a_q, const float* a_scale, const 
  * `cols` fixes the width for every later launch of the process, 0 restores the model.  The environment variable
  * CDB_GEMM_BN sets the initial value.  Results do not depend on the width (bitwise). */
 CDB_API int cdb_tuning_set_gemm_tile_cols(int cols);
-
 /* ------------------------------------------------------------------------------------------
  * Transformer-block glue between the FP8 linears.  No counterpart in the reference: there these
  * are eager PyTorch ops inside the diffusers transformer blocks that cache-dit wraps.  They are

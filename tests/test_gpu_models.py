@@ -194,3 +194,52 @@ def test_final_latents_against_library_fp8_linears():
     assert abs(s_ours.residual_diffs[k] - v) <= 6e-2 * abs(v) + 1e-12
   rel = np.linalg.norm(got - want) / np.linalg.norm(want)
   assert np.isfinite(got).all() and 0.0 < rel < 2e-2, rel
+
+
+def test_fused_forwards_for_a_foreign_model_with_the_flux_attribute_layout(monkeypatch):
+  """`quantize` gives blocks that merely LOOK like the public FLUX blocks (attribute names, calling convention of
+  the reference's patched forward) the producer-fused forwards; the result must agree with the same FP8 model run
+  through its own eager forwards (separate quantization kernels, eager LayerNorm / GELU / concat / RoPE), and take
+  far fewer launches of this package's kernels plus none of the eager glue."""
+  from cache_dit_b200 import _native as nat
+  from tests.fake_flux_layout import TinyFlux
+  dev = torch.device("cuda")
+  g = torch.Generator().manual_seed(11)
+
+  def build(fuse: bool):
+    monkeypatch.setenv("CACHE_DIT_B200_FUSE_BLOCKS", "1" if fuse else "0")
+    torch.manual_seed(4)
+    model = TinyFlux().to(torch.bfloat16).to(dev).eval().requires_grad_(False)
+    for blk in list(model.transformer_blocks) + list(model.single_transformer_blocks):  # small modulation: a tame residual stream
+      for name in ("norm1", "norm1_context", "norm"):
+        if hasattr(blk, name):
+          torch.nn.init.normal_(getattr(blk, name).linear.weight, std=0.02)
+    cd.quantize(model, cd.QuantizeConfig(quant_type="float8_per_row"))
+    return model
+
+  n_img, n_txt, dim, d = 192, 24, 256, 128
+  x = torch.randn(2, n_img, dim, generator=g).to(dev, torch.bfloat16)
+  c = torch.randn(2, n_txt, dim, generator=g).to(dev, torch.bfloat16)
+  temb = torch.randn(2, dim, generator=g).to(dev, torch.bfloat16)
+  ang = torch.rand(n_txt + n_img, d // 2, generator=g) * 6.28
+  rope = (torch.cos(ang).repeat_interleave(2, dim=-1).to(dev), torch.sin(ang).repeat_interleave(2, dim=-1).to(dev))  # fp32, as diffusers passes them
+
+  eager = build(False)
+  assert eager._quantize_stats["fused_blocks"] == 0
+  l0 = nat.launch_count
+  want_c, want_x = eager(x, c, temb, rope)
+  eager_launches = nat.launch_count - l0
+  fused = build(True)
+  assert fused._quantize_stats["fused_blocks"] == 4
+  l0 = nat.launch_count
+  got_c, got_x = fused(x, c, temb, rope)
+  fused_launches = nat.launch_count - l0
+  torch.cuda.synchronize()
+  for got, want in ((got_x, want_x), (got_c, want_c)):
+    rel = float((got.float() - want.float()).norm() / want.float().norm())
+    assert torch.isfinite(got).all() and rel < 2e-2, rel
+  assert fused_launches < eager_launches, (fused_launches, eager_launches)
+  # removing the quantization statistics puts the blocks' own forwards back
+  from cache_dit_b200.quantization import remove_quantization_stats
+  remove_quantization_stats(fused)
+  assert not getattr(fused.transformer_blocks[0], "_cdb_fused_forward", False)

