@@ -48,6 +48,7 @@ SIGNATURES = {
   "cdb_gated_residual_pair": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64,
                                       c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64,
                                       c_int64, c_void_p]),
+  "cdb_bf16_gemv": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p]),
   "cdb_peer_enable_access": (c_int, [c_int]),
   "cdb_peer_alloc": (c_int, [c_size_t, POINTER(c_void_p)]),
   "cdb_peer_free": (c_int, [c_void_p]),
@@ -345,6 +346,21 @@ def gated_residual(x, gate, y):
                                 _ptr(out), b * t, t, c, _stream(x))
   check(st, "cdb_gated_residual")
   return out
+
+
+def bf16_gemv(x2d, w, bias, out):
+  """out[M, N] = bf16(x2d[M, K] @ w[N, K]^T + bias[N]) for M <= 4 (see cdb_bf16_gemv); rows of x2d / out may be strided."""
+  _need_cuda(x2d, w, bias, out)
+  _need_contig(w, bias)
+  m, k = x2d.shape
+  n = w.shape[0]
+  if x2d.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or w.shape[1] != k \
+      or tuple(out.shape) != (m, n) or x2d.stride(1) != 1 or out.stride(1) != 1 \
+      or (bias is not None and (bias.dtype != torch.bfloat16 or bias.numel() != n)):
+    raise RuntimeError("bf16_gemv: bf16 x [M, K], w [N, K], bias [N], out [M, N] with unit column strides")
+  st = lib().cdb_bf16_gemv(_ptr(x2d), x2d.stride(0) if m > 1 else max(k, x2d.stride(0)), _ptr(w), _ptr(bias), _ptr(out),
+                           out.stride(0) if m > 1 else max(n, out.stride(0)), m, n, k, _stream(x2d))
+  check(st, "cdb_bf16_gemv")
 
 
 def fp8_quant_rows_concat_gelu(head2d, tail2d, q, scale):

@@ -76,9 +76,104 @@ __global__ void __launch_bounds__(256) gated_residual_pair_kernel(const __grid_c
   }
 }
 
+// ---- few-row bf16 product (adaLN modulation projections kept in bf16) ---------------------------------------
+// out[m, n] = bf16( sum_k x[m, k] * w[n, k] + bias[n] ), M <= 4 rows: a weight-streaming pass (HBM-bound, N * K * 2
+// bytes), a warp per output column, lanes reading 16-byte pieces of the weight row, fp32 accumulation, the few
+// activation rows staged in shared memory as fp32.  Every column is computed by one warp in a fixed order, so
+// the result of a column does not depend on which slice of the weight matrix a launch is given: this is what
+// lets a context-parallel run shard the columns over the ranks and still get the single-GPU bits.
+constexpr int BGEMV_THREADS = 256;
+constexpr int BGEMV_MAX_M = 4;
+
+template <int TM>
+__global__ void __launch_bounds__(BGEMV_THREADS)
+    bf16_gemv_kernel(const __nv_bfloat16* __restrict__ x, int64_t ld_x, const __nv_bfloat16* __restrict__ w,
+                     const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ out, int64_t ld_out, int N,
+                     int K) {
+  pdl_launch_dependents();
+  pdl_wait_prior();
+  extern __shared__ __align__(16) float s_x[];  // [TM][K]
+  for (int i = threadIdx.x; i < TM * K; i += BGEMV_THREADS) {
+    const int m = i / K, k = i - m * K;
+    s_x[i] = __bfloat162float(x[(int64_t)m * ld_x + k]);
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const int warp = (blockIdx.x * BGEMV_THREADS + threadIdx.x) >> 5;
+  const int nwarps = (gridDim.x * BGEMV_THREADS) >> 5;
+  const int chunks = K >> 3;  // 16-byte pieces per weight row
+  for (int n = warp; n < N; n += nwarps) {
+    const uint4* wrow = reinterpret_cast<const uint4*>(w + (int64_t)n * K);
+    float acc[TM];
+#pragma unroll
+    for (int m = 0; m < TM; ++m) acc[m] = 0.f;
+    for (int c0 = lane; c0 < chunks; c0 += 32 * 4) {  // four independent loads in flight per lane
+      uint4 wv[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int c = c0 + j * 32;
+        wv[j] = c < chunks ? __ldcs(wrow + c) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int c = c0 + j * 32;
+        if (c < chunks) {
+          const uint32_t ww[4] = {wv[j].x, wv[j].y, wv[j].z, wv[j].w};
+#pragma unroll
+          for (int m = 0; m < TM; ++m) {
+            const float4* xs = reinterpret_cast<const float4*>(s_x + (int64_t)m * K + c * 8);
+            const float4 a = xs[0], b = xs[1];
+            acc[m] = fmaf(__uint_as_float(ww[0] << 16), a.x, acc[m]);
+            acc[m] = fmaf(__uint_as_float(ww[0] & 0xffff0000u), a.y, acc[m]);
+            acc[m] = fmaf(__uint_as_float(ww[1] << 16), a.z, acc[m]);
+            acc[m] = fmaf(__uint_as_float(ww[1] & 0xffff0000u), a.w, acc[m]);
+            acc[m] = fmaf(__uint_as_float(ww[2] << 16), b.x, acc[m]);
+            acc[m] = fmaf(__uint_as_float(ww[2] & 0xffff0000u), b.y, acc[m]);
+            acc[m] = fmaf(__uint_as_float(ww[3] << 16), b.z, acc[m]);
+            acc[m] = fmaf(__uint_as_float(ww[3] & 0xffff0000u), b.w, acc[m]);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int m = 0; m < TM; ++m) acc[m] = warp_sum(acc[m]);
+    if (lane == 0) {
+      const float b = bias != nullptr ? __bfloat162float(bias[n]) : 0.f;
+#pragma unroll
+      for (int m = 0; m < TM; ++m) out[(int64_t)m * ld_out + n] = __float2bfloat16_rn(acc[m] + b);
+    }
+  }
+}
+
 }  // namespace cdb
 
 using namespace cdb;
+
+extern "C" int cdb_bf16_gemv(const void* x, int64_t ld_x, const void* w, const void* bias, void* out, int64_t ld_out,
+                             int64_t M, int64_t N, int64_t K, void* stream) {
+  if (!x || !w || !out || M < 0 || N <= 0 || K <= 0 || ld_x < K || ld_out < N) return CDB_ERR_BAD_ARGUMENT;
+  if (M == 0) return CDB_OK;
+  if (M > BGEMV_MAX_M || K % 8 != 0 || !aligned16(w) || N > INT32_MAX || K > INT32_MAX) return CDB_ERR_UNSUPPORTED;
+  const size_t smem = (size_t)M * K * sizeof(float);
+  if (smem > 48 * 1024) return CDB_ERR_UNSUPPORTED;  // 4 x 3072 fp32 fits; wider inputs need the tile kernels
+  const int64_t want = (N + BGEMV_THREADS / 32 - 1) / (BGEMV_THREADS / 32);
+  const int64_t cap = (int64_t)sm_count() * 4;
+  const dim3 grid((unsigned)(want < cap ? want : cap));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
+  const __nv_bfloat16* wp = static_cast<const __nv_bfloat16*>(w);
+  const __nv_bfloat16* bp = static_cast<const __nv_bfloat16*>(bias);
+  __nv_bfloat16* op = static_cast<__nv_bfloat16*>(out);
+#define CDB_BGEMV(TM) \
+  CDB_CUDA_CHECK(launch_pdl(bf16_gemv_kernel<TM>, grid, dim3(BGEMV_THREADS), smem, st, xp, ld_x, wp, bp, op, ld_out, (int)N, (int)K))
+  if (M == 1) CDB_BGEMV(1);
+  else if (M == 2) CDB_BGEMV(2);
+  else if (M == 3) CDB_BGEMV(3);
+  else CDB_BGEMV(4);
+#undef CDB_BGEMV
+  return CDB_OK;
+}
+
 
 extern "C" int cdb_scatter_heads(const void* x, int64_t ld_x, const void* norm_weight, int norm_across_heads,
                                  const void* cos_table, const void* sin_table, int table_row_offset,

@@ -7,11 +7,12 @@ ranks hold one token more): the reference's `ulysses_anything` mode.
 """
 from __future__ import annotations
 
+import os
 from typing import List, Optional
 
 import torch
 
-from .layers import UlyssesGroup
+from .layers import ModulationBank, UlyssesGroup
 
 
 class ContextParallelMixin:
@@ -30,15 +31,45 @@ class ContextParallelMixin:
       raise NotImplementedError("FP8 head/token exchange is built for the peer-memory exchange only "
                                 "(parallel_kwargs={'exchange': 'peer'})")
     self._cp = UlyssesGroup(group, exchange)
-    for block in self._cp_blocks():
+    self._cp_block_list = self._cp_blocks()  # inside `forward` of a cache-enabled model the list holds the cache runner
+    for block in self._cp_block_list:
       block.cp = self._cp
+    self._mod_bank = None
+    self._mod_bank_wanted = self._cp.world > 1 and os.environ.get("CACHE_DIT_B200_MODULATION_BANK", "1") != "0"
 
   def disable_context_parallel(self):
     if self._cp is not None and self._cp.exchange is not None:
       self._cp.exchange.close()
     self._cp = None
+    self._mod_bank = None
+    self._mod_bank_wanted = False
     for block in self._cp_blocks():
       block.cp = None
+      block.mod_bank = None
+
+  def _modulation_groups(self, blocks):
+    """Per block, the linears that read only SiLU(temb) (none: the model has no per-block modulation projections)."""
+    return []
+
+  def modulation_for_call(self, temb: torch.Tensor) -> None:
+    """Under context parallelism: all blocks' modulation vectors as one column-sharded product + all-gather per call
+    (`ModulationBank`) instead of one replicated weight-streaming product per block and rank."""
+    if not getattr(self, "_mod_bank_wanted", False) or not temb.is_cuda:
+      return
+    bank = self._mod_bank
+    if bank is None or not bank.still_valid():
+      groups = self._modulation_groups(self._cp_block_list)
+      try:
+        bank = ModulationBank(groups, self._cp.group) if groups else None
+      except ValueError:
+        bank = None
+      if bank is None:
+        self._mod_bank_wanted = False
+        return
+      self._mod_bank = bank
+      for b in self._cp_block_list:
+        b.mod_bank = bank
+    bank.compute(temb)
 
   def cp_active(self) -> bool:
     return self._cp is not None and self._cp.world > 1

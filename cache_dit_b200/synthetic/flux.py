@@ -182,6 +182,8 @@ class FluxTransformer2DModel(nn.Module):
       block.cp = self._cp
     self._mod_bank = None
     self._mod_bank_wanted = self._cp.world > 1 and os.environ.get("CACHE_DIT_B200_MODULATION_BANK", "1") != "0"
+    # the block modules themselves: inside `forward` of a cache-enabled model the two lists hold the cache runner
+    self._mod_bank_blocks = (list(self.transformer_blocks), list(self.single_transformer_blocks))
 
   def disable_context_parallel(self):
     if self._cp is not None and self._cp.exchange is not None:
@@ -192,16 +194,17 @@ class FluxTransformer2DModel(nn.Module):
     for block in list(self.transformer_blocks) + list(self.single_transformer_blocks):
       block.cp = None
       block.mod_bank = None
+    self._mod_bank_blocks = ([], [])
 
   def _modulation_for_step(self, temb):
     """Under context parallelism with FP8 modulation linears: all blocks' modulation vectors as one column-sharded
     product + all-gather per step (`ModulationBank`) instead of 57 replicated weight-streaming products."""
     if not getattr(self, "_mod_bank_wanted", False) or not temb.is_cuda:
       return
-    if self._mod_bank is None:
+    if self._mod_bank is None or not self._mod_bank.still_valid():
       from ..quantization.linear import Float8RowwiseLinear
-      groups = [(b.norm1.linear, b.norm1_context.linear) for b in self.transformer_blocks] + \
-               [(b.norm.linear, ) for b in self.single_transformer_blocks]
+      double, single = self._mod_bank_blocks
+      groups = [(b.norm1.linear, b.norm1_context.linear) for b in double] + [(b.norm.linear, ) for b in single]
       if not all(isinstance(l, Float8RowwiseLinear) for g in groups for l in g):
         self._mod_bank_wanted = False
         return
@@ -210,7 +213,7 @@ class FluxTransformer2DModel(nn.Module):
       except ValueError:
         self._mod_bank_wanted = False
         return
-      for b in list(self.transformer_blocks) + list(self.single_transformer_blocks):
+      for b in double + single:
         b.mod_bank = self._mod_bank
     self._mod_bank.compute(temb)
 

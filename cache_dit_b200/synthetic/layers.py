@@ -16,7 +16,7 @@ import torch.nn.functional as F
 from torch import nn
 
 from .. import _native
-from ..quantization.linear import (Float8RowwiseLinear, fused_group, grouped_forward_quantized,
+from ..quantization.linear import (Float8RowwiseLinear, _members_share_storage, fused_group, grouped_forward_quantized,
                                    quantize_rows_fused, quantize_rows_fused_pair)
 
 
@@ -107,16 +107,32 @@ def concat_gelu_linear(head: torch.Tensor, tail: torch.Tensor, linear: nn.Module
   return linear(torch.cat([head, F.gelu(tail, approximate="tanh")], dim=-1))
 
 
+def modulation_rows(temb: torch.Tensor, linear: nn.Module) -> torch.Tensor:
+  """linear(SiLU(temb)) for the few rows of a timestep embedding.  A bf16 `nn.Linear` on the GPU goes through the
+  weight-streaming kernel (`cdb_bf16_gemv`), whose per-column arithmetic is what `ModulationBank` reproduces when
+  it shards the columns over the ranks; everything else is the eager call."""
+  x = F.silu(temb)
+  if type(linear) is nn.Linear and x.is_cuda and x.dtype == torch.bfloat16 and linear.weight.dtype == torch.bfloat16 \
+      and x.dim() == 2 and x.shape[0] <= 4 and x.shape[0] * x.shape[1] * 4 <= 48 * 1024 and x.shape[1] % 8 == 0 \
+      and linear.weight.is_contiguous():
+    out = torch.empty((x.shape[0], linear.out_features), dtype=torch.bfloat16, device=x.device)
+    _native.bf16_gemv(x if x.stride(1) == 1 else x.contiguous(), linear.weight, linear.bias, out)
+    return out
+  return linear(x)
+
+
 class ModulationBank:
-  """Every adaLN modulation projection of a model as ONE weight-streaming product per step, column-sharded over
+  """Every adaLN modulation projection of a model as ONE weight-streaming product per call, column-sharded over
   the ranks of a context-parallel group.
 
-  The projections read only SiLU(temb), which is known when a step starts and is the same on every rank, so under
-  context parallelism each rank would stream all of their weights (2.1 GB for the FLUX shape: the one part of a
-  step that does not shrink with the number of GPUs).  Here rank r computes columns [r, r + 1) * cols / W of the
-  concatenated projection and one all-gather hands every rank the whole vector; the blocks then take views of it.
-  Same kernel, same arithmetic per column as the per-block products: results are bitwise unchanged.
-  The output lives in one buffer that is overwritten every step, so captured block graphs read it in place."""
+  The projections read only SiLU(temb), which is known when a call starts and is the same on every rank, so under
+  context parallelism each rank would stream all of their weights (2.1 GB of FP8 for the FLUX shape, 13.6 GB of
+  bf16 for the Qwen-Image shape: the one part of a step that does not shrink with the number of GPUs).  Here rank
+  r computes columns [r, r + 1) * cols / W of the concatenated projection and one all-gather hands every rank
+  the whole vector; the blocks then take views of it.  Members are either all FP8 linears (the M <= 4 path of the
+  FP8 product) or all bf16 `nn.Linear` (`cdb_bf16_gemv`); both kernels compute a column in a fixed order that
+  does not depend on the slice, so results equal the per-block products bit for bit.
+  The output lives in one buffer that is overwritten every call, so captured block graphs read it in place."""
 
   def __init__(self, groups: Sequence[Sequence[nn.Module]], group=None):
     import torch.distributed as dist
@@ -124,32 +140,62 @@ class ModulationBank:
     self.world = dist.get_world_size(group)
     self.rank = dist.get_rank(group)
     self.linears = [l for g in groups for l in g]
-    self.fused = fused_group(self.linears)
-    self.cols = self.fused.out_features
+    self.fp8 = _all_fp8(self.linears)
+    if self.fp8:
+      self.fused = fused_group(self.linears)
+      self.cols = self.fused.out_features
+    else:
+      if not all(type(l) is nn.Linear and l.weight.dtype == torch.bfloat16 for l in self.linears):
+        raise ValueError("a modulation bank holds FP8 linears or bf16 nn.Linear layers, not a mixture")
+      self.weight = torch.cat([l.weight.detach() for l in self.linears], dim=0)  # [cols, K]; members become views
+      has_bias = [l.bias is not None for l in self.linears]
+      self.bias = torch.cat([l.bias.detach() if hb else torch.zeros(l.out_features, dtype=torch.bfloat16, device=self.weight.device)
+                             for l, hb in zip(self.linears, has_bias)]) if any(has_bias) else None
+      self.cols = self.weight.shape[0]
     if self.cols % (self.world * 8) != 0:
       raise ValueError("the concatenated modulation width must divide by 8 x the number of ranks")
     self.per_rank = self.cols // self.world
     self.offsets = {}
     start = 0
-    for l in self.linears:
+    for i, l in enumerate(self.linears):
       self.offsets[id(l)] = (start, l.out_features)
+      if not self.fp8:  # the members keep working on their own, on the shared storage
+        l.weight = nn.Parameter(self.weight[start:start + l.out_features], requires_grad=False)
+        if has_bias[i]:
+          l.bias = nn.Parameter(self.bias[start:start + l.out_features], requires_grad=False)
       start += l.out_features
     self._out = None
+
+  def still_valid(self) -> bool:
+    """False once a member's weight no longer lives in the shared storage (the model was moved or reloaded)."""
+    if self.fp8:
+      return _members_share_storage(self.fused, self.linears)
+    base = self.weight.data_ptr()
+    k = self.weight.shape[1] * 2
+    return all(l.weight.device == self.weight.device and l.weight.data_ptr() == base + self.offsets[id(l)][0] * k
+               for l in self.linears)
 
   def compute(self, temb: torch.Tensor) -> None:
     import torch.distributed as dist
     x = F.silu(temb)
-    a_q, a_scale = self.linears[0].quantize_input(x)
     lo, hi = self.rank * self.per_rank, (self.rank + 1) * self.per_rank
-    f = self.fused
-    local = torch.empty((a_q.shape[0], self.per_rank), dtype=torch.bfloat16, device=x.device)
-    _native.fp8_gemm_rowscaled(a_q, a_scale, f.weight_q[lo:hi], f.weight_scale[lo:hi],
-                               None if f.bias is None else f.bias[lo:hi], local)
+    local = torch.empty((x.shape[0], self.per_rank), dtype=torch.bfloat16, device=x.device)
+    if self.fp8:
+      a_q, a_scale = self.linears[0].quantize_input(x)
+      f = self.fused
+      _native.fp8_gemm_rowscaled(a_q, a_scale, f.weight_q[lo:hi], f.weight_scale[lo:hi],
+                                 None if f.bias is None else f.bias[lo:hi], local)
+    else:
+      _native.bf16_gemv(x if x.stride(1) == 1 else x.contiguous(), self.weight[lo:hi],
+                        None if self.bias is None else self.bias[lo:hi], local)
     if self._out is None or self._out.shape[0] != local.shape[0]:
       self._out = torch.empty((local.shape[0], self.cols), dtype=torch.bfloat16, device=x.device)
       self._gathered = torch.empty((self.world, local.shape[0], self.per_rank), dtype=torch.bfloat16, device=x.device)
-    dist.all_gather_into_tensor(self._gathered, local, group=self.group)
-    self._out.view(local.shape[0], self.world, self.per_rank).copy_(self._gathered.permute(1, 0, 2))
+    if self.world > 1:
+      dist.all_gather_into_tensor(self._gathered, local, group=self.group)
+      self._out.view(local.shape[0], self.world, self.per_rank).copy_(self._gathered.permute(1, 0, 2))
+    else:
+      self._out.copy_(local)
 
   def outputs(self, linears: Sequence[nn.Module]) -> List[torch.Tensor]:
     """Views [batch, out_features] of the gathered vector for the given member linears."""

@@ -22,7 +22,7 @@ from ..caching.block_adapters import BlockAdapter, BlockAdapterRegister
 from ..caching.forward_pattern import ForwardPattern
 from .context_parallel import ContextParallelMixin
 from .layers import (RMSNorm, RopeCache, TimestepMLP, UlyssesGroup, gated_add_pair, gelu_linear_pair, joint_attention,
-                     linear_pair, norm_modulate, norm_modulate_linears_pair, timestep_embedding)
+                     linear_pair, modulation_rows, norm_modulate, norm_modulate_linears_pair, timestep_embedding)
 
 
 class _GeluProj(nn.Module):
@@ -67,8 +67,13 @@ class QwenImageTransformerBlock(nn.Module):
 
   def forward(self, hidden_states, encoder_hidden_states, temb, image_rotary_emb):
     a = self.attn
-    shift1, scale1, gate1, shift2, scale2, gate2 = self.img_mod(temb).chunk(6, dim=-1)
-    c_shift1, c_scale1, c_gate1, c_shift2, c_scale2, c_gate2 = self.txt_mod(temb).chunk(6, dim=-1)
+    bank = getattr(self, "mod_bank", None)
+    if bank is not None:  # computed once per call for all blocks, column-sharded over the ranks
+      img, txt = bank.outputs((self.img_mod[1], self.txt_mod[1]))
+    else:
+      img, txt = modulation_rows(temb, self.img_mod[1]), modulation_rows(temb, self.txt_mod[1])
+    shift1, scale1, gate1, shift2, scale2, gate2 = img.chunk(6, dim=-1)
+    c_shift1, c_scale1, c_gate1, c_shift2, c_scale2, c_gate2 = txt.chunk(6, dim=-1)
     (q, k, v), (cq, ck, cv) = norm_modulate_linears_pair(
       (hidden_states, shift1, scale1, (a.to_q, a.to_k, a.to_v)),
       (encoder_hidden_states, c_shift1, c_scale1, (a.add_q_proj, a.add_k_proj, a.add_v_proj)))
@@ -111,6 +116,9 @@ class QwenImageTransformer2DModel(ContextParallelMixin, nn.Module):
   def _cp_blocks(self):
     return list(self.transformer_blocks)
 
+  def _modulation_groups(self, blocks):
+    return [(b.img_mod[1], b.txt_mod[1]) for b in blocks]
+
   def forward(self, hidden_states, encoder_hidden_states, timestep, img_ids, txt_ids):
     n_img = hidden_states.shape[1]
     hidden_states, encoder_hidden_states = self.cp_shard(hidden_states, 1), self.cp_shard(encoder_hidden_states, 1)
@@ -119,6 +127,7 @@ class QwenImageTransformer2DModel(ContextParallelMixin, nn.Module):
     hidden_states = self.img_in(hidden_states)
     encoder_hidden_states = self.txt_in(self.txt_norm(encoder_hidden_states))
     temb = self.time_text_embed(timestep_embedding(timestep * self.time_scale, 256).to(dt))
+    self.modulation_for_call(temb)
     rope = self._rope_cache.get((txt_ids, img_ids), self.axes_dims_rope, dt)
     for block in self.transformer_blocks:
       encoder_hidden_states, hidden_states = block(hidden_states, encoder_hidden_states, temb, rope)

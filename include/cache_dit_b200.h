@@ -310,6 +310,15 @@ CDB_API int cdb_peer_wait(const void* my_flags, int world, void* sync, uint64_t 
 CDB_API int cdb_peer_barrier(void* const* flag_ptrs, const void* my_flags, int world, int my_rank, void* sync,
                      uint64_t timeout_ns, void* stream);
 
+/* Few-row bf16 product for adaLN modulation projections that stay in bf16 (the reference's name filter keeps
+ * layers named *mod* out of FP8, src/cache_dit/quantization/config.py:356-361, so there they are cuBLAS calls
+ * inside the diffusers block): out[m, n] = bf16(sum_k x[m, k] * w[n, k] + bias[n]) for M <= 4 rows, fp32
+ * accumulation, w [N, K] bf16 row-major and 16-byte aligned, K % 8 == 0, M * K * 4 <= 48 KB.  Streams the weights
+ * once; a column's result does not depend on which row slice of `w` a call covers, so a context-parallel run can
+ * shard the columns over the ranks without changing a bit. */
+CDB_API int cdb_bf16_gemv(const void* x, int64_t ld_x, const void* w, const void* bias, void* out, int64_t ld_out,
+                          int64_t M, int64_t N, int64_t K, void* stream);
+
 /* cdb_gated_residual on two (x, y, gate, out) sets of the same width in one launch. */
 CDB_API int cdb_gated_residual_pair(const void* x, const void* y, int64_t ld_y, const void* gate, int64_t ld_gate,
                             void* out, int64_t rows, int64_t rows_per_batch, const void* x2, const void* y2,

@@ -104,11 +104,18 @@ def main():
   peer, st_peer, _ = generation(world, "peer", False)
   graphed, st_graph, replays = generation(world, "peer", True)
   wire8, st_wire8, _ = generation(world, "peer", True, fp8_wire=True)
+  # the column-sharded modulation bank (on by default in everything above) against per-block modulation products
+  os.environ["CACHE_DIT_B200_MODULATION_BANK"] = "0"
+  no_bank, _, _ = generation(world, "peer", False)
+  qwen_no_bank, qwen_no_bank_mask, _ = other_model(world, "qwen", "peer", False)
+  os.environ["CACHE_DIT_B200_MODULATION_BANK"] = "1"
   rel8 = float((wire8[-1][0].float() - peer[-1][0].float()).norm() / peer[-1][0].float().norm())
   others = {}
   for which in ("qwen", "wan"):
     o_nccl, m_nccl, _ = other_model(world, which, "nccl", False)
     o_peer, m_peer, st = other_model(world, which, "peer", False)
+    if which == "qwen":
+      qwen_peer_out, qwen_peer_mask = o_peer, m_peer
     o_graph, m_graph, st_g = other_model(world, which, "peer", True)
     others[which] = dict(masks=[m_nccl, m_peer, m_graph], status=[st, st_g],
                          peer_equals_nccl=bool(torch.equal(o_nccl, o_peer)),
@@ -120,6 +127,8 @@ def main():
     peer_equals_nccl=all(torch.equal(a, b) for (a, _), (b, _) in zip(nccl, peer)),
     graphs_equal_peer=all(torch.equal(a, b) for (a, _), (b, _) in zip(peer, graphed)),
     status_peer=st_peer, status_graphs=st_graph, replays=replays,
+    bank_equals_per_block=all(torch.equal(a, b) and ma == mb for (a, ma), (b, mb) in zip(peer, no_bank)),
+    qwen_bank_equals_per_block=bool(torch.equal(qwen_no_bank, qwen_peer_out)) and qwen_no_bank_mask == qwen_peer_mask,
     finite=bool(torch.isfinite(peer[-1][0]).all().item()))
   with open(os.path.join(out_dir, f"rank{rank}.json"), "w") as f:
     json.dump(report, f)

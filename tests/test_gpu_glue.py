@@ -137,3 +137,36 @@ def test_gated_residual_pair_equals_separate(nat):
   a, b = nat.gated_residual_pair(*sets[0], *sets[1])
   assert torch.equal(a, sets[0][0] + sets[0][1][:, None] * sets[0][2])
   assert torch.equal(b, sets[1][0] + sets[1][1][:, None] * sets[1][2])
+
+
+@pytest.mark.parametrize("m,n,k,bias", [(1, 1536, 256, True), (2, 18432, 3072, True), (4, 1000, 512, False), (3, 72, 3072, True)])
+def test_bf16_gemv_matches_linear_and_is_slice_independent(m, n, k, bias):
+  """`cdb_bf16_gemv` (modulation projections that stay in bf16): fp32-accumulated product within one bf16 step of an
+  fp32 reference, rows of x / out strided, and - what the column-sharded modulation bank relies on - a column's
+  bits do not depend on which row slice of the weight matrix the call covers."""
+  from cache_dit_b200 import _native as nat
+  g = torch.Generator().manual_seed(m * n + k)
+  x_wide = torch.randn(m, k + 8, generator=g).to("cuda", torch.bfloat16)
+  x = x_wide[:, :k]  # strided rows
+  w = (0.05 * torch.randn(n, k, generator=g)).to("cuda", torch.bfloat16)
+  b = torch.randn(n, generator=g).to("cuda", torch.bfloat16) if bias else None
+  out_wide = torch.full((m, n + 16), float("nan"), device="cuda", dtype=torch.bfloat16)
+  out = out_wide[:, 8:8 + n]
+  nat.bf16_gemv(x, w, b, out)
+  torch.cuda.synchronize()
+  ref = x.float() @ w.float().t() + (b.float() if bias else 0.0)
+  assert torch.isnan(out_wide[:, :8]).all() and torch.isnan(out_wide[:, 8 + n:]).all()
+  assert ((out.float() - ref).abs() <= 2.0**-7 * ref.abs() + 1e-3).all().item()
+  lo, hi = (n // 3) // 8 * 8, (2 * n // 3) // 8 * 8
+  part = torch.empty(m, hi - lo, device="cuda", dtype=torch.bfloat16)
+  nat.bf16_gemv(x, w[lo:hi], None if b is None else b[lo:hi], part)
+  assert torch.equal(part, out[:, lo:hi])
+  from cache_dit_b200.synthetic.layers import modulation_rows
+  lin = torch.nn.Linear(k, n, bias=bias).to("cuda", torch.bfloat16)
+  with torch.no_grad():
+    lin.weight.copy_(w)
+    if bias:
+      lin.bias.copy_(b)
+    got = modulation_rows(x_wide[:, :k].contiguous(), lin)
+    want = lin(torch.nn.functional.silu(x_wide[:, :k].contiguous()))
+  assert ((got.float() - want.float()).abs() <= 2.0**-6 * want.float().abs() + 2e-3).all().item()

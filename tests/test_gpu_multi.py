@@ -58,3 +58,11 @@ def test_fp8_on_the_wire(reports):
     assert f["finite"] and f["status"] == 0
     assert f["rel"] < 0.1, f["rel"]
   assert reports[0]["fp8_wire"]["masks"] == reports[1]["fp8_wire"]["masks"]
+
+
+def test_modulation_bank_equals_per_block_products(reports):
+  """All blocks' adaLN modulation vectors as one column-sharded product + all-gather per call (FP8 members in the
+  FLUX shape, bf16 members in the Qwen-Image shape) against one product per block and rank: same bits, same masks."""
+  for r in reports:
+    assert r["bank_equals_per_block"]
+    assert r["qwen_bank_equals_per_block"]

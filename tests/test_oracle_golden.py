@@ -74,3 +74,27 @@ def test_sharded_mean_of_means_differs_only_for_uneven_shards():
   even = O.rel_l1(prev[:, :6888], cur[:, :6888], "fp32", shards=8)
   assert abs(even - O.rel_l1(prev[:, :6888], cur[:, :6888], "fp32")) < 1e-3 * whole
   assert O.rel_l1(prev, cur, "fp32", shards=8) != whole
+
+
+def test_torch_cpu_ops_equal_the_numpy_restatement():
+  """oracle/cache_ops_torch.py (the reference's eager op sequences on CPU tensors, used to time the CPU baseline)
+  against oracle/cache_oracle.py on bf16 and fp32 inputs: same bits for every tensor result, same check value."""
+  import numpy as np
+  import torch
+  from oracle import cache_ops_torch as T
+  from oracle import cache_oracle as O
+  g = torch.Generator().manual_seed(3)
+  for dtype, name in ((torch.bfloat16, "bf16"), (torch.float32, "fp32")):
+    prev = torch.randn(1, 96, 320, generator=g).to(dtype)
+    cur = (prev.float() + 0.05 * torch.randn(1, 96, 320, generator=g)).to(dtype)
+    older = (prev.float() - 0.07 * torch.randn(1, 96, 320, generator=g)).to(dtype)
+    f = lambda t: t.float().numpy()
+    assert T.rel_l1(prev, cur) == float(O.rel_l1(f(prev), f(cur), name))
+    np.testing.assert_array_equal(f(T.residual(cur, prev)), O.residual(f(cur), f(prev), name))
+    y = T.residual(cur, prev)
+    got = T.taylor_derivatives(y, [older, None], 3, True)
+    want = O.taylor_derivatives(f(y), [f(older), None], 3, True, name)
+    np.testing.assert_array_equal(f(got[1]), want[1])
+    np.testing.assert_array_equal(f(T.taylor_series(got, 2)), O.taylor_series(want, 2, name))
+    np.testing.assert_array_equal(f(T.apply_add(T.taylor_series(got, 2), cur)),
+                                  O.apply_add(O.taylor_series(want, 2, name), f(cur), name))
