@@ -111,6 +111,11 @@ class CachedBlocks(torch.nn.Module):
     return (a, b) if self.forward_pattern.Return_H_First else (b, a)
 
   def _run(self, blocks, hidden, encoder, args, kwargs):
+    # A model may want to get per-call work for exactly the blocks that are about to run out of the way first
+    # (e.g. their adaLN modulation vectors as one product): it is told here, outside any captured graph.
+    prepare = getattr(self.transformer, "prepare_blocks", None)
+    if prepare is not None and len(blocks) > 0:
+      prepare(blocks)
     runner = self.graph_runner
     if runner is None or len(blocks) == 0:
       return self._run_eager(blocks, hidden, encoder, args, kwargs)

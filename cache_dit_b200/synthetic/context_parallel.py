@@ -67,9 +67,30 @@ class ContextParallelMixin:
         self._mod_bank_wanted = False
         return
       self._mod_bank = bank
+      self._mod_bank_index = {id(b): i for i, b in enumerate(self._cp_block_list)}
       for b in self._cp_block_list:
         b.mod_bank = bank
-    bank.compute(temb)
+    bank.begin_call(temb)
+    if self._runs_blocks_itself():
+      bank.prepare(0, len(self._cp_block_list))
+
+  def _runs_blocks_itself(self) -> bool:
+    """False while a cache runner stands in for the block list (it announces the blocks it runs)."""
+    return True
+
+  @staticmethod
+  def is_cache_runner_list(block_list) -> bool:
+    """During `forward` of a cache-enabled model a block list attribute holds a one-element list with the runner."""
+    return len(block_list) == 1 and hasattr(block_list[0], "context_manager") and hasattr(block_list[0], "transformer_blocks")
+
+  def prepare_blocks(self, blocks) -> None:
+    """Called by the cache runner before it runs `blocks` (a contiguous slice of the block list)."""
+    bank = getattr(self, "_mod_bank", None)
+    if bank is None or not getattr(self, "_mod_bank_wanted", False):
+      return
+    index = self._mod_bank_index
+    if id(blocks[0]) in index:
+      bank.prepare(index[id(blocks[0])], index[id(blocks[-1])] + 1)
 
   def cp_active(self) -> bool:
     return self._cp is not None and self._cp.world > 1

@@ -213,9 +213,22 @@ class FluxTransformer2DModel(nn.Module):
       except ValueError:
         self._mod_bank_wanted = False
         return
+      self._mod_bank_index = {id(b): i for i, b in enumerate(double + single)}
       for b in double + single:
         b.mod_bank = self._mod_bank
-    self._mod_bank.compute(temb)
+    self._mod_bank.begin_call(temb)
+    first = self.transformer_blocks
+    if not (len(first) == 1 and hasattr(first[0], "context_manager")):  # no cache runner stands in for the block list
+      self._mod_bank.prepare(0, len(self._mod_bank_index))
+
+  def prepare_blocks(self, blocks) -> None:
+    """Called by the cache runner before it runs `blocks` (a contiguous slice of the 57-block list)."""
+    bank = getattr(self, "_mod_bank", None)
+    if bank is None or not getattr(self, "_mod_bank_wanted", False):
+      return
+    index = self._mod_bank_index
+    if id(blocks[0]) in index:
+      bank.prepare(index[id(blocks[0])], index[id(blocks[-1])] + 1)
 
   def forward(self, hidden_states, encoder_hidden_states, pooled_projections, timestep, img_ids, txt_ids,
               guidance=None):

@@ -128,8 +128,9 @@ class ModulationBank:
   The projections read only SiLU(temb), which is known when a call starts and is the same on every rank, so under
   context parallelism each rank would stream all of their weights (2.1 GB of FP8 for the FLUX shape, 13.6 GB of
   bf16 for the Qwen-Image shape: the one part of a step that does not shrink with the number of GPUs).  Here rank
-  r computes columns [r, r + 1) * cols / W of the concatenated projection and one all-gather hands every rank
-  the whole vector; the blocks then take views of it.  Members are either all FP8 linears (the M <= 4 path of the
+  r computes its 1/W of the columns of the blocks that are about to run (all of them without a cache runner;
+  with one, the first blocks at the start of a call and the rest only when the step turns out to be computed) and
+  one all-gather hands every rank the whole vector; the blocks then take views of it.  Members are either all FP8 linears (the M <= 4 path of the
   FP8 product) or all bf16 `nn.Linear` (`cdb_bf16_gemv`); both kernels compute a column in a fixed order that
   does not depend on the slice, so results equal the per-block products bit for bit.
   The output lives in one buffer that is overwritten every call, so captured block graphs read it in place."""
@@ -152,10 +153,15 @@ class ModulationBank:
       self.bias = torch.cat([l.bias.detach() if hb else torch.zeros(l.out_features, dtype=torch.bfloat16, device=self.weight.device)
                              for l, hb in zip(self.linears, has_bias)]) if any(has_bias) else None
       self.cols = self.weight.shape[0]
-    if self.cols % (self.world * 8) != 0:
-      raise ValueError("the concatenated modulation width must divide by 8 x the number of ranks")
-    self.per_rank = self.cols // self.world
+    if any(l.out_features % 8 for l in self.linears):
+      raise ValueError("modulation widths must be multiples of 8")
     self.offsets = {}
+    self.group_cols = []  # per group (block): [first column, last column + 1)
+    start = 0
+    for g in groups:
+      width = sum(l.out_features for l in g)
+      self.group_cols.append((start, start + width))
+      start += width
     start = 0
     for i, l in enumerate(self.linears):
       self.offsets[id(l)] = (start, l.out_features)
@@ -175,27 +181,44 @@ class ModulationBank:
     return all(l.weight.device == self.weight.device and l.weight.data_ptr() == base + self.offsets[id(l)][0] * k
                for l in self.linears)
 
-  def compute(self, temb: torch.Tensor) -> None:
-    import torch.distributed as dist
+  def begin_call(self, temb: torch.Tensor) -> None:
+    """Remember this call's SiLU(temb) (quantized once for FP8 members); nothing is computed yet."""
     x = F.silu(temb)
-    lo, hi = self.rank * self.per_rank, (self.rank + 1) * self.per_rank
-    local = torch.empty((x.shape[0], self.per_rank), dtype=torch.bfloat16, device=x.device)
+    self._x = x if x.stride(1) == 1 else x.contiguous()
     if self.fp8:
-      a_q, a_scale = self.linears[0].quantize_input(x)
+      self._a_q, self._a_scale = self.linears[0].quantize_input(self._x)
+    if self._out is None or self._out.shape[0] != x.shape[0]:
+      self._out = torch.empty((x.shape[0], self.cols), dtype=torch.bfloat16, device=x.device)
+
+  def prepare(self, first: int, last: int) -> None:
+    """Compute the vectors of groups [first, last) (one group per block): this rank's share of their columns as
+    one product, then one all-gather.  Called before the blocks run - with a cache runner once for the first
+    blocks of a call and, only when the step is computed, once for the rest."""
+    import torch.distributed as dist
+    c0, c1 = self.group_cols[first][0], self.group_cols[last - 1][1]
+    width = c1 - c0
+    batch = self._x.shape[0]
+    sharded = self.world > 1 and width % (self.world * 8) == 0
+    per = width // self.world if sharded else width
+    lo = c0 + (self.rank * per if sharded else 0)
+    local = torch.empty((batch, per), dtype=torch.bfloat16, device=self._x.device)
+    if self.fp8:
       f = self.fused
-      _native.fp8_gemm_rowscaled(a_q, a_scale, f.weight_q[lo:hi], f.weight_scale[lo:hi],
-                                 None if f.bias is None else f.bias[lo:hi], local)
+      _native.fp8_gemm_rowscaled(self._a_q, self._a_scale, f.weight_q[lo:lo + per], f.weight_scale[lo:lo + per],
+                                 None if f.bias is None else f.bias[lo:lo + per], local)
     else:
-      _native.bf16_gemv(x if x.stride(1) == 1 else x.contiguous(), self.weight[lo:hi],
-                        None if self.bias is None else self.bias[lo:hi], local)
-    if self._out is None or self._out.shape[0] != local.shape[0]:
-      self._out = torch.empty((local.shape[0], self.cols), dtype=torch.bfloat16, device=x.device)
-      self._gathered = torch.empty((self.world, local.shape[0], self.per_rank), dtype=torch.bfloat16, device=x.device)
-    if self.world > 1:
-      dist.all_gather_into_tensor(self._gathered, local, group=self.group)
-      self._out.view(local.shape[0], self.world, self.per_rank).copy_(self._gathered.permute(1, 0, 2))
+      _native.bf16_gemv(self._x, self.weight[lo:lo + per], None if self.bias is None else self.bias[lo:lo + per], local)
+    if sharded:
+      gathered = torch.empty((self.world, batch, per), dtype=torch.bfloat16, device=local.device)
+      dist.all_gather_into_tensor(gathered, local, group=self.group)
+      self._out[:, c0:c1].unflatten(1, (self.world, per)).copy_(gathered.permute(1, 0, 2))
     else:
-      self._out.copy_(local)
+      self._out[:, c0:c1].copy_(local)
+
+  def compute(self, temb: torch.Tensor) -> None:
+    """All groups at once (a model that runs without a cache runner)."""
+    self.begin_call(temb)
+    self.prepare(0, len(self.group_cols))
 
   def outputs(self, linears: Sequence[nn.Module]) -> List[torch.Tensor]:
     """Views [batch, out_features] of the gathered vector for the given member linears."""

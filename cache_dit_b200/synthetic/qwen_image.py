@@ -119,6 +119,9 @@ class QwenImageTransformer2DModel(ContextParallelMixin, nn.Module):
   def _modulation_groups(self, blocks):
     return [(b.img_mod[1], b.txt_mod[1]) for b in blocks]
 
+  def _runs_blocks_itself(self) -> bool:
+    return not self.is_cache_runner_list(self.transformer_blocks)
+
   def forward(self, hidden_states, encoder_hidden_states, timestep, img_ids, txt_ids):
     n_img = hidden_states.shape[1]
     hidden_states, encoder_hidden_states = self.cp_shard(hidden_states, 1), self.cp_shard(encoder_hidden_states, 1)
