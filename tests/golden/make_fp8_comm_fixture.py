@@ -6,15 +6,15 @@ src/cache_dit/kernels/triton/_ops_registery.py:50-180 and called from
 src/cache_dit/distributed/core/_distributed_primitives.py:741-813).  They need a GPU, and the reference tree
 does not exist on the GPU machine, so this script works in two steps:
 
-  here (reference tree present, no GPU):
-      python tests/golden/make_fp8_comm_fixture.py --stage
+  where a checkout of the reference exists (no GPU needed):
+      python tests/golden/make_fp8_comm_fixture.py --stage --reference /path/to/cache-dit
     places unmodified copies of the three Triton source files the ops need under baseline/_ref/ (git-ignored: not part
     of this repository's history; a `pip install --target baseline/_ref` of the reference fails here because its build
     needs setuptools-scm, which is not installed);
   on a B200:
-      python tests/golden/make_fp8_comm_fixture.py --out gpurun_out/fp8_comm_reference.npz
+      python tests/golden/make_fp8_comm_fixture.py [--out FILE]
     imports the staged ops, runs them on small seeded inputs and stores inputs (bf16 bit patterns) and outputs
-    (raw bytes).  The file is then committed as tests/golden/fp8_comm_reference.npz.
+    (raw bytes) as tests/golden/fp8_comm_reference.npz, which is committed.
 
 Cases (all bf16 inputs, seeded):
   qkv.<name>  x [B, S, W, N, D] -> fp8_comm_qkv_permute_quant -> [W, S, B, N, D + 4] bytes (D codes + fp32 scale per
@@ -31,17 +31,17 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 STAGED = os.path.join(ROOT, "baseline", "_ref", "cache_dit_triton_kernels")
-REFERENCE_DIR = "/root/reference/src/cache_dit/kernels/triton"
+REFERENCE_SUBDIR = os.path.join("src", "cache_dit", "kernels", "triton")
 FILES = ["_float8_comm.py", "_merge_attn_states.py", "_ops_registery.py"]
 
 QKV_CASES = {"w2_d64": (1, 40, 2, 2, 64), "w4_d128": (2, 24, 4, 2, 128), "w8_d128": (1, 33, 8, 3, 128)}
 O_CASES = {"d64": (160, 64), "d128": (2 * 24 * 8, 128)}
 
 
-def stage():
+def stage(reference_root):
   os.makedirs(STAGED, exist_ok=True)
   for name in FILES:
-    shutil.copyfile(os.path.join(REFERENCE_DIR, name), os.path.join(STAGED, name))
+    shutil.copyfile(os.path.join(reference_root, REFERENCE_SUBDIR, name), os.path.join(STAGED, name))
   with open(os.path.join(STAGED, "__init__.py"), "w") as f:
     f.write("")
   print("staged", FILES, "->", STAGED)
@@ -108,9 +108,12 @@ def generate(out_path):
 if __name__ == "__main__":
   ap = argparse.ArgumentParser()
   ap.add_argument("--stage", action="store_true")
-  ap.add_argument("--out", default=os.path.join(ROOT, "gpurun_out", "fp8_comm_reference.npz"))
+  ap.add_argument("--reference", help="root of a checkout of the reference (with --stage)")
+  ap.add_argument("--out", default=os.path.join(HERE, "fp8_comm_reference.npz"))
   a = ap.parse_args()
   if a.stage:
-    stage()
+    if not a.reference:
+      ap.error("--stage needs --reference /path/to/cache-dit")
+    stage(a.reference)
   else:
     generate(a.out)
