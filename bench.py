@@ -68,7 +68,12 @@ class ClockSampler:
            "clocks_event_reasons.sw_power_cap")
 
   def __init__(self, index: int):
-    self.index = index
+    # nvidia-smi numbers the machine's GPUs, torch the visible ones: address the device by UUID where torch knows it
+    self.index = str(index)
+    try:
+      self.index = "GPU-" + str(torch.cuda.get_device_properties(index).uuid)
+    except Exception:
+      pass
     self.proc = None
     self.lines = []
 

@@ -43,6 +43,7 @@ SIGNATURES = {
                                      c_int64, c_int64, c_int64, c_void_p, c_void_p]),
   "cdb_fp8_gemm_rowscaled_grouped": (c_int, [c_void_p, c_int, c_void_p, c_void_p]),
   "cdb_tuning_set_gemm_tile_cols": (c_int, [c_int]),
+  "cdb_tuning_set_gemm_kernel": (c_int, [c_int]),
   "cdb_qk_norm_rope": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                                c_int64, c_int64, c_int, c_int, c_int, c_float, c_void_p]),
   "cdb_gated_residual_pair": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64,

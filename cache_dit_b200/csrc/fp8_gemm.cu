@@ -1018,6 +1018,21 @@ static std::atomic<int> g_forced_tile_cols{[] {
   return (v >= 16 && v <= BN && v % 16 == 0) ? v : 0;
 }()};
 
+// Tuning / testing knob: 0 = choose by shape, 1 = single-CTA kernel, 2 = CTA-pair kernel.  Initialised from
+// CDB_GEMM_KERNEL ("1cta" | "2cta").
+static std::atomic<int> g_forced_kernel{[] {
+  const char* env = getenv("CDB_GEMM_KERNEL");
+  if (env && strcmp(env, "1cta") == 0) return 1;
+  if (env && strcmp(env, "2cta") == 0) return 2;
+  return 0;
+}()};
+
+extern "C" int cdb_tuning_set_gemm_kernel(int kind) {
+  if (kind < 0 || kind > 2) return CDB_ERR_BAD_ARGUMENT;
+  g_forced_kernel.store(kind, std::memory_order_relaxed);
+  return CDB_OK;
+}
+
 extern "C" int cdb_tuning_set_gemm_tile_cols(int cols) {
   if (cols != 0 && (cols < 16 || cols > BN || cols % 16 != 0)) return CDB_ERR_BAD_ARGUMENT;
   g_forced_tile_cols.store(cols, std::memory_order_relaxed);
@@ -1026,35 +1041,31 @@ extern "C" int cdb_tuning_set_gemm_tile_cols(int cols) {
 
 // Tile width of the single-CTA kernel for one launch.  With 128-row tiles a rank shard of a context-parallel
 // run has only 3-18 row tiles, and at the full width of 256 columns the tile count often leaves most of the
-// last wave idle (576 x 3072: 60 tiles on 148 SMs; 576 x 9216: 180 tiles = 1.2 waves).  A narrower tile costs
-// operand bandwidth per flop (the A tile is re-read for fewer columns) but fills the waves, so the width is the
-// multiple of 16 that minimises a small cost model:
-//     waves x (K blocks x cycles per K block + epilogue) with
-//     cycles per K block = max(tensor time 2 x bn, operand bytes (16 KB + 128 x bn) / ~100 bytes per clock,
-//                              load latency / stages of the ring at that width).
-// The full width wins ties and anything within 3 %, so tall problems keep the shape they were tuned with.
-static int choose_tile_cols(const cdb_gemm_problem_abi* g, int n, int sms) {
+// last wave idle (576 x 3072: 60 tiles on 148 SMs; 576 x 9216: 180 tiles = 1.2 waves).  A narrower tile fills
+// the waves but buys less than its width suggests: timed on rank-shard shapes (cold weights, 576 - 2304 rows,
+// widths 128 / 192 / 256) a K block of a tile takes about 760 + bn clocks, i.e. mostly a width-independent
+// part.  So the width is the multiple of 16 that minimises
+//     waves x (K blocks x (760 + 1.04 x bn) + epilogue per 64 columns) + launch,
+// and the full width wins ties and anything within 3 %, so tall problems keep the shape they were tuned with.
+static int choose_tile_cols(const cdb_gemm_problem_abi* g, int n, int sms, double* cost_out) {
   const int forced = g_forced_tile_cols.load(std::memory_order_relaxed);
-  if (forced) return forced;
   auto cost_of = [&](int bn) {
     int64_t tiles = 0;
     double per_tile = 0.0;
     for (int i = 0; i < n; ++i) {
       const int64_t mt = (g[i].M + BM - 1) / BM, nt = (g[i].N + bn - 1) / bn, kb = (g[i].K + BK - 1) / BK;
       tiles += mt * nt;
-      const double tensor = 2.0 * bn, ingest = (A_STAGE_BYTES + 128.0 * bn) / 100.0;
-      // the ring hides only `stages` K blocks of load latency (~2400 clocks from issue to use under load)
-      const int stage_bytes = A_STAGE_BYTES + bn * BK;
-      const int stages = SMEM_TILE_BYTES / stage_bytes < MAX_STAGES ? SMEM_TILE_BYTES / stage_bytes : MAX_STAGES;
-      const double latency = 2400.0 / stages;
-      double per_kb = tensor > ingest ? tensor : ingest;
-      per_kb = per_kb > latency ? per_kb : latency;
+      const double per_kb = 760.0 + 1.04 * bn;
       const double t = kb * per_kb + 150.0 * ((bn + 63) / 64);
       per_tile = t > per_tile ? t : per_tile;
     }
     const int64_t waves = (tiles + sms - 1) / sms;
     return waves * per_tile + 3000.0;
   };
+  if (forced) {
+    *cost_out = cost_of(forced);
+    return forced;
+  }
   int best = BN;
   double best_cost = 0.97 * cost_of(BN);
   for (int bn = BN - 16; bn >= 64; bn -= 16) {
@@ -1064,7 +1075,27 @@ static int choose_tile_cols(const cdb_gemm_problem_abi* g, int n, int sms) {
       best_cost = c;
     }
   }
+  *cost_out = best == BN ? cost_of(BN) : best_cost;
   return best;
+}
+
+// The same model for the CTA-pair kernel (256 x 256 tiles, one per pair of SMs): a K block of a pair tile takes
+// about 875 clocks on the same shapes, against 1026 for a single-CTA tile of that width (a CTA of a pair takes in
+// only its half of the weight tile, and the smaller stage gives its ring 6 stages instead of 4).  A pair tile
+// is the cheaper one, and what decides is the wave count: 256-row tiles waste up to a tile of rows (576 rows =
+// 2.25 tiles) and there are half as many tile slots.
+static double pair_cost(const cdb_gemm_problem_abi* g, int n, int sms) {
+  int64_t tiles = 0;
+  double per_tile = 0.0;
+  for (int i = 0; i < n; ++i) {
+    const int64_t mt = (g[i].M + P_BM - 1) / P_BM, nt = (g[i].N + BN - 1) / BN, kb = (g[i].K + BK - 1) / BK;
+    tiles += mt * nt;
+    const double t = kb * 875.0 + 150.0 * (BN / 64);
+    per_tile = t > per_tile ? t : per_tile;
+  }
+  const int64_t slots = sms / 2 > 0 ? sms / 2 : 1;
+  const int64_t waves = (tiles + slots - 1) / slots;
+  return waves * per_tile + 3000.0;
 }
 
 static int launch_few_rows(const cdb_gemm_problem_abi& g, int sms, cudaStream_t st) {
@@ -1110,21 +1141,20 @@ extern "C" int cdb_fp8_gemm_rowscaled_grouped(const void* problems_v, int count,
                                P_SMEM_TOTAL_BYTES);
     return (int64_t)e;
   });
-  static const int mode = [] {  // 0 = choose by shape, 1 = single-CTA kernel, 2 = CTA-pair kernel
-    const char* env = getenv("CDB_GEMM_KERNEL");  // tuning / testing knob: "1cta" | "2cta"
-    if (env && strcmp(env, "1cta") == 0) return 1;
-    if (env && strcmp(env, "2cta") == 0) return 2;
-    return 0;
-  }();
+  const int mode = g_forced_kernel.load(std::memory_order_relaxed);
   CDB_CUDA_CHECK(attr_err);
   const int sms = sm_count();
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (n == 1 && mode == 0 && g[0].M <= GEMV_MAX_M && g[0].M * g[0].K * 2 <= 48 * 1024) return launch_few_rows(g[0], sms, st);
-  // CTA pairs pay off on tall problems; below ~4096 rows (rank shards of a context-parallel run: 2304,
-  // 1152, 576) the single-CTA kernel's 128-row tiles waste less and measured 4-25 % faster
-  const bool pair = mode == 2 || (mode == 0 && g[0].M >= 4096 && CDB_GEMM_DEFAULT_PAIR);
+  // CTA pairs for tall problems; below 4096 rows (rank shards of a context-parallel run: 2304, 1152, 576 rows)
+  // whichever kernel the wave-count model expects to finish first
+  double single_cost = 0.0;
+  const int single_bn = choose_tile_cols(g, n, sms, &single_cost);
+  const bool width_forced = g_forced_tile_cols.load(std::memory_order_relaxed) != 0;  // a forced width means the single-CTA kernel
+  const bool pair = mode == 2 || (mode == 0 && CDB_GEMM_DEFAULT_PAIR &&
+                                  (g[0].M >= 4096 || (!width_forced && pair_cost(g, n, sms) < single_cost)));
   const int64_t tile_rows = pair ? P_BM : BM;
-  const int bn = pair ? BN : choose_tile_cols(g, n, sms);
+  const int bn = pair ? BN : single_bn;
   GemmProblems ps{};
   ps.count = n;
   int64_t tiles = 0;

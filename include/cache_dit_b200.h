@@ -207,6 +207,11 @@ CDB_API int cdb_fp8_gemm_rowscaled(const void* a_q, const float* a_scale, const 
  * `cols` fixes the width for every later launch of the process, 0 restores the model.  The environment variable
  * CDB_GEMM_BN sets the initial value.  Results do not depend on the width (bitwise). */
 CDB_API int cdb_tuning_set_gemm_tile_cols(int cols);
+/* Tuning knob (no counterpart in the reference): which tile kernel the FP8 product launches.  0 = chosen per
+ * launch by a wave-count model, 1 = the single-CTA kernel, 2 = the CTA-pair kernel (cta_group::2).  The
+ * environment variable CDB_GEMM_KERNEL ("1cta" | "2cta") sets the initial value.  Results do not depend on the
+ * choice (bitwise). */
+CDB_API int cdb_tuning_set_gemm_kernel(int kind);
 /* ------------------------------------------------------------------------------------------
  * Transformer-block glue between the FP8 linears.  No counterpart in the reference: there these
  * are eager PyTorch ops inside the diffusers transformer blocks that cache-dit wraps.  They are

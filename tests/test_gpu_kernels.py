@@ -278,6 +278,48 @@ def test_fp8_gemm_result_is_independent_of_the_tile_width(nat, M, N, K, bias):
   assert nat.gemm_device_status(want.device) == 0
 
 
+@pytest.mark.parametrize("shapes", [[(64, 3072, 512)], [(576, 3072, 1024)], [(894, 1000, 256)], [(1152, 3080, 512)],
+                                    [(576, 9216, 512), (64, 9216, 512)], [(1024, 3072, 1536), (128, 3072, 1536)]])
+def test_fp8_gemm_pair_kernel_gives_the_single_cta_kernels_bits(nat, shapes):
+  """Below 4096 rows a wave-count model picks the single-CTA or the CTA-pair kernel per launch (rank shards of a
+  context-parallel run).  Both accumulate every output element over the K blocks in the same order, so the
+  choice must not change a bit: rows that fill a quarter of a 256-row pair tile, ragged row and column counts,
+  a strided output, and two products in one launch."""
+  lib = nat.lib()
+  problems = {1: [], 2: [], 0: []}
+  wides = {1: [], 2: [], 0: []}
+  for i, (M, N, K) in enumerate(shapes):
+    x_d, _ = activations(M, K, M + K + i)
+    w_d, _ = activations(N, K, N + K + i)
+    g = torch.Generator().manual_seed(7 + i)
+    b = torch.randn(N, generator=g).to(torch.bfloat16).cuda()
+    aq = torch.empty(M, K, dtype=torch.float8_e4m3fn, device="cuda")
+    sa = torch.empty(M, dtype=torch.float32, device="cuda")
+    wq = torch.empty(N, K, dtype=torch.float8_e4m3fn, device="cuda")
+    sw = torch.empty(N, dtype=torch.float32, device="cuda")
+    nat.fp8_quant_rows(x_d, aq, sa)
+    nat.fp8_quant_rows(w_d, wq, sw)
+    for kind in (1, 2, 0):
+      wide = torch.full((M, N + 24), float("nan"), dtype=torch.bfloat16, device="cuda")
+      wides[kind].append(wide)
+      problems[kind].append((aq, sa, wq, sw, b, wide[:, 8:8 + N]))
+  try:
+    for kind in (1, 2, 0):
+      assert lib.cdb_tuning_set_gemm_kernel(kind) == 0
+      nat.fp8_gemm_rowscaled_grouped(problems[kind])
+      torch.cuda.synchronize()
+    assert lib.cdb_tuning_set_gemm_kernel(3) != 0
+  finally:
+    lib.cdb_tuning_set_gemm_kernel(0)
+  for i, (M, N, K) in enumerate(shapes):
+    single = wides[1][i]
+    assert torch.isfinite(single[:, 8:8 + N]).all()
+    for kind in (2, 0):
+      assert torch.equal(wides[kind][i][:, 8:8 + N], single[:, 8:8 + N]), (kind, i)
+      assert torch.isnan(wides[kind][i][:, :8]).all() and torch.isnan(wides[kind][i][:, 8 + N:]).all(), (kind, i)
+  assert nat.gemm_device_status(torch.device("cuda")) == 0
+
+
 def test_fp8_gemm_strided_output_and_back_to_back(nat):
   M, N, K = 256, 512, 256
   x_d, _ = activations(M, K, 1)
