@@ -39,9 +39,12 @@ SIGNATURES = {
                                             c_void_p, c_void_p, c_int64, c_int, c_float, c_void_p]),
   "cdb_fp8_quant_rows_concat_gelu": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64,
                                              c_void_p, c_void_p, c_void_p]),
+  "cdb_fp8_quant_rows_concat": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64,
+                                             c_void_p, c_void_p, c_void_p]),
   "cdb_fp8_gemm_rowscaled": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                                      c_int64, c_int64, c_int64, c_void_p, c_void_p]),
   "cdb_fp8_gemm_rowscaled_grouped": (c_int, [c_void_p, c_int, c_void_p, c_void_p]),
+  "cdb_fp8_gemm_rowscaled_grouped_act": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
   "cdb_tuning_set_gemm_tile_cols": (c_int, [c_int]),
   "cdb_tuning_set_gemm_kernel": (c_int, [c_int]),
   "cdb_qk_norm_rope": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
@@ -364,8 +367,10 @@ def bf16_gemv(x2d, w, bias, out):
   check(st, "cdb_bf16_gemv")
 
 
-def fp8_quant_rows_concat_gelu(head2d, tail2d, q, scale):
-  """Quantize rows of [head | gelu_tanh(tail)] (bf16 matrices, rows may be strided) into q / scale."""
+def fp8_quant_rows_concat_gelu(head2d, tail2d, q, scale, tail_activated=False):
+  """Quantize rows of [head | gelu_tanh(tail)] (bf16 matrices, rows may be strided) into q / scale.  With
+  `tail_activated` the tail already holds gelu_tanh(...) (written by a product with an activation in its
+  epilogue) and is only concatenated."""
   _need_cuda(head2d, tail2d, q, scale)
   _need_contig(q, scale)
   for t in (head2d, tail2d):
@@ -375,10 +380,11 @@ def fp8_quant_rows_concat_gelu(head2d, tail2d, q, scale):
   c2 = tail2d.shape[1]
   if tail2d.shape[0] != rows or q.shape != (rows, c1 + c2):
     raise RuntimeError("fp8_quant_rows_concat_gelu: row counts / output width do not match")
-  st = lib().cdb_fp8_quant_rows_concat_gelu(_ptr(head2d), c1, head2d.stride(0) if rows > 1 else max(c1, head2d.stride(0)),
-                                            _ptr(tail2d), c2, tail2d.stride(0) if rows > 1 else max(c2, tail2d.stride(0)),
-                                            rows, _ptr(q), _ptr(scale), _stream(head2d))
-  check(st, "cdb_fp8_quant_rows_concat_gelu")
+  fn = lib().cdb_fp8_quant_rows_concat if tail_activated else lib().cdb_fp8_quant_rows_concat_gelu
+  st = fn(_ptr(head2d), c1, head2d.stride(0) if rows > 1 else max(c1, head2d.stride(0)),
+          _ptr(tail2d), c2, tail2d.stride(0) if rows > 1 else max(c2, tail2d.stride(0)),
+          rows, _ptr(q), _ptr(scale), _stream(head2d))
+  check(st, "cdb_fp8_quant_rows_concat" if tail_activated else "cdb_fp8_quant_rows_concat_gelu")
 
 
 # ---- Ulysses exchange over peer memory ---------------------------------------------------------
@@ -547,8 +553,9 @@ class GemmProblem(ctypes.Structure):
               ("out", c_void_p), ("M", c_int64), ("N", c_int64), ("K", c_int64), ("ld_out", c_int64)]
 
 
-def fp8_gemm_rowscaled_grouped(problems):
-  """Up to two products (a_q, a_scale, w_q, w_scale, bias, out) in one launch; see fp8_gemm_rowscaled."""
+def fp8_gemm_rowscaled_grouped(problems, gelu_from=None):
+  """Up to two products (a_q, a_scale, w_q, w_scale, bias, out) in one launch; see fp8_gemm_rowscaled.
+  gelu_from: per problem the first output column that passes through tanh-GELU in the epilogue (None: none)."""
   if not 1 <= len(problems) <= 2:
     raise RuntimeError("fp8_gemm_rowscaled_grouped: one or two problems per launch")
   arr = (GemmProblem * len(problems))()
@@ -575,8 +582,13 @@ def fp8_gemm_rowscaled_grouped(problems):
     start = torch.cuda.Event(enable_timing=True)
     end = torch.cuda.Event(enable_timing=True)
     start.record()
-  st = lib().cdb_fp8_gemm_rowscaled_grouped(ctypes.cast(arr, c_void_p), len(problems),
-                                            _ptr(gemm_status_word(out0.device)), _stream(out0))
+  if gelu_from is not None and any(g is not None for g in gelu_from):
+    cols = (c_int64 * len(problems))(*[-1 if g is None else int(g) for g in gelu_from])
+    st = lib().cdb_fp8_gemm_rowscaled_grouped_act(ctypes.cast(arr, c_void_p), len(problems), ctypes.cast(cols, c_void_p),
+                                                  _ptr(gemm_status_word(out0.device)), _stream(out0))
+  else:
+    st = lib().cdb_fp8_gemm_rowscaled_grouped(ctypes.cast(arr, c_void_p), len(problems),
+                                              _ptr(gemm_status_word(out0.device)), _stream(out0))
   if timer is not None:
     end.record()
     timer.append((start, end, flops))

@@ -229,10 +229,17 @@ __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.a
 // A tile width that is not a multiple of 64 leaves a last block of 16, 32 or 48 columns: a 64-column TMA
 // store would spill into the neighbouring tile's columns, so that block goes out as 16-byte global stores
 // straight from the registers.
+// tanh-GELU of an output pair that has already been rounded to bf16, rounded to bf16 again: what an eager
+// `gelu(linear(x))` computes, and bit for bit what the GELU variant of the quantization kernel computes when it
+// reads the linear's output back.
+__device__ __forceinline__ uint32_t gelu_bf16x2(uint32_t w) {
+  return pack_bf16x2(gelu_tanh(__uint_as_float(w << 16)), gelu_tanh(__uint_as_float(w & 0xffff0000u)));
+}
 __device__ __forceinline__ void epilogue_rows(const CUtensorMap* map_out, __nv_bfloat16* out, int64_t ld_out,
                                               uint8_t* staging, uint32_t taddr, float rs,
                                               const float* s_colscale, const __nv_bfloat16* s_bias, int row0,
-                                              int n0, int M, int N, int bn, int lane, uint32_t& blocks_done) {
+                                              int n0, int M, int N, int bn, int act_col, int lane,
+                                              uint32_t& blocks_done) {
   if (row0 >= M) return;  // the whole 32-row slice is padding
 #pragma unroll 1
   for (int cblk = 0; cblk < bn; cblk += OUT_BOX_COLS) {
@@ -258,6 +265,7 @@ __device__ __forceinline__ void epilogue_rows(const CUtensorMap* map_out, __nv_b
               const float v0 = __uint_as_float(acc[h][g * 8 + 2 * j]) * rs * s_colscale[c] + b.x;
               const float v1 = __uint_as_float(acc[h][g * 8 + 2 * j + 1]) * rs * s_colscale[c + 1] + b.y;
               w[j] = pack_bf16x2(v0, v1);
+              if (n0 + cb >= act_col) w[j] = gelu_bf16x2(w[j]);
             }
             *reinterpret_cast<uint4*>(out + (int64_t)row * ld_out + n0 + cb) = make_uint4(w[0], w[1], w[2], w[3]);
           }
@@ -283,6 +291,10 @@ __device__ __forceinline__ void epilogue_rows(const CUtensorMap* map_out, __nv_b
           const float v0 = __uint_as_float(acc[h][g * 8 + 2 * j]) * rs * s_colscale[c] + b.x;
           const float v1 = __uint_as_float(acc[h][g * 8 + 2 * j + 1]) * rs * s_colscale[c + 1] + b.y;
           w[j] = pack_bf16x2(v0, v1);
+        }
+        if (n0 + cb >= act_col) {  // warp-uniform: act_col is a multiple of 8
+#pragma unroll
+          for (int j = 0; j < 4; ++j) w[j] = gelu_bf16x2(w[j]);
         }
         const int chunk = (h * 4 + g) ^ (lane & 7);
         *reinterpret_cast<uint4*>(rowp + chunk * 16) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -313,6 +325,7 @@ struct GemmProblem {
   int M, N, K;
   int m_tiles, n_tiles, k_blocks, group_m;
   int tile_begin;  // index of this problem's first tile in the launch's tile sequence
+  int act_col;     // output columns >= act_col pass through tanh-GELU in the epilogue (INT32_MAX: none)
   // Tile width in columns: a multiple of 16 up to BN, chosen on the host so that the tile count fills whole
   // waves of SMs (single-CTA kernel; the CTA-pair kernel always uses BN).  `idesc` is the instruction
   // descriptor for that width.
@@ -515,7 +528,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       const float rs = row < M ? __ldg(sa + row) : 0.f;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
       epilogue_rows(&pr->map_out, pr->out, pr->ld_out, s_staging + quarter * 2 * OUT_BLOCK_BYTES, taddr, rs,
-                    s_colscale, s_bias, m0 + quarter * 32, n0, M, N, bn, lane, blocks_done);
+                    s_colscale, s_bias, m0 + quarter * 32, n0, M, N, bn, pr->act_col, lane, blocks_done);
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&gb->acc_empty[buf]);
@@ -788,7 +801,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
       const float rs = row < M ? __ldg(sa + row) : 0.f;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
       epilogue_rows(&pr->map_out, pr->out, pr->ld_out, s_staging + quarter * 2 * OUT_BLOCK_BYTES, taddr, rs,
-                    s_colscale, s_bias, m0 + quarter * 32, n0, M, N, BN, lane, blocks_done);
+                    s_colscale, s_bias, m0 + quarter * 32, n0, M, N, BN, pr->act_col, lane, blocks_done);
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&gb->acc_empty[buf]), 0));
@@ -1118,19 +1131,35 @@ static int launch_few_rows(const cdb_gemm_problem_abi& g, int sms, cudaStream_t 
   return CDB_OK;
 }
 
-// Up to two products in one launch of the tile kernels; the one with more rows goes first.
-extern "C" int cdb_fp8_gemm_rowscaled_grouped(const void* problems_v, int count, int32_t* status_word, void* stream) {
+// Up to two products in one launch of the tile kernels; the one with more rows goes first.  `gelu_from_col`
+// (may be null) gives, per problem, the first output column that passes through tanh-GELU in the epilogue.
+extern "C" int cdb_fp8_gemm_rowscaled_grouped_act(const void* problems_v, int count, const int64_t* gelu_from_col,
+                                                  int32_t* status_word, void* stream) {
   const cdb_gemm_problem_abi* in = static_cast<const cdb_gemm_problem_abi*>(problems_v);
   if (!in || count < 1 || count > MAX_PROBLEMS) return CDB_ERR_BAD_ARGUMENT;
   cdb_gemm_problem_abi g[MAX_PROBLEMS];
+  int act[MAX_PROBLEMS];
   int n = 0;
+  bool any_act = false;
   for (int i = 0; i < count; ++i) {
     const int rc = check_problem(in[i]);
     if (rc != CDB_OK) return rc;
-    if (in[i].M > 0) g[n++] = in[i];
+    int a = INT32_MAX;
+    if (gelu_from_col != nullptr && gelu_from_col[i] >= 0 && gelu_from_col[i] < in[i].N) {
+      if (gelu_from_col[i] % 8 != 0) return CDB_ERR_UNSUPPORTED;  // the epilogue decides per 16-byte chunk
+      a = (int)gelu_from_col[i];
+    }
+    if (in[i].M > 0) {
+      any_act = any_act || a != INT32_MAX;
+      act[n] = a;
+      g[n++] = in[i];
+    }
   }
   if (n == 0) return CDB_OK;
-  if (n == 2 && g[1].M > g[0].M) std::swap(g[0], g[1]);
+  if (n == 2 && g[1].M > g[0].M) {
+    std::swap(g[0], g[1]);
+    std::swap(act[0], act[1]);
+  }
   // The opt-in to more than 48 KB of dynamic shared memory is a per-device function attribute.
   static PerDevice attr_state;
   const cudaError_t attr_err = (cudaError_t)attr_state.get([]() -> int64_t {
@@ -1145,7 +1174,8 @@ extern "C" int cdb_fp8_gemm_rowscaled_grouped(const void* problems_v, int count,
   CDB_CUDA_CHECK(attr_err);
   const int sms = sm_count();
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (n == 1 && mode == 0 && g[0].M <= GEMV_MAX_M && g[0].M * g[0].K * 2 <= 48 * 1024) return launch_few_rows(g[0], sms, st);
+  if (n == 1 && mode == 0 && !any_act && g[0].M <= GEMV_MAX_M && g[0].M * g[0].K * 2 <= 48 * 1024)
+    return launch_few_rows(g[0], sms, st);
   // CTA pairs for tall problems; below 4096 rows (rank shards of a context-parallel run: 2304, 1152, 576 rows)
   // whichever kernel the wave-count model expects to finish first
   double single_cost = 0.0;
@@ -1182,6 +1212,7 @@ extern "C" int cdb_fp8_gemm_rowscaled_grouped(const void* problems_v, int count,
     o.k_blocks = (int)((g[i].K + BK - 1) / BK);
     o.group_m = tile_group_rows(o.m_tiles);
     o.tile_begin = (int)tiles;
+    o.act_col = act[i];
     tiles += (int64_t)o.m_tiles * o.n_tiles;
   }
   if (tiles > INT32_MAX) return CDB_ERR_TOO_LARGE;
@@ -1199,10 +1230,14 @@ extern "C" int cdb_fp8_gemm_rowscaled_grouped(const void* problems_v, int count,
   return CDB_OK;
 }
 
+extern "C" int cdb_fp8_gemm_rowscaled_grouped(const void* problems_v, int count, int32_t* status_word, void* stream) {
+  return cdb_fp8_gemm_rowscaled_grouped_act(problems_v, count, nullptr, status_word, stream);
+}
+
 extern "C" int cdb_fp8_gemm_rowscaled(const void* a_q, const float* a_scale, const void* w_q,
                                       const float* w_scale, const void* bias, void* out, int64_t M,
                                       int64_t N, int64_t K, int64_t ld_out, int32_t* status_word,
                                       void* stream) {
   const cdb_gemm_problem_abi g{a_q, a_scale, w_q, w_scale, bias, out, M, N, K, ld_out};
-  return cdb_fp8_gemm_rowscaled_grouped(&g, 1, status_word, stream);
+  return cdb_fp8_gemm_rowscaled_grouped_act(&g, 1, nullptr, status_word, stream);
 }

@@ -27,6 +27,7 @@ struct QuantFuse {
   const __nv_bfloat16* tail;
   int64_t ld_tail;
   int head_packs;
+  int tail_plain;  // CDB_PRE_CONCAT_GELU only: the tail already is activated (the product that wrote it did it)
   // Second tensor quantized by the same launch (x2 != nullptr): rows [rows1, rows) of the launch are its
   // rows 0..; it has its own modulation vectors and outputs.  Used for the image and the text stream of a
   // double-stream block, whose text part alone would be a launch of a few microseconds.
@@ -39,19 +40,6 @@ struct QuantFuse {
   float* scale_out2;
 };
 
-// tanh-GELU as x * sigmoid(2u), u = sqrt(2/pi) (x + 0.044715 x^3) = x / (1 + 2^(c x (1 + 0.044715 x^2))),
-// c = -2 sqrt(2/pi) log2(e): three multiply-adds, one ex2 and one fast division instead of the
-// ~25-instruction tanhf (the special-function unit is what bounds this kernel).  The ~1e-6 relative
-// error disappears in the rounding of the result to bf16 except for a handful of values per million
-// that sit on a rounding boundary.
-__device__ __forceinline__ float gelu_tanh(float x) {
-  constexpr float c = -2.0f * 0.7978845608028654f * 1.4426950408889634f;
-  const float p = fmaf(x * x, c * 0.044715f, c);
-  float e;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * p));
-  return __fdividef(x, 1.0f + e);
-}
-
 // bf16x2 word <-> two floats (bf16 -> fp32 is a 16-bit shift: no conversion instruction)
 __device__ __forceinline__ float lo_f(uint32_t u) { return __uint_as_float(u << 16); }
 __device__ __forceinline__ float hi_f(uint32_t u) { return __uint_as_float(u & 0xffff0000u); }
@@ -61,6 +49,17 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 }
 __device__ __forceinline__ __nv_bfloat162 as_bf2(uint32_t u) { return *reinterpret_cast<__nv_bfloat162*>(&u); }
 __device__ __forceinline__ uint32_t as_u32(__nv_bfloat162 v) { return *reinterpret_cast<uint32_t*>(&v); }
+
+// Four floats -> four e4m3 codes (round to nearest even, saturating) in one word, a in the lowest byte: two
+// conversion instructions and one register pairing.
+__device__ __forceinline__ uint32_t e4m3x4(float a, float b, float c, float d) {
+  uint16_t lo, hi;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;" : "=h"(lo) : "f"(a), "f"(b));
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;" : "=h"(hi) : "f"(c), "f"(d));
+  uint32_t r;
+  asm("mov.b32 %0, {%1, %2};" : "=r"(r) : "h"(lo), "h"(hi));
+  return r;
+}
 
 constexpr int Q_CTA = 256;  // threads per CTA; a CTA works on Q_CTA / TPR rows at once
 
@@ -235,7 +234,7 @@ __global__ void __launch_bounds__(Q_CTA)
     } else if constexpr (PREOP == CDB_PRE_CONCAT_GELU) {
 #pragma unroll
       for (int k = 0; k < VPT; ++k) {
-        if (tig + k * TPR >= f.head_packs) {
+        if (tig + k * TPR >= f.head_packs && !f.tail_plain) {
           uint32_t w[4] = {pk[k].x, pk[k].y, pk[k].z, pk[k].w};
 #pragma unroll
           for (int j = 0; j < 4; ++j) w[j] = pack2(gelu_tanh(lo_f(w[j])), gelu_tanh(hi_f(w[j])));
@@ -271,31 +270,42 @@ __global__ void __launch_bounds__(Q_CTA)
     // x * (1/sc) can change an e4m3 code only when the quotient is within two fp32 ulps of a rounding
     // midpoint (about 2^-19 of the elements), so the correction is dropped.  Rows whose scale is so
     // small that 1/sc would overflow take the plain division.
-    const bool tiny = sc < 1e-30f;
-    const float inv = tiny ? 0.f : __frcp_rn(sc);
-    auto quot = [&](float v) -> float {
-      if (tiny) return __fdiv_rn(v, sc);
-      float t = v * inv;
-      if constexpr (PREOP != CDB_PRE_NONE) return t;
-      float r = fmaf(-t, sc, v);
-      return fmaf(r, inv, t);
-    };
     uint8_t* qr = out2 ? f.q2 + (row - f.rows1) * (int64_t)cols : q + (valid ? row : 0) * (int64_t)cols;
+    if (sc >= 1e-30f) {  // same for every thread of the row, so the branch is uniform per warp
+      const float inv = __frcp_rn(sc);
 #pragma unroll
-    for (int k = 0; k < VPT; ++k) {
-      const int p = tig + k * TPR;
-      if (valid && p < npack) {
-        const uint32_t w[4] = {pk[k].x, pk[k].y, pk[k].z, pk[k].w};
-        uint32_t o[2];
+      for (int k = 0; k < VPT; ++k) {
+        const int p = tig + k * TPR;
+        if (valid && p < npack) {
+          const uint32_t w[4] = {pk[k].x, pk[k].y, pk[k].z, pk[k].w};
+          float t[8];
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const uint32_t a = __nv_cvt_float2_to_fp8x2(make_float2(quot(lo_f(w[2 * h])), quot(hi_f(w[2 * h]))),
-                                                      __NV_SATFINITE, __NV_E4M3);
-          const uint32_t b = __nv_cvt_float2_to_fp8x2(
-              make_float2(quot(lo_f(w[2 * h + 1])), quot(hi_f(w[2 * h + 1]))), __NV_SATFINITE, __NV_E4M3);
-          o[h] = a | (b << 16);
+          for (int j = 0; j < 4; ++j) {
+            const float v0 = lo_f(w[j]), v1 = hi_f(w[j]);
+            t[2 * j] = v0 * inv;
+            t[2 * j + 1] = v1 * inv;
+            if constexpr (PREOP == CDB_PRE_NONE) {
+              // copysign: the correction of a zero quotient is +0, which would turn -0 into +0
+              t[2 * j] = copysignf(fmaf(fmaf(-t[2 * j], sc, v0), inv, t[2 * j]), v0);
+              t[2 * j + 1] = copysignf(fmaf(fmaf(-t[2 * j + 1], sc, v1), inv, t[2 * j + 1]), v1);
+            }
+          }
+          __stcs(reinterpret_cast<uint2*>(qr + (int64_t)p * 8),
+                 make_uint2(e4m3x4(t[0], t[1], t[2], t[3]), e4m3x4(t[4], t[5], t[6], t[7])));
         }
-        __stcs(reinterpret_cast<uint2*>(qr + (int64_t)p * 8), make_uint2(o[0], o[1]));
+      }
+    } else {  // a scale so small that its reciprocal would overflow: plain division
+#pragma unroll
+      for (int k = 0; k < VPT; ++k) {
+        const int p = tig + k * TPR;
+        if (valid && p < npack) {
+          const uint32_t w[4] = {pk[k].x, pk[k].y, pk[k].z, pk[k].w};
+          __stcs(reinterpret_cast<uint2*>(qr + (int64_t)p * 8),
+                 make_uint2(e4m3x4(__fdiv_rn(lo_f(w[0]), sc), __fdiv_rn(hi_f(w[0]), sc), __fdiv_rn(lo_f(w[1]), sc),
+                                   __fdiv_rn(hi_f(w[1]), sc)),
+                            e4m3x4(__fdiv_rn(lo_f(w[2]), sc), __fdiv_rn(hi_f(w[2]), sc), __fdiv_rn(lo_f(w[3]), sc),
+                                   __fdiv_rn(hi_f(w[3]), sc))));
+        }
       }
     }
   }
@@ -434,9 +444,8 @@ extern "C" int cdb_fp8_quant_rows_fused_pair(const void* x, int64_t rows, int64_
   }
 }
 
-extern "C" int cdb_fp8_quant_rows_concat_gelu(const void* head, int64_t head_cols, int64_t ld_head,
-                                              const void* tail, int64_t tail_cols, int64_t ld_tail, int64_t rows,
-                                              void* q, float* scale, void* stream) {
+static int quant_rows_concat(const void* head, int64_t head_cols, int64_t ld_head, const void* tail, int64_t tail_cols,
+                             int64_t ld_tail, int64_t rows, bool tail_plain, void* q, float* scale, void* stream) {
   if (!head || !tail || !q || !scale || rows < 0 || head_cols <= 0 || tail_cols <= 0 || ld_head < head_cols ||
       ld_tail < tail_cols)
     return CDB_ERR_BAD_ARGUMENT;
@@ -448,8 +457,22 @@ extern "C" int cdb_fp8_quant_rows_concat_gelu(const void* head, int64_t head_col
   f.tail = static_cast<const __nv_bfloat16*>(tail);
   f.ld_tail = ld_tail;
   f.head_packs = (int)(head_cols / 8);
+  f.tail_plain = tail_plain ? 1 : 0;
   return launch_quant<CDB_PRE_CONCAT_GELU>(head, rows, head_cols + tail_cols, ld_head, f, q, scale,
                                            static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int cdb_fp8_quant_rows_concat_gelu(const void* head, int64_t head_cols, int64_t ld_head,
+                                              const void* tail, int64_t tail_cols, int64_t ld_tail, int64_t rows,
+                                              void* q, float* scale, void* stream) {
+  return quant_rows_concat(head, head_cols, ld_head, tail, tail_cols, ld_tail, rows, false, q, scale, stream);
+}
+
+// The same row [head | tail] without the activation: for a tail whose producer already applied it.
+extern "C" int cdb_fp8_quant_rows_concat(const void* head, int64_t head_cols, int64_t ld_head, const void* tail,
+                                         int64_t tail_cols, int64_t ld_tail, int64_t rows, void* q, float* scale,
+                                         void* stream) {
+  return quant_rows_concat(head, head_cols, ld_head, tail, tail_cols, ld_tail, rows, true, q, scale, stream);
 }
 
 extern "C" int cdb_fp8_quant_rows(const void* x, int64_t rows, int64_t cols, int64_t ld_x, void* q,

@@ -94,7 +94,7 @@ def _modulation(linear, temb, chunks):
 
 def flux_double_block_forward(self, hidden_states, encoder_hidden_states, temb, image_rotary_emb=None,
                               joint_attention_kwargs=None):
-  from ..synthetic.layers import (gated_add_pair, gelu_linear_pair, joint_attention, linear_pair,
+  from ..synthetic.layers import (gated_add_pair, gelu_in_product, gelu_linear_pair, joint_attention, linear_pair,
                                   norm_modulate_linears_pair, shared_input_linears)
   a = self.attn
   rope = _ROPE.get(image_rotary_emb, hidden_states.dtype)
@@ -109,25 +109,28 @@ def flux_double_block_forward(self, hidden_states, encoder_hidden_states, temb, 
   n_txt = encoder_hidden_states.shape[1]
   y, cy = linear_pair(o[:, n_txt:], a.to_out[0], o[:, :n_txt], a.to_add_out)
   hidden_states, encoder_hidden_states = gated_add_pair(hidden_states, gate, y, encoder_hidden_states, c_gate, cy)
+  act = gelu_in_product()
   (h, ), (c, ) = norm_modulate_linears_pair((hidden_states, shift_mlp, scale_mlp, (self.ff.net[0].proj, )),
-                                            (encoder_hidden_states, c_shift_mlp, c_scale_mlp, (self.ff_context.net[0].proj, )))
-  y, cy = gelu_linear_pair(h, self.ff.net[2], c, self.ff_context.net[2])
+                                            (encoder_hidden_states, c_shift_mlp, c_scale_mlp, (self.ff_context.net[0].proj, )),
+                                            gelu_last=act)
+  y, cy = gelu_linear_pair(h, self.ff.net[2], c, self.ff_context.net[2], activated=act)
   hidden_states, encoder_hidden_states = gated_add_pair(hidden_states, gate_mlp, y, encoder_hidden_states, c_gate_mlp, cy)
   return encoder_hidden_states, hidden_states
 
 
 def flux_single_block_forward(self, hidden_states, encoder_hidden_states, temb, image_rotary_emb=None,
                               joint_attention_kwargs=None):
-  from ..synthetic.layers import (concat_gelu_linear, gated_add, join_tokens, joint_attention, norm_modulate_linears,
+  from ..synthetic.layers import (concat_gelu_linear, gated_add, gelu_in_product, join_tokens, joint_attention, norm_modulate_linears,
                                   split_tokens)
   a = self.attn
   rope = _ROPE.get(image_rotary_emb, hidden_states.dtype)
   n_txt = encoder_hidden_states.shape[1]
   x = join_tokens(encoder_hidden_states, hidden_states)
   shift, scale, gate = _modulation(self.norm.linear, temb, 3)
-  q, k, v, mlp = norm_modulate_linears(x, shift, scale, (a.to_q, a.to_k, a.to_v, self.proj_mlp))
+  act = gelu_in_product()
+  q, k, v, mlp = norm_modulate_linears(x, shift, scale, (a.to_q, a.to_k, a.to_v, self.proj_mlp), gelu_last=act)
   o = joint_attention(((q, a.norm_q), ), ((k, a.norm_k), ), (v, ), rope, a.heads, getattr(self, "cp", None))
-  y = concat_gelu_linear(o, mlp, self.proj_out)
+  y = concat_gelu_linear(o, mlp, self.proj_out, tail_activated=act)
   return split_tokens(gated_add(x, gate, y), n_txt)
 
 

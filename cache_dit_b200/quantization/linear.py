@@ -56,10 +56,14 @@ class Float8RowwiseLinear(torch.nn.Module):
     _native.fp8_quant_rows(x2, a_q, a_scale)
     return a_q, a_scale
 
-  def forward_quantized(self, a_q: torch.Tensor, a_scale: torch.Tensor, lead_shape) -> torch.Tensor:
-    """Product for activations that a fused producer kernel already quantized."""
+  def forward_quantized(self, a_q: torch.Tensor, a_scale: torch.Tensor, lead_shape, gelu: bool = False) -> torch.Tensor:
+    """Product for activations that a fused producer kernel already quantized.  `gelu`: the output passes
+    through tanh-GELU in the product's epilogue (bf16(gelu(bf16(y))), what an eager gelu(linear(x)) gives)."""
     out = torch.empty((a_q.shape[0], self.out_features), dtype=torch.bfloat16, device=a_q.device)
-    _native.fp8_gemm_rowscaled(a_q, a_scale, self.weight_q, self.weight_scale, self.bias, out)
+    if gelu:
+      _native.fp8_gemm_rowscaled_grouped([(a_q, a_scale, self.weight_q, self.weight_scale, self.bias, out)], [0])
+    else:
+      _native.fp8_gemm_rowscaled(a_q, a_scale, self.weight_q, self.weight_scale, self.bias, out)
     return out.view(*lead_shape, self.out_features)
 
   def forward(self, x: torch.Tensor) -> torch.Tensor:
@@ -142,9 +146,19 @@ class FusedFloat8Linears(torch.nn.Module):
         l.bias = b[start:start + n]
       start += n
 
-  def forward_quantized(self, a_q: torch.Tensor, a_scale: torch.Tensor, lead_shape):
+  def gelu_column(self, gelu_last: bool):
+    """First output column of the last member (whose output is to be activated), or None."""
+    return self.out_features - self.splits[-1] if gelu_last else None
+
+  def forward_quantized(self, a_q: torch.Tensor, a_scale: torch.Tensor, lead_shape, gelu_last: bool = False):
+    """`gelu_last`: the last member's output passes through tanh-GELU in the epilogue (the MLP-in projection
+    behind q/k/v)."""
     out = torch.empty((a_q.shape[0], self.out_features), dtype=torch.bfloat16, device=a_q.device)
-    _native.fp8_gemm_rowscaled(a_q, a_scale, self.weight_q, self.weight_scale, self.bias, out)
+    if gelu_last:
+      _native.fp8_gemm_rowscaled_grouped([(a_q, a_scale, self.weight_q, self.weight_scale, self.bias, out)],
+                                         [self.gelu_column(True)])
+    else:
+      _native.fp8_gemm_rowscaled(a_q, a_scale, self.weight_q, self.weight_scale, self.bias, out)
     out = out.view(*lead_shape, self.out_features)
     return out.split(self.splits, dim=-1)
 
@@ -179,15 +193,19 @@ def fused_group(linears) -> FusedFloat8Linears:
   return fused
 
 
-def grouped_forward_quantized(items):
+def grouped_forward_quantized(items, gelu_last: bool = False):
   """Products of up to two FP8 linears (or fused groups) with already quantized activations as ONE
   launch: items = [(module, a_q, a_scale, lead_shape), ...].  Returns each module's usual result (a
   tensor, or the tuple of splits of a fused group).  The second product is typically the small text
-  stream of a double-stream block, whose tiles fill the tail wave of the first."""
+  stream of a double-stream block, whose tiles fill the tail wave of the first.  `gelu_last`: every item's
+  output (its last member's, for a fused group) passes through tanh-GELU in the epilogue."""
   outs = [torch.empty((a_q.shape[0], m.out_features), dtype=torch.bfloat16, device=a_q.device) for m, a_q, _, _ in items]
   problems = [(a_q, a_scale, m.weight_q, m.weight_scale, m.bias, out) for (m, a_q, a_scale, _), out in zip(items, outs)]
+  act = None
+  if gelu_last:
+    act = [m.gelu_column(True) if isinstance(m, FusedFloat8Linears) else 0 for m, _, _, _ in items]
   for i in range(0, len(problems), 2):
-    _native.fp8_gemm_rowscaled_grouped(problems[i:i + 2])
+    _native.fp8_gemm_rowscaled_grouped(problems[i:i + 2], None if act is None else act[i:i + 2])
   results = []
   for (m, _, _, lead), out in zip(items, outs):
     out = out.view(*lead, m.out_features)

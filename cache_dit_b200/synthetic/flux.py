@@ -21,7 +21,7 @@ from torch import nn
 from ..caching.block_adapters import BlockAdapter, BlockAdapterRegister
 from ..caching.forward_pattern import ForwardPattern
 from .layers import (ModulationBank, RMSNorm, RopeCache, TimestepMLP, UlyssesGroup, concat_gelu_linear, gated_add, gated_add_pair,
-                     gelu_linear_pair,
+                     gelu_in_product, gelu_linear_pair,
                      joint_attention, join_tokens, linear_pair, norm_modulate, norm_modulate_linears,
                      norm_modulate_linears_pair, shared_input_linears, split_tokens, timestep_embedding)
 
@@ -100,9 +100,11 @@ class FluxTransformerBlock(nn.Module):
     n_txt = encoder_hidden_states.shape[1]
     y, cy = linear_pair(o[:, n_txt:], a.to_out, o[:, :n_txt], a.to_add_out)
     hidden_states, encoder_hidden_states = gated_add_pair(hidden_states, gate, y, encoder_hidden_states, c_gate, cy)
+    act = gelu_in_product()
     (h, ), (c, ) = norm_modulate_linears_pair((hidden_states, shift_mlp, scale_mlp, (self.ff.proj_in, )),
-                                              (encoder_hidden_states, c_shift_mlp, c_scale_mlp, (self.ff_context.proj_in, )))
-    y, cy = gelu_linear_pair(h, self.ff.proj_out, c, self.ff_context.proj_out)
+                                              (encoder_hidden_states, c_shift_mlp, c_scale_mlp, (self.ff_context.proj_in, )),
+                                              gelu_last=act)
+    y, cy = gelu_linear_pair(h, self.ff.proj_out, c, self.ff_context.proj_out, activated=act)
     hidden_states, encoder_hidden_states = gated_add_pair(hidden_states, gate_mlp, y, encoder_hidden_states, c_gate_mlp, cy)
     return encoder_hidden_states, hidden_states
 
@@ -124,9 +126,10 @@ class FluxSingleTransformerBlock(nn.Module):
     x = join_tokens(encoder_hidden_states, hidden_states)
     bank = getattr(self, "mod_bank", None)
     shift, scale, gate = bank.outputs((self.norm.linear, ))[0].chunk(3, dim=-1) if bank is not None else self.norm(temb)
-    q, k, v, mlp = norm_modulate_linears(x, shift, scale, (a.to_q, a.to_k, a.to_v, self.proj_mlp))
+    act = gelu_in_product()
+    q, k, v, mlp = norm_modulate_linears(x, shift, scale, (a.to_q, a.to_k, a.to_v, self.proj_mlp), gelu_last=act)
     o = joint_attention(((q, a.norm_q), ), ((k, a.norm_k), ), (v, ), image_rotary_emb, a.heads, self.cp)
-    y = concat_gelu_linear(o, mlp, self.proj_out)
+    y = concat_gelu_linear(o, mlp, self.proj_out, tail_activated=act)
     return split_tokens(gated_add(x, gate, y), n_txt)
 
 

@@ -9,6 +9,7 @@ them (q/k/v), so the bf16 intermediate is never written.
 from __future__ import annotations
 
 import math
+import os
 from typing import List, Optional, Sequence, Tuple
 
 import torch
@@ -24,17 +25,28 @@ def _all_fp8(linears: Sequence[nn.Module]) -> bool:
   return all(isinstance(l, Float8RowwiseLinear) for l in linears)
 
 
+def gelu_in_product() -> bool:
+  """Whether an MLP-in projection applies the MLP's tanh-GELU in its own epilogue (default), so that the
+  quantization in front of the MLP-out projection only concatenates / quantizes.
+  CACHE_DIT_B200_GELU_IN_PRODUCT=0 keeps the activation in that quantization kernel."""
+  return os.environ.get("CACHE_DIT_B200_GELU_IN_PRODUCT", "1") != "0"
+
+
 def norm_modulate_linears(x: torch.Tensor, shift: torch.Tensor, scale: torch.Tensor,
-                          linears: Sequence[nn.Module], eps: float = 1e-6) -> List[torch.Tensor]:
-  """[lin(LayerNorm(x) * (1 + scale) + shift) for lin in linears]; shift / scale are [B, C]."""
+                          linears: Sequence[nn.Module], eps: float = 1e-6, gelu_last: bool = False) -> List[torch.Tensor]:
+  """[lin(LayerNorm(x) * (1 + scale) + shift) for lin in linears]; shift / scale are [B, C].
+  `gelu_last`: the last output is returned as gelu_tanh(lin(...)) (an MLP-in projection)."""
   if _all_fp8(linears) and x.is_cuda:
     # shift / scale are column slices of one modulation matrix: passed as strided views
     a_q, a_scale, lead = quantize_rows_fused(x, _native.PRE_LAYERNORM_MOD, shift, scale, eps)
     if len(linears) > 1:  # one GEMM over the concatenated output rows
-      return list(fused_group(linears).forward_quantized(a_q, a_scale, lead))
-    return [linears[0].forward_quantized(a_q, a_scale, lead)]
+      return list(fused_group(linears).forward_quantized(a_q, a_scale, lead, gelu_last))
+    return [linears[0].forward_quantized(a_q, a_scale, lead, gelu_last)]
   y = F.layer_norm(x, (x.shape[-1], ), eps=eps) * (1 + scale[:, None]) + shift[:, None]
-  return [l(y) for l in linears]
+  outs = [l(y) for l in linears]
+  if gelu_last:
+    outs[-1] = F.gelu(outs[-1], approximate="tanh")
+  return outs
 
 
 # ---- two streams at once -----------------------------------------------------------------------------
@@ -45,14 +57,16 @@ def _pair_ready(xa, xb, linears) -> bool:
   return xa.is_cuda and xb.is_cuda and _all_fp8(linears)
 
 
-def norm_modulate_linears_pair(a, b, eps: float = 1e-6):
-  """(x, shift, scale, linears) for each stream -> (outputs of stream a, outputs of stream b)."""
+def norm_modulate_linears_pair(a, b, eps: float = 1e-6, gelu_last: bool = False):
+  """(x, shift, scale, linears) for each stream -> (outputs of stream a, outputs of stream b); `gelu_last` as in
+  `norm_modulate_linears`, for both streams."""
   (xa, sha, sca, la), (xb, shb, scb, lb) = a, b
   if not _pair_ready(xa, xb, tuple(la) + tuple(lb)):
-    return norm_modulate_linears(xa, sha, sca, la, eps), norm_modulate_linears(xb, shb, scb, lb, eps)
+    return (norm_modulate_linears(xa, sha, sca, la, eps, gelu_last),
+            norm_modulate_linears(xb, shb, scb, lb, eps, gelu_last))
   qa, qb = quantize_rows_fused_pair(xa, xb, _native.PRE_LAYERNORM_MOD, (sha, sca), (shb, scb), eps)
   items = [(fused_group(lin) if len(lin) > 1 else lin[0], *triple) for lin, triple in ((la, qa), (lb, qb))]
-  ra, rb = grouped_forward_quantized(items)
+  ra, rb = grouped_forward_quantized(items, gelu_last)
   as_list = lambda r: list(r) if isinstance(r, (tuple, list)) else [r]
   return as_list(ra), as_list(rb)
 
@@ -66,11 +80,12 @@ def linear_pair(xa, lina, xb, linb):
   return ra, rb
 
 
-def gelu_linear_pair(xa, lina, xb, linb):
-  """(lina(gelu_tanh(xa)), linb(gelu_tanh(xb))) with one GEMM launch."""
+def gelu_linear_pair(xa, lina, xb, linb, activated: bool = False):
+  """(lina(gelu_tanh(xa)), linb(gelu_tanh(xb))) with one GEMM launch.  `activated`: xa and xb already hold the
+  activated values (their producer applied the GELU)."""
   if not _pair_ready(xa, xb, (lina, linb)):
-    return gelu_linear(xa, lina), gelu_linear(xb, linb)
-  qa, qb = quantize_rows_fused_pair(xa, xb, _native.PRE_GELU_TANH)
+    return gelu_linear(xa, lina, activated), gelu_linear(xb, linb, activated)
+  qa, qb = quantize_rows_fused_pair(xa, xb, _native.PRE_NONE if activated else _native.PRE_GELU_TANH)
   ra, rb = grouped_forward_quantized([(lina, *qa), (linb, *qb)])
   return ra, rb
 
@@ -87,24 +102,26 @@ def norm_modulate(x: torch.Tensor, shift: torch.Tensor, scale: torch.Tensor, eps
   return F.layer_norm(x, (x.shape[-1], ), eps=eps) * (1 + scale[:, None]) + shift[:, None]
 
 
-def gelu_linear(x: torch.Tensor, linear: nn.Module) -> torch.Tensor:
-  """linear(gelu_tanh(x))."""
+def gelu_linear(x: torch.Tensor, linear: nn.Module, activated: bool = False) -> torch.Tensor:
+  """linear(gelu_tanh(x)); with `activated`, x already holds gelu_tanh(...)."""
   if isinstance(linear, Float8RowwiseLinear) and x.is_cuda:
-    a_q, a_scale, lead = quantize_rows_fused(x, _native.PRE_GELU_TANH)
+    a_q, a_scale, lead = quantize_rows_fused(x, _native.PRE_NONE if activated else _native.PRE_GELU_TANH)
     return linear.forward_quantized(a_q, a_scale, lead)
-  return linear(F.gelu(x, approximate="tanh"))
+  return linear(x if activated else F.gelu(x, approximate="tanh"))
 
 
-def concat_gelu_linear(head: torch.Tensor, tail: torch.Tensor, linear: nn.Module) -> torch.Tensor:
+def concat_gelu_linear(head: torch.Tensor, tail: torch.Tensor, linear: nn.Module,
+                       tail_activated: bool = False) -> torch.Tensor:
   """linear(cat([head, gelu_tanh(tail)], dim=-1)): the output projection of a parallel attention + MLP
-  block.  With an FP8 linear neither the activated MLP branch nor the concatenation is written."""
+  block.  With an FP8 linear neither the activated MLP branch nor the concatenation is written.
+  `tail_activated`: tail already holds gelu_tanh(...)."""
   if isinstance(linear, Float8RowwiseLinear) and head.is_cuda:
     h2, t2 = head.reshape(-1, head.shape[-1]), tail.reshape(-1, tail.shape[-1])
     a_q = torch.empty((h2.shape[0], h2.shape[1] + t2.shape[1]), dtype=torch.float8_e4m3fn, device=head.device)
     a_scale = torch.empty(h2.shape[0], dtype=torch.float32, device=head.device)
-    _native.fp8_quant_rows_concat_gelu(h2, t2, a_q, a_scale)
+    _native.fp8_quant_rows_concat_gelu(h2, t2, a_q, a_scale, tail_activated)
     return linear.forward_quantized(a_q, a_scale, head.shape[:-1])
-  return linear(torch.cat([head, F.gelu(tail, approximate="tanh")], dim=-1))
+  return linear(torch.cat([head, tail if tail_activated else F.gelu(tail, approximate="tanh")], dim=-1))
 
 
 def modulation_rows(temb: torch.Tensor, linear: nn.Module) -> torch.Tensor:

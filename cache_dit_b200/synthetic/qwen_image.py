@@ -21,7 +21,7 @@ from torch import nn
 from ..caching.block_adapters import BlockAdapter, BlockAdapterRegister
 from ..caching.forward_pattern import ForwardPattern
 from .context_parallel import ContextParallelMixin
-from .layers import (RMSNorm, RopeCache, TimestepMLP, UlyssesGroup, gated_add_pair, gelu_linear_pair, joint_attention,
+from .layers import (RMSNorm, RopeCache, TimestepMLP, UlyssesGroup, gated_add_pair, gelu_in_product, gelu_linear_pair, joint_attention,
                      linear_pair, modulation_rows, norm_modulate, norm_modulate_linears_pair, timestep_embedding)
 
 
@@ -82,9 +82,11 @@ class QwenImageTransformerBlock(nn.Module):
     n_txt = encoder_hidden_states.shape[1]
     y, cy = linear_pair(o[:, n_txt:], a.to_out[0], o[:, :n_txt], a.to_add_out)
     hidden_states, encoder_hidden_states = gated_add_pair(hidden_states, gate1, y, encoder_hidden_states, c_gate1, cy)
+    act = gelu_in_product()
     (h, ), (c, ) = norm_modulate_linears_pair((hidden_states, shift2, scale2, (self.img_mlp.net[0].proj, )),
-                                              (encoder_hidden_states, c_shift2, c_scale2, (self.txt_mlp.net[0].proj, )))
-    y, cy = gelu_linear_pair(h, self.img_mlp.net[2], c, self.txt_mlp.net[2])
+                                              (encoder_hidden_states, c_shift2, c_scale2, (self.txt_mlp.net[0].proj, )),
+                                              gelu_last=act)
+    y, cy = gelu_linear_pair(h, self.img_mlp.net[2], c, self.txt_mlp.net[2], activated=act)
     hidden_states, encoder_hidden_states = gated_add_pair(hidden_states, gate2, y, encoder_hidden_states, c_gate2, cy)
     return encoder_hidden_states, hidden_states
 

@@ -23,7 +23,7 @@ from torch import nn
 from ..caching.block_adapters import BlockAdapter, BlockAdapterRegister
 from ..caching.forward_pattern import ForwardPattern
 from .context_parallel import ContextParallelMixin
-from .layers import (RMSNorm, TimestepMLP, UlyssesGroup, gated_add, gelu_linear, joint_attention, norm_modulate,
+from .layers import (RMSNorm, TimestepMLP, UlyssesGroup, gated_add, gelu_in_product, gelu_linear, joint_attention, norm_modulate,
                      norm_modulate_linears, RopeCache, timestep_embedding)
 from .qwen_image import QwenFeedForward
 
@@ -66,8 +66,9 @@ class WanTransformerBlock(nn.Module):
     o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)).transpose(1, 2)
     hidden_states = hidden_states + a.to_out[0](o.flatten(2))
     # 3. feed-forward
-    (h, ) = norm_modulate_linears(hidden_states, c_shift, c_scale, (self.ffn.net[0].proj, ))
-    return gated_add(hidden_states, c_gate, gelu_linear(h, self.ffn.net[2]))
+    act = gelu_in_product()
+    (h, ) = norm_modulate_linears(hidden_states, c_shift, c_scale, (self.ffn.net[0].proj, ), gelu_last=act)
+    return gated_add(hidden_states, c_gate, gelu_linear(h, self.ffn.net[2], activated=act))
 
 
 class WanTransformer3DModel(ContextParallelMixin, nn.Module):

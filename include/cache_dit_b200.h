@@ -167,6 +167,15 @@ typedef struct cdb_gemm_problem {
 } cdb_gemm_problem;
 CDB_API int cdb_fp8_gemm_rowscaled_grouped(const void* problems /* cdb_gemm_problem[count] */, int count,
                                    int32_t* status_word, void* stream);
+/* The same launch with an activation in the epilogue (no counterpart in the reference, where the MLP's GELU is
+ * an eager op of the wrapped block): for problem i, output columns >= gelu_from_col[i] are written as
+ * bf16(gelu_tanh(bf16(product))), i.e. what `gelu(linear(x))` gives in bf16, so the tensor a following
+ * quantization reads needs no activation pass of its own.  gelu_from_col may be NULL; an entry that is negative
+ * or >= N means no activation for that problem; other entries must be multiples of 8.  0 activates the whole
+ * output (an MLP-in projection), the offset of a member activates one member of a concatenated product (the
+ * MLP-in columns behind q/k/v). */
+CDB_API int cdb_fp8_gemm_rowscaled_grouped_act(const void* problems /* cdb_gemm_problem[count] */, int count,
+                                       const int64_t* gelu_from_col, int32_t* status_word, void* stream);
 
 /* cdb_fp8_quant_rows_fused on two tensors of the same width in one launch (image and text stream of a
  * double-stream block): each has its own rows, row stride, modulation vectors (LayerNorm variant) and
@@ -186,6 +195,11 @@ CDB_API int cdb_fp8_quant_rows_fused_pair(const void* x, int64_t rows, int64_t l
 CDB_API int cdb_fp8_quant_rows_concat_gelu(const void* head, int64_t head_cols, int64_t ld_head,
                                    const void* tail, int64_t tail_cols, int64_t ld_tail,
                                    int64_t rows, void* q, float* scale, void* stream);
+/* The same for [head | tail] with a tail that already is activated (written by
+ * cdb_fp8_gemm_rowscaled_grouped_act): concatenation and quantization only. */
+CDB_API int cdb_fp8_quant_rows_concat(const void* head, int64_t head_cols, int64_t ld_head, const void* tail,
+                              int64_t tail_cols, int64_t ld_tail, int64_t rows, void* q, float* scale,
+                              void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * Row-scaled FP8 GEMM.  Replaces the torch._scaled_mm call at

@@ -320,6 +320,86 @@ def test_fp8_gemm_pair_kernel_gives_the_single_cta_kernels_bits(nat, shapes):
   assert nat.gemm_device_status(torch.device("cuda")) == 0
 
 
+@pytest.mark.parametrize("kind,cols", [(1, 0), (1, 80), (2, 0)])
+@pytest.mark.parametrize("shapes,gelu_from", [([(320, 1024, 256)], [0]), ([(576, 3072 + 1024, 512)], [3072]),
+                                              ([(520, 2048, 256), (72, 2048, 256)], [0, 0]),
+                                              ([(300, 1000, 256), (64, 512, 256)], [None, 256])])
+def test_fp8_gemm_epilogue_gelu(nat, kind, cols, shapes, gelu_from):
+  """An MLP-in product can apply the MLP's tanh-GELU in its epilogue: columns from `gelu_from` on are written as
+  bf16(gelu(bf16(y))).  Columns in front of it must keep the plain product's bits; the activated ones must be what
+  the GELU variant of the quantization kernel computes from the plain output (same device function, so the
+  quantized activations agree: equal scales, and codes that differ only where that variant's uncorrected division
+  lands on the other side of a rounding boundary), and within one bf16 step of torch's gelu where that is itself accurate.  Both tile kernels,
+  a ragged tile width, two products per launch."""
+  lib = nat.lib()
+  plain, acted, probs_plain, probs_act = [], [], [], []
+  for i, (M, N, K) in enumerate(shapes):
+    x_d, _ = activations(M, K, 40 + i)
+    w_d, _ = activations(N, K, 50 + i)
+    g = torch.Generator().manual_seed(60 + i)
+    b = torch.randn(N, generator=g).to(torch.bfloat16).cuda()
+    aq = torch.empty(M, K, dtype=torch.float8_e4m3fn, device="cuda")
+    sa = torch.empty(M, dtype=torch.float32, device="cuda")
+    wq = torch.empty(N, K, dtype=torch.float8_e4m3fn, device="cuda")
+    sw = torch.empty(N, dtype=torch.float32, device="cuda")
+    nat.fp8_quant_rows(x_d, aq, sa)
+    nat.fp8_quant_rows(w_d, wq, sw)
+    plain.append(torch.empty(M, N, dtype=torch.bfloat16, device="cuda"))
+    acted.append(torch.empty(M, N, dtype=torch.bfloat16, device="cuda"))
+    probs_plain.append((aq, sa, wq, sw, b, plain[-1]))
+    probs_act.append((aq, sa, wq, sw, b, acted[-1]))
+  try:
+    assert lib.cdb_tuning_set_gemm_kernel(kind) == 0 and lib.cdb_tuning_set_gemm_tile_cols(cols) == 0
+    nat.fp8_gemm_rowscaled_grouped(probs_plain)
+    nat.fp8_gemm_rowscaled_grouped(probs_act, gelu_from)
+    torch.cuda.synchronize()
+  finally:
+    lib.cdb_tuning_set_gemm_kernel(0)
+    lib.cdb_tuning_set_gemm_tile_cols(0)
+  for (M, N, K), c0, y, z in zip(shapes, gelu_from, plain, acted):
+    if c0 is None:
+      assert torch.equal(y, z)
+      continue
+    assert torch.equal(y[:, :c0], z[:, :c0])
+    want = torch.nn.functional.gelu(y[:, c0:].float(), approximate="tanh").to(torch.bfloat16)
+    got = z[:, c0:]
+    # one bf16 step, plus the absolute error of torch's own 0.5 x (1 + tanh u) where 1 + tanh u cancels (x < -4)
+    err = (got.float() - want.float()).abs()
+    assert bool((err <= 2.0 ** -7 * want.float().abs() + 1e-6).all())
+    assert float(((got != want) & (want.float().abs() > 1e-3)).float().mean()) < 2e-3  # away from that tail: rare last-bit ties
+    n = N - c0
+    qa = torch.empty(M, n, dtype=torch.float8_e4m3fn, device="cuda")
+    sa_ = torch.empty(M, dtype=torch.float32, device="cuda")
+    qb = torch.empty(M, n, dtype=torch.float8_e4m3fn, device="cuda")
+    sb_ = torch.empty(M, dtype=torch.float32, device="cuda")
+    nat.fp8_quant_rows(y[:, c0:], qa, sa_, nat.PRE_GELU_TANH)
+    nat.fp8_quant_rows(got, qb, sb_)
+    assert torch.equal(sa_, sb_)
+    assert float((qa.view(torch.uint8) != qb.view(torch.uint8)).float().mean()) < 1e-4
+  assert nat.gemm_device_status(torch.device("cuda")) == 0
+  assert lib.cdb_fp8_gemm_rowscaled_grouped_act(None, 1, None, None, None) != 0
+
+
+def test_fp8_quant_concat_with_activated_tail(nat):
+  """[head | tail] with a tail that already is activated = the concat + GELU kernel on the plain tail."""
+  rows, c1, c2 = 200, 3072, 4096
+  head, _ = activations(rows, c1, 71)
+  tail, _ = activations(rows, c2, 72)
+  want_q = torch.empty(rows, c1 + c2, dtype=torch.float8_e4m3fn, device="cuda")
+  want_s = torch.empty(rows, dtype=torch.float32, device="cuda")
+  nat.fp8_quant_rows_concat_gelu(head, tail, want_q, want_s)
+  # torch's gelu stands in for the product epilogue here; it differs from the device function in the last bf16
+  # bit of a few values, hence the tolerances (the epilogue's own bits are held in test_fp8_gemm_epilogue_gelu)
+  act = torch.nn.functional.gelu(tail.float(), approximate="tanh").to(torch.bfloat16)
+  got_q = torch.empty_like(want_q)
+  got_s = torch.empty_like(want_s)
+  nat.fp8_quant_rows_concat_gelu(head, act, got_q, got_s, tail_activated=True)
+  torch.cuda.synchronize()
+  assert float((got_s != want_s).float().mean()) < 1e-2  # torch's gelu may differ from the device function in the last bf16 bit
+  close = (got_q.view(torch.uint8).int() - want_q.view(torch.uint8).int()).abs()
+  assert float((close != 0).float().mean()) < 2e-3 and int(close.max()) <= 1
+
+
 def test_fp8_gemm_strided_output_and_back_to_back(nat):
   M, N, K = 256, 512, 256
   x_d, _ = activations(M, K, 1)
@@ -427,6 +507,7 @@ def test_fp8_quant_matches_torch_cast_pipeline(nat, rows, cols):
   zero scale -> 1 at :43-71)."""
   x_d, _ = activations(rows, cols, 21)
   x_d[3].zero_()
+  x_d[min(5, rows - 1), :7] = -0.0  # a negative zero keeps its sign through the division (code 0x80)
   q = torch.empty(rows, cols, dtype=torch.float8_e4m3fn, device="cuda")
   s = torch.empty(rows, dtype=torch.float32, device="cuda")
   nat.fp8_quant_rows(x_d, q, s)

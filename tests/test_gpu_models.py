@@ -196,6 +196,33 @@ def test_final_latents_against_library_fp8_linears():
   assert np.isfinite(got).all() and 0.0 < rel < 2e-2, rel
 
 
+@pytest.mark.parametrize("build", [_qwen, _wan, "flux"], ids=["qwen_image", "wan", "flux"])
+def test_gelu_in_the_product_epilogue_equals_gelu_in_the_quantization_kernel(build, monkeypatch):
+  """By default an MLP-in projection applies the MLP's tanh-GELU in its own epilogue and the quantization in front
+  of the MLP-out projection only quantizes; CACHE_DIT_B200_GELU_IN_PRODUCT=0 keeps the activation in that
+  quantization kernel.  Same device function and rounding points: same cache decisions, and final latents that
+  differ only by the few FP8 codes the corrected division of the plain quantization kernel decides differently."""
+  if build == "flux":
+    def build():
+      from cache_dit_b200.synthetic import FluxDenoisePipeline, FluxTransformer2DModel
+      with torch.device("cuda"):
+        model = FluxTransformer2DModel(num_layers=3, num_single_layers=4, dim=256, heads=4, in_channels=16,
+                                       joint_attention_dim=64, pooled_projection_dim=32, axes_dims_rope=(8, 28, 28),
+                                       time_scale=1.0, modulation_init_std=0.02)
+      inputs = FluxTransformer2DModel.example_inputs(height=256, width=256, text_tokens=16, in_channels=16,
+                                                     joint_attention_dim=64, pooled_projection_dim=32)
+      return model, inputs, FluxDenoisePipeline
+  results = {}
+  for flag in ("1", "0"):
+    monkeypatch.setenv("CACHE_DIT_B200_GELU_IN_PRODUCT", flag)
+    results[flag] = _generate(build, None, steps=12)
+  (a, sa, _, fa), (b, sb, _, _) = results["1"], results["0"]
+  assert fa["quantized"] > 0
+  assert sa.cached_steps == sb.cached_steps and len(sa.cached_steps) >= 2
+  rel = np.linalg.norm(a - b) / np.linalg.norm(b)
+  assert np.isfinite(a).all() and rel < 2e-3, rel
+
+
 def test_fused_forwards_for_a_foreign_model_with_the_flux_attribute_layout(monkeypatch):
   """`quantize` gives blocks that merely LOOK like the public FLUX blocks (attribute names, calling convention of
   the reference's patched forward) the producer-fused forwards; the result must agree with the same FP8 model run
