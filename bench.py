@@ -1031,6 +1031,14 @@ def small_case():
   out1 = torch.empty(1, N, device=dev, dtype=bf)
   nat.fp8_quant_rows(x1, aq1, sa1)
   xg, yg = mk(1, M, K), mk(1, M, K)
+
+  def single_cta(launch):  # the rank-shard product on the single-CTA kernel, whatever the launch model would pick
+    nat.lib().cdb_tuning_set_gemm_kernel(1)
+    try:
+      launch()
+    finally:
+      nat.lib().cdb_tuning_set_gemm_kernel(0)
+
   launches = [
     lambda: nat.rel_l1(h, None, p, None, means),
     lambda: nat.rel_l1(h, h0, p, o, means),
@@ -1047,8 +1055,11 @@ def small_case():
            dst_ptrs=[joint_k.data_ptr()], dst_batch_stride=joint.stride(0), dst_row_offset=0, eps=1e-6)], H),
     lambda: nat.gated_residual(xg, mod[:, 2 * K:3 * K], yg),
     lambda: nat.fp8_gemm_rowscaled(aq, sa, wq, sw, None, out),
-    lambda: nat.fp8_gemm_rowscaled(aqs, sas, wq, sw, None, outs),
+    lambda: single_cta(lambda: nat.fp8_gemm_rowscaled(aqs, sas, wq, sw, None, outs)),
     lambda: nat.fp8_gemm_rowscaled(aq1, sa1, wq, sw, None, out1),
+    # the MLP-in product with the GELU in its epilogue, and the concatenating quantization that then follows
+    lambda: nat.fp8_gemm_rowscaled_grouped([(aq, sa, wq, sw, None, out)], [0]),
+    lambda: nat.fp8_quant_rows_concat_gelu(attn, wide[:, 9216:], aq2, sa, tail_activated=True),
   ]
   for _ in range(2):
     for launch in launches:

@@ -1096,7 +1096,9 @@ static int choose_tile_cols(const cdb_gemm_problem_abi* g, int n, int sms, doubl
 // about 875 clocks on the same shapes, against 1026 for a single-CTA tile of that width (a CTA of a pair takes in
 // only its half of the weight tile, and the smaller stage gives its ring 6 stages instead of 4).  A pair tile
 // is the cheaper one, and what decides is the wave count: 256-row tiles waste up to a tile of rows (576 rows =
-// 2.25 tiles) and there are half as many tile slots.
+// 2.25 tiles) and there are half as many tile slots.  The pair kernel also wins near-ties (within 8 %): where
+// one wave is not full, the narrow single-CTA tiles the model would pick gain nothing in practice (576 x 3072 x
+// 15360: 58.5 us at 112 columns as at 256, 50.8 us with pairs).
 static double pair_cost(const cdb_gemm_problem_abi* g, int n, int sms) {
   int64_t tiles = 0;
   double per_tile = 0.0;
@@ -1182,7 +1184,7 @@ extern "C" int cdb_fp8_gemm_rowscaled_grouped_act(const void* problems_v, int co
   const int single_bn = choose_tile_cols(g, n, sms, &single_cost);
   const bool width_forced = g_forced_tile_cols.load(std::memory_order_relaxed) != 0;  // a forced width means the single-CTA kernel
   const bool pair = mode == 2 || (mode == 0 && CDB_GEMM_DEFAULT_PAIR &&
-                                  (g[0].M >= 4096 || (!width_forced && pair_cost(g, n, sms) < single_cost)));
+                                  (g[0].M >= 4096 || (!width_forced && pair_cost(g, n, sms) < 1.08 * single_cost)));
   const int64_t tile_rows = pair ? P_BM : BM;
   const int bn = pair ? BN : single_bn;
   GemmProblems ps{};
