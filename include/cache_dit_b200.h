@@ -216,7 +216,7 @@ CDB_API int cdb_fp8_gemm_rowscaled(const void* a_q, const float* a_scale, const 
                            int64_t N, int64_t K, int64_t ld_out, int32_t* status_word,
                            void* stream);
 
-/* Tuning knob (no counterpart in the reference): the single-CTA tile kernel (M < 4096) picks its tile width,
+/* Tuning knob (no counterpart in the reference): the single-CTA tile kernel picks its tile width,
  * a multiple of 16 columns up to 256, from a cost model so that the tiles fill whole waves of SMs; a non-zero
  * `cols` fixes the width for every later launch of the process, 0 restores the model.  The environment variable
  * CDB_GEMM_BN sets the initial value.  Results do not depend on the width (bitwise). */
