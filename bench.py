@@ -690,8 +690,12 @@ def run_ours(args):
   records, nat.gemm_timer = nat.gemm_timer, None
   for r in runners:
     r.enabled = True
-  gemm_ms = sum(s.elapsed_time(e) for s, e, _ in records)
-  gemm_flops = sum(f for _, _, f in records)
+  gemm_ms = sum(s.elapsed_time(e) for s, e, _, _ in records)
+  gemm_flops = sum(f for _, _, f, _ in records)
+  # launches whose epilogue also applies the MLP's GELU (work the flop count does not see), and the rest
+  act_records = [r_ for r_ in records if r_[3]]
+  plain_ms = sum(s.elapsed_time(e) for s, e, _, a in records if not a)
+  plain_flops = sum(f for _, _, f, a in records if not a)
 
   # -------- optional: per-kernel time table of this rank (CUPTI activity records through torch.profiler; not ncu:
   # a profiler that serialises one rank's kernels would let the peers' bounded waits run out)
@@ -815,6 +819,8 @@ def run_ours(args):
     "library_fp8_burst": round(fp8_lib[0], 1) if fp8_lib else None,
     "frac_of_library_fp8_sustained": round(achieved / fp8_lib[1], 3) if fp8_lib else None,
     "launches": len(records), "avg_launch_us": round(1e3 * gemm_ms / max(len(records), 1), 2),
+    "launches_with_gelu_epilogue": len(act_records),
+    "achieved_by_launches_without_gelu_epilogue": round(plain_flops / (plain_ms * 1e-3) / 1e12, 1) if plain_ms > 0 else None,
     # time inside these launches per step / the timed region's time per step (compare with the kernel's share in
     # the committed launch list)
     "share_of_step": round((gemm_ms / max(instrumented_steps, 1)) / (ms / steps), 3),

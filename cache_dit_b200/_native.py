@@ -302,7 +302,7 @@ def fp8_gemm_rowscaled(a_q, a_scale, w_q, w_scale, bias, out):
                                     _ptr(gemm_status_word(out.device)), _stream(out))
   if timer is not None:
     end.record()
-    timer.append((start, end, 2.0 * M * N * K))
+    timer.append((start, end, 2.0 * M * N * K, False))
   check(st, "cdb_fp8_gemm_rowscaled")
 
 
@@ -591,7 +591,7 @@ def fp8_gemm_rowscaled_grouped(problems, gelu_from=None):
                                               _ptr(gemm_status_word(out0.device)), _stream(out0))
   if timer is not None:
     end.record()
-    timer.append((start, end, flops))
+    timer.append((start, end, flops, bool(gelu_from is not None and any(g is not None for g in gelu_from))))
   check(st, "cdb_fp8_gemm_rowscaled_grouped")
 
 
