@@ -52,7 +52,7 @@ def test_rel_l1_matches_oracle(nat, dtype, shape, fused_residual):
   # the storage dtype on each mean (usually they are identical)
   assert abs(got[0] - md) <= ULP[dtype] * abs(md), (got, md, mp)
   assert abs(got[1] - mp) <= ULP[dtype] * abs(mp), (got, md, mp)
-  diff = float(O.rnd(np.float32(got[0]) / np.float32(got[1]), dtype))
+  diff = float(np.asarray(O.rnd(np.float32(got[0]) / np.float32(got[1]), dtype)).reshape(-1)[0])
   assert abs(diff - O.rel_l1(prev, cur, dtype)) <= 1e-3 * diff + 2 * ULP[dtype] * diff
 
 
