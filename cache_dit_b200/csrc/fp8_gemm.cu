@@ -327,7 +327,7 @@ struct GemmProblem {
   int tile_begin;  // index of this problem's first tile in the launch's tile sequence
   int act_col;     // output columns >= act_col pass through tanh-GELU in the epilogue (INT32_MAX: none)
   // Tile width in columns: a multiple of 16 up to BN, chosen on the host so that the tile count fills whole
-  // waves of SMs (single-CTA kernel; the CTA-pair kernel always uses BN).  `idesc` is the instruction
+  // waves of SMs (the CTA-pair kernel: BN unless a multiple of 32 is forced).  `idesc` is the instruction
   // descriptor for that width.
   int bn;
   uint32_t idesc;
@@ -573,7 +573,6 @@ constexpr int P_SMEM_TILE_BYTES = P_STAGES * P_STAGE_BYTES;
 constexpr int P_SMEM_TOTAL_BYTES =
     1024 + P_SMEM_TILE_BYTES + OUT_STAGING_BYTES + BN * 4 + BN * 2 + (int)sizeof(PairBarriers);
 static_assert(P_SMEM_TOTAL_BYTES <= 232448, "exceeds the 227 KB of shared memory a CTA can opt in to");
-constexpr uint32_t IDESC_E4M3_F32_M256 = idesc_e4m3_f32(P_BM, BN);
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -694,7 +693,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
       int mi, ni;
       tile_coords(local, pr->m_tiles, pr->n_tiles, pr->group_m, mi, ni);
       const int m0 = mi * P_BM + half;
-      const int n0 = ni * BN + half;
+      const int n0 = ni * pr->bn + (int)rank * (pr->bn >> 1);  // this CTA's half of the weight tile
+      const uint32_t pair_tx = 2u * (uint32_t)(P_A_BYTES + (pr->bn >> 1) * BK);  // both CTAs' bytes of one stage
       for (int kb = 0; kb < k_blocks; ++kb, ++it) {
         if (lane == 0) {
           const int s = it % P_STAGES;
@@ -703,7 +703,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
           if (ok) {
             uint8_t* a_dst = smem + s * P_STAGE_BYTES;
             uint8_t* b_dst = a_dst + P_A_BYTES;
-            if (rank == 0) mbar_expect_tx(&gb->full[s], 2 * P_STAGE_BYTES);  // both CTAs' bytes
+            if (rank == 0) mbar_expect_tx(&gb->full[s], pair_tx);
             const uint32_t full_addr = map_to_cta(smem_u32(&gb->full[s]), 0);
             tma_load_2d_pair(&pr->map_a, full_addr, a_dst, kb * BK, m0);
             tma_load_2d_pair(&pr->map_w, full_addr, b_dst, kb * BK, n0);
@@ -740,7 +740,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
         tcgen05_fence_after();
         const uint32_t tmem_d = tmem_base + buf * BN;
         int local;
-        const int k_blocks = problem_of(ps, tile, local)->k_blocks;
+        const GemmProblem* pr = problem_of(ps, tile, local);
+        const int k_blocks = pr->k_blocks;
+        const uint32_t idesc = pr->idesc;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % P_STAGES;
           const uint32_t ph = (it / P_STAGES) & 1u;
@@ -753,7 +755,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             umma_f8_pair(tmem_d, adesc + (uint64_t)(k * (UMMA_K >> 4)), bdesc + (uint64_t)(k * (UMMA_K >> 4)),
-                         IDESC_E4M3_F32_M256, (kb | k) != 0 ? 1u : 0u);
+                         idesc, (kb | k) != 0 ? 1u : 0u);
           }
           const uint32_t e = smem_u32(&gb->empty[s]);
           tcgen05_commit_pair(map_to_cta(e, 0));  // frees the stage in this CTA ...
@@ -783,11 +785,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
       int mi, ni;
       tile_coords(local, pr->m_tiles, pr->n_tiles, pr->group_m, mi, ni);
       const int m0 = mi * P_BM + (int)rank * 128;
-      const int n0 = ni * BN;
+      const int bn = pr->bn;
+      const int n0 = ni * bn;
       const uint32_t buf = local_tile & 1u;
       const uint32_t use = local_tile >> 1;
       asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
-      for (int c = et; c < BN; c += EPI_THREADS) {
+      for (int c = et; c < bn; c += EPI_THREADS) {
         const int col = n0 + c;
         s_colscale[c] = col < N ? __ldg(sw + col) : 0.f;
         s_bias[c] = (bias != nullptr && col < N) ? bias[col] : __float2bfloat16(0.f);
@@ -801,7 +804,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
       const float rs = row < M ? __ldg(sa + row) : 0.f;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
       epilogue_rows(&pr->map_out, pr->out, pr->ld_out, s_staging + quarter * 2 * OUT_BLOCK_BYTES, taddr, rs,
-                    s_colscale, s_bias, m0 + quarter * 32, n0, M, N, BN, pr->act_col, lane, blocks_done);
+                    s_colscale, s_bias, m0 + quarter * 32, n0, M, N, bn, pr->act_col, lane, blocks_done);
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&gb->acc_empty[buf]), 0));
@@ -1099,6 +1102,11 @@ static int choose_tile_cols(const cdb_gemm_problem_abi* g, int n, int sms, doubl
 // 2.25 tiles) and there are half as many tile slots.  The pair kernel also wins near-ties (within 8 %): where
 // one wave is not full, the narrow single-CTA tiles the model would pick gain nothing in practice (576 x 3072 x
 // 15360: 58.5 us at 112 columns as at 256, 50.8 us with pairs).
+// Pair tiles may be narrower than 256 columns (a multiple of 32: each CTA holds half of the weight tile), but only
+// when forced (tuning knobs): timed on the rank-shard shapes a K block of a pair tile takes 0.39 - 0.44 us at 128,
+// 192 and 256 columns alike, with or without its loads, so a narrower tile never buys back what its extra tiles
+// cost (576 x 3072 x 15360, 36 wide tiles for 74 pairs: 53.7 / 52.4 / 53.3 us at 256 / 192 / 128 columns;
+// 2304 x 21504 x 3072: 128 / 159 / 217 us).
 static double pair_cost(const cdb_gemm_problem_abi* g, int n, int sms) {
   int64_t tiles = 0;
   double per_tile = 0.0;
@@ -1182,17 +1190,24 @@ extern "C" int cdb_fp8_gemm_rowscaled_grouped_act(const void* problems_v, int co
   // whichever kernel the wave-count model expects to finish first
   double single_cost = 0.0;
   const int single_bn = choose_tile_cols(g, n, sms, &single_cost);
-  const bool width_forced = g_forced_tile_cols.load(std::memory_order_relaxed) != 0;  // a forced width means the single-CTA kernel
+  // a forced width means the single-CTA kernel, unless the pair kernel is forced as well (then: a multiple of 32)
+  const int forced_cols = g_forced_tile_cols.load(std::memory_order_relaxed);
+  int pair_bn = BN;
+  const double pair_c = pair_cost(g, n, sms);
+  if (mode == 2 && forced_cols != 0) {
+    if (forced_cols % 32 != 0) return CDB_ERR_UNSUPPORTED;
+    pair_bn = forced_cols;
+  }
   const bool pair = mode == 2 || (mode == 0 && CDB_GEMM_DEFAULT_PAIR &&
-                                  (g[0].M >= 4096 || (!width_forced && pair_cost(g, n, sms) < 1.08 * single_cost)));
+                                  (g[0].M >= 4096 || (forced_cols == 0 && pair_c < 1.08 * single_cost)));
   const int64_t tile_rows = pair ? P_BM : BM;
-  const int bn = pair ? BN : single_bn;
+  const int bn = pair ? pair_bn : single_bn;
   GemmProblems ps{};
   ps.count = n;
   int64_t tiles = 0;
   for (int i = 0; i < n; ++i) {
     GemmProblem& o = ps.p[i];
-    const uint32_t a_box = pair ? 128 : BM, w_box = pair ? 128 : (uint32_t)bn;
+    const uint32_t a_box = pair ? 128 : BM, w_box = pair ? (uint32_t)bn / 2 : (uint32_t)bn;
     if (!operand_map(&o.map_a, g[i].a_q, (uint64_t)g[i].M, (uint64_t)g[i].K, a_box) ||
         !operand_map(&o.map_w, g[i].w_q, (uint64_t)g[i].N, (uint64_t)g[i].K, w_box) ||
         !output_map(&o.map_out, g[i].out, (uint64_t)g[i].M, (uint64_t)g[i].N, (uint64_t)g[i].ld_out)) {
@@ -1209,7 +1224,7 @@ extern "C" int cdb_fp8_gemm_rowscaled_grouped_act(const void* problems_v, int co
     o.out = static_cast<__nv_bfloat16*>(g[i].out);
     o.ld_out = g[i].ld_out;
     o.bn = bn;
-    o.idesc = idesc_e4m3_f32(BM, bn);
+    o.idesc = pair ? idesc_e4m3_f32(P_BM, bn) : idesc_e4m3_f32(BM, bn);
     o.n_tiles = (int)((g[i].N + bn - 1) / bn);
     o.k_blocks = (int)((g[i].K + BK - 1) / BK);
     o.group_m = tile_group_rows(o.m_tiles);

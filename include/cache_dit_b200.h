@@ -219,7 +219,8 @@ CDB_API int cdb_fp8_gemm_rowscaled(const void* a_q, const float* a_scale, const 
 /* Tuning knob (no counterpart in the reference): the single-CTA tile kernel picks its tile width,
  * a multiple of 16 columns up to 256, from a cost model so that the tiles fill whole waves of SMs; a non-zero
  * `cols` fixes the width for every later launch of the process, 0 restores the model.  The environment variable
- * CDB_GEMM_BN sets the initial value.  Results do not depend on the width (bitwise). */
+ * CDB_GEMM_BN sets the initial value.  Results do not depend on the width (bitwise).  Together with
+ * cdb_tuning_set_gemm_kernel(2) a multiple of 32 fixes the width of the CTA-pair kernel's tiles instead. */
 CDB_API int cdb_tuning_set_gemm_tile_cols(int cols);
 /* Tuning knob (no counterpart in the reference): which tile kernel the FP8 product launches.  0 = chosen per
  * launch by a wave-count model, 1 = the single-CTA kernel, 2 = the CTA-pair kernel (cta_group::2).  The

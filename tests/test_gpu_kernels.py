@@ -284,10 +284,12 @@ def test_fp8_gemm_pair_kernel_gives_the_single_cta_kernels_bits(nat, shapes):
   """Below 4096 rows a wave-count model picks the single-CTA or the CTA-pair kernel per launch (rank shards of a
   context-parallel run).  Both accumulate every output element over the K blocks in the same order, so the
   choice must not change a bit: rows that fill a quarter of a 256-row pair tile, ragged row and column counts,
-  a strided output, and two products in one launch."""
+  a strided output, two products in one launch, and pair tiles narrower than 256 columns (the launch model uses
+  128 where the wide tiles would leave most pairs idle)."""
   lib = nat.lib()
-  problems = {1: [], 2: [], 0: []}
-  wides = {1: [], 2: [], 0: []}
+  kinds = (1, 2, 0, (2, 128), (2, 192), (2, 64), (2, 32))  # (2, cols): the pair kernel at a forced tile width
+  problems = {k: [] for k in kinds}
+  wides = {k: [] for k in kinds}
   for i, (M, N, K) in enumerate(shapes):
     x_d, _ = activations(M, K, M + K + i)
     w_d, _ = activations(N, K, N + K + i)
@@ -299,22 +301,24 @@ def test_fp8_gemm_pair_kernel_gives_the_single_cta_kernels_bits(nat, shapes):
     sw = torch.empty(N, dtype=torch.float32, device="cuda")
     nat.fp8_quant_rows(x_d, aq, sa)
     nat.fp8_quant_rows(w_d, wq, sw)
-    for kind in (1, 2, 0):
+    for kind in kinds:
       wide = torch.full((M, N + 24), float("nan"), dtype=torch.bfloat16, device="cuda")
       wides[kind].append(wide)
       problems[kind].append((aq, sa, wq, sw, b, wide[:, 8:8 + N]))
   try:
-    for kind in (1, 2, 0):
-      assert lib.cdb_tuning_set_gemm_kernel(kind) == 0
+    for kind in kinds:
+      k, cols = kind if isinstance(kind, tuple) else (kind, 0)
+      assert lib.cdb_tuning_set_gemm_kernel(k) == 0 and lib.cdb_tuning_set_gemm_tile_cols(cols) == 0
       nat.fp8_gemm_rowscaled_grouped(problems[kind])
       torch.cuda.synchronize()
     assert lib.cdb_tuning_set_gemm_kernel(3) != 0
   finally:
     lib.cdb_tuning_set_gemm_kernel(0)
+    lib.cdb_tuning_set_gemm_tile_cols(0)
   for i, (M, N, K) in enumerate(shapes):
     single = wides[1][i]
     assert torch.isfinite(single[:, 8:8 + N]).all()
-    for kind in (2, 0):
+    for kind in kinds[1:]:
       assert torch.equal(wides[kind][i][:, 8:8 + N], single[:, 8:8 + N]), (kind, i)
       assert torch.isnan(wides[kind][i][:, :8]).all() and torch.isnan(wides[kind][i][:, 8 + N:]).all(), (kind, i)
   assert nat.gemm_device_status(torch.device("cuda")) == 0
