@@ -1,10 +1,13 @@
 // Row-scaled FP8 (e4m3) GEMM for sm_100a: out[m,n] = (sum_k A[m,k] W[n,k]) * sa[m] * sw[n] (+ bias[n])
 //
 // Blackwell-native structure
-//   * operands: TMA (cp.async.bulk.tensor.2d, 128-byte swizzle) into a 4-stage shared-memory ring,
-//     one CTA per SM, every CTA loads its own tiles (no cluster-wide loads);
-//   * math: tcgen05.mma.cta_group::1.kind::f8f6f4, 128 x 256 x 32 per instruction, issued by one
-//     elected thread, fp32 accumulators in tensor memory (TMEM);
+//   * operands: TMA (cp.async.bulk.tensor.2d, 128-byte swizzle) into a shared-memory ring of 4 to 8 stages
+//     (192 KB; 6 stages of 32 KB in the CTA-pair kernel), one CTA per SM, every CTA loads its own tiles (no
+//     cluster-wide loads);
+//   * math: tcgen05.mma.kind::f8f6f4 issued by one elected thread, fp32 accumulators in tensor memory (TMEM):
+//     cta_group::1, 128 x bn x 32 per instruction (bn a multiple of 16 up to 256) in the single-CTA kernel,
+//     cta_group::2, 256 x 256 x 32 over a pair of SMs in the CTA-pair kernel further down;
+//   * an optional tanh-GELU of output columns in the epilogue (the MLP-in projection of a transformer block);
 //   * two 256-column TMEM accumulators so the epilogue of tile i overlaps the main loop of tile i+1;
 //   * epilogue: tcgen05.ld (32 lanes x 32 columns per warp), per-row x per-column scale, optional
 //     bias, bf16 pack into a swizzled shared-memory staging block, TMA store (cp.async.bulk.tensor
