@@ -147,20 +147,29 @@ class FusedFloat8Linears(torch.nn.Module):
       start += n
 
   def gelu_column(self, gelu_last: bool):
-    """First output column of the last member (whose output is to be activated), or None."""
-    return self.out_features - self.splits[-1] if gelu_last else None
+    """First output column of the last member (whose output is to be activated by the product's epilogue), or
+    None: no activation wanted, or the member does not start on a multiple of 8 columns (the epilogue decides per
+    16-byte chunk; the caller then activates the split itself)."""
+    col = self.out_features - self.splits[-1]
+    return col if gelu_last and col % 8 == 0 else None
+
+  def finish(self, out: torch.Tensor, lead_shape, gelu_last: bool):
+    """The members' outputs as views of the product; activates the last one here when the epilogue could not."""
+    parts = list(out.view(*lead_shape, self.out_features).split(self.splits, dim=-1))
+    if gelu_last and self.gelu_column(True) is None:
+      parts[-1] = torch.nn.functional.gelu(parts[-1], approximate="tanh")
+    return tuple(parts)
 
   def forward_quantized(self, a_q: torch.Tensor, a_scale: torch.Tensor, lead_shape, gelu_last: bool = False):
-    """`gelu_last`: the last member's output passes through tanh-GELU in the epilogue (the MLP-in projection
-    behind q/k/v)."""
+    """`gelu_last`: the last member's output passes through tanh-GELU, in the product's epilogue where possible
+    (the MLP-in projection behind q/k/v)."""
     out = torch.empty((a_q.shape[0], self.out_features), dtype=torch.bfloat16, device=a_q.device)
-    if gelu_last:
-      _native.fp8_gemm_rowscaled_grouped([(a_q, a_scale, self.weight_q, self.weight_scale, self.bias, out)],
-                                         [self.gelu_column(True)])
+    col = self.gelu_column(gelu_last)
+    if col is not None:
+      _native.fp8_gemm_rowscaled_grouped([(a_q, a_scale, self.weight_q, self.weight_scale, self.bias, out)], [col])
     else:
       _native.fp8_gemm_rowscaled(a_q, a_scale, self.weight_q, self.weight_scale, self.bias, out)
-    out = out.view(*lead_shape, self.out_features)
-    return out.split(self.splits, dim=-1)
+    return self.finish(out, lead_shape, gelu_last)
 
 
 def _members_share_storage(fused: FusedFloat8Linears, linears) -> bool:
@@ -208,6 +217,8 @@ def grouped_forward_quantized(items, gelu_last: bool = False):
     _native.fp8_gemm_rowscaled_grouped(problems[i:i + 2], None if act is None else act[i:i + 2])
   results = []
   for (m, _, _, lead), out in zip(items, outs):
-    out = out.view(*lead, m.out_features)
-    results.append(out.split(m.splits, dim=-1) if isinstance(m, FusedFloat8Linears) else out)
+    if isinstance(m, FusedFloat8Linears):
+      results.append(m.finish(out, lead, gelu_last))
+    else:
+      results.append(out.view(*lead, m.out_features))
   return results

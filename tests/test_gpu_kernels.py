@@ -634,3 +634,26 @@ def test_fused_linear_group_follows_its_members_when_they_move():
   outs = second.forward_quantized(a_q, a_scale, (64, ))
   separate = [l.forward_quantized(a_q, a_scale, (64, )) for l in holder.lins]
   assert all(torch.equal(o, s) for o, s in zip(outs, separate))
+
+
+@pytest.mark.parametrize("sizes", [(128, 128, 256), (40, 24)])
+def test_fused_group_activates_its_last_member(sizes):
+  """`gelu_last` returns the last member's output activated by the product's epilogue (FP8 linears have a multiple
+  of 8 output features, so a member always starts on a 16-byte chunk): the other members keep the plain product's
+  bits and the last one is gelu of them."""
+  from cache_dit_b200.quantization.linear import Float8RowwiseLinear, fused_group, grouped_forward_quantized
+  torch.manual_seed(4)
+  dev = torch.device("cuda")
+  lins = [Float8RowwiseLinear.from_linear(torch.nn.Linear(64, n).to(torch.bfloat16).to(dev)) for n in sizes]
+  x = torch.randn(40, 64, device=dev).to(torch.bfloat16)
+  a_q, a_scale = lins[0].quantize_input(x)
+  group = fused_group(lins)
+  plain = [o.clone() for o in group.forward_quantized(a_q, a_scale, (40, ))]
+  acted = group.forward_quantized(a_q, a_scale, (40, ), gelu_last=True)
+  (paired, ) = grouped_forward_quantized([(group, a_q, a_scale, (40, ))], gelu_last=True)
+  for got in (acted, paired):
+    for a, b in zip(plain[:-1], got[:-1]):
+      assert torch.equal(a, b)
+    want = torch.nn.functional.gelu(plain[-1].float(), approximate="tanh").to(torch.bfloat16)
+    err = (got[-1].float() - want.float()).abs()
+    assert bool((err <= 2.0 ** -7 * want.float().abs() + 1e-6).all())
