@@ -45,6 +45,7 @@ SIGNATURES = {
                                      c_int64, c_int64, c_int64, c_void_p, c_void_p]),
   "cdb_fp8_gemm_rowscaled_grouped": (c_int, [c_void_p, c_int, c_void_p, c_void_p]),
   "cdb_fp8_gemm_rowscaled_grouped_act": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
+  "cdb_fp8_gemm_plan": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p]),
   "cdb_tuning_set_gemm_tile_cols": (c_int, [c_int]),
   "cdb_tuning_set_gemm_kernel": (c_int, [c_int]),
   "cdb_qk_norm_rope": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
@@ -551,6 +552,18 @@ class GemmProblem(ctypes.Structure):
   """ctypes image of `cdb_gemm_problem`."""
   _fields_ = [("a_q", c_void_p), ("a_scale", c_void_p), ("w_q", c_void_p), ("w_scale", c_void_p), ("bias", c_void_p),
               ("out", c_void_p), ("M", c_int64), ("N", c_int64), ("K", c_int64), ("ld_out", c_int64)]
+
+
+def fp8_gemm_plan(shapes, sm_count=148):
+  """(kind, tile_cols) a launch of these one or two (M, N, K) problems would take on a GPU with `sm_count` SMs:
+  kind 1 = single-CTA tile kernel, 2 = CTA-pair kernel, 3 = few-row kernel.  Host arithmetic only (no GPU)."""
+  arr = (GemmProblem * len(shapes))()
+  for slot, (M, N, K) in zip(arr, shapes):
+    slot.M, slot.N, slot.K, slot.ld_out = M, N, K, N
+  kind, cols = c_int(0), c_int(0)
+  check(lib().cdb_fp8_gemm_plan(ctypes.cast(arr, c_void_p), len(shapes), sm_count, ctypes.byref(kind), ctypes.byref(cols)),
+        "cdb_fp8_gemm_plan")
+  return kind.value, cols.value
 
 
 def fp8_gemm_rowscaled_grouped(problems, gelu_from=None):

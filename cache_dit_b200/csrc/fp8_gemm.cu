@@ -1124,6 +1124,54 @@ static double pair_cost(const cdb_gemm_problem_abi* g, int n, int sms) {
   return waves * per_tile + 3000.0;
 }
 
+// Which tile kernel a launch takes and at which tile width (host arithmetic only).  CTA pairs for tall problems;
+// below 4096 rows (rank shards of a context-parallel run: 2304, 1152, 576 rows) whichever kernel the wave-count
+// model expects to finish first.  `g` holds the problems with rows > 0, the one with more rows first.
+static int plan_launch(const cdb_gemm_problem_abi* g, int n, int sms, bool* pair_out, int* bn_out) {
+  const int mode = g_forced_kernel.load(std::memory_order_relaxed);
+  double single_cost = 0.0;
+  const int single_bn = choose_tile_cols(g, n, sms, &single_cost);
+  // a forced width means the single-CTA kernel, unless the pair kernel is forced as well (then: a multiple of 32)
+  const int forced_cols = g_forced_tile_cols.load(std::memory_order_relaxed);
+  int pair_bn = BN;
+  const double pair_c = pair_cost(g, n, sms);
+  if (mode == 2 && forced_cols != 0) {
+    if (forced_cols % 32 != 0) return CDB_ERR_UNSUPPORTED;
+    pair_bn = forced_cols;
+  }
+  const bool pair = mode == 2 || (mode == 0 && CDB_GEMM_DEFAULT_PAIR &&
+                                  (g[0].M >= 4096 || (forced_cols == 0 && pair_c < 1.08 * single_cost)));
+  *pair_out = pair;
+  *bn_out = pair ? pair_bn : single_bn;
+  return CDB_OK;
+}
+
+// The plan of a launch without launching it: kind 1 = single-CTA tile kernel, 2 = CTA-pair kernel, 3 = few-row
+// weight-streaming kernel.  Touches no GPU: `sm_count` is given (148 on a B200).
+extern "C" int cdb_fp8_gemm_plan(const void* problems_v, int count, int sm_count_hint, int* kind, int* tile_cols) {
+  const cdb_gemm_problem_abi* in = static_cast<const cdb_gemm_problem_abi*>(problems_v);
+  if (!in || !kind || !tile_cols || count < 1 || count > MAX_PROBLEMS || sm_count_hint < 2) return CDB_ERR_BAD_ARGUMENT;
+  cdb_gemm_problem_abi g[MAX_PROBLEMS];
+  int n = 0;
+  for (int i = 0; i < count; ++i) {
+    if (in[i].M < 0 || in[i].N <= 0 || in[i].K <= 0) return CDB_ERR_BAD_ARGUMENT;
+    if (in[i].M > 0) g[n++] = in[i];
+  }
+  *kind = 0;
+  *tile_cols = 0;
+  if (n == 0) return CDB_OK;
+  if (n == 2 && g[1].M > g[0].M) std::swap(g[0], g[1]);
+  if (n == 1 && g_forced_kernel.load(std::memory_order_relaxed) == 0 && g[0].M <= GEMV_MAX_M &&
+      g[0].M * g[0].K * 2 <= 48 * 1024) {
+    *kind = 3;
+    return CDB_OK;
+  }
+  bool pair = false;
+  const int rc = plan_launch(g, n, sm_count_hint, &pair, tile_cols);
+  *kind = pair ? 2 : 1;
+  return rc;
+}
+
 static int launch_few_rows(const cdb_gemm_problem_abi& g, int sms, cudaStream_t st) {
   const uint8_t* ap = static_cast<const uint8_t*>(g.a_q);
   const uint8_t* wp = static_cast<const uint8_t*>(g.w_q);
@@ -1189,22 +1237,11 @@ extern "C" int cdb_fp8_gemm_rowscaled_grouped_act(const void* problems_v, int co
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (n == 1 && mode == 0 && !any_act && g[0].M <= GEMV_MAX_M && g[0].M * g[0].K * 2 <= 48 * 1024)
     return launch_few_rows(g[0], sms, st);
-  // CTA pairs for tall problems; below 4096 rows (rank shards of a context-parallel run: 2304, 1152, 576 rows)
-  // whichever kernel the wave-count model expects to finish first
-  double single_cost = 0.0;
-  const int single_bn = choose_tile_cols(g, n, sms, &single_cost);
-  // a forced width means the single-CTA kernel, unless the pair kernel is forced as well (then: a multiple of 32)
-  const int forced_cols = g_forced_tile_cols.load(std::memory_order_relaxed);
-  int pair_bn = BN;
-  const double pair_c = pair_cost(g, n, sms);
-  if (mode == 2 && forced_cols != 0) {
-    if (forced_cols % 32 != 0) return CDB_ERR_UNSUPPORTED;
-    pair_bn = forced_cols;
-  }
-  const bool pair = mode == 2 || (mode == 0 && CDB_GEMM_DEFAULT_PAIR &&
-                                  (g[0].M >= 4096 || (forced_cols == 0 && pair_c < 1.08 * single_cost)));
+  bool pair = false;
+  int bn = BN;
+  const int plan_rc = plan_launch(g, n, sms, &pair, &bn);
+  if (plan_rc != CDB_OK) return plan_rc;
   const int64_t tile_rows = pair ? P_BM : BM;
-  const int bn = pair ? pair_bn : single_bn;
   GemmProblems ps{};
   ps.count = n;
   int64_t tiles = 0;

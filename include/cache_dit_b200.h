@@ -221,6 +221,11 @@ CDB_API int cdb_fp8_gemm_rowscaled(const void* a_q, const float* a_scale, const 
  * `cols` fixes the width for every later launch of the process, 0 restores the model.  The environment variable
  * CDB_GEMM_BN sets the initial value.  Results do not depend on the width (bitwise).  Together with
  * cdb_tuning_set_gemm_kernel(2) a multiple of 32 fixes the width of the CTA-pair kernel's tiles instead. */
+/* What a launch of cdb_fp8_gemm_rowscaled_grouped would run for these problems on a GPU with `sm_count` SMs, without
+ * launching anything or touching a GPU (only M, N, K of the problems are read): *kind = 1 single-CTA tile kernel,
+ * 2 CTA-pair kernel, 3 few-row weight-streaming kernel, 0 nothing to do; *tile_cols = the tile width (0 for kind 3). */
+CDB_API int cdb_fp8_gemm_plan(const void* problems /* cdb_gemm_problem[count] */, int count, int sm_count, int* kind,
+                      int* tile_cols);
 CDB_API int cdb_tuning_set_gemm_tile_cols(int cols);
 /* Tuning knob (no counterpart in the reference): which tile kernel the FP8 product launches.  0 = chosen per
  * launch by a wave-count model, 1 = the single-CTA kernel, 2 = the CTA-pair kernel (cta_group::2).  The
